@@ -1,0 +1,382 @@
+"""Benchmark of the ConvNN-Attention forward path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N=1 and per GPU at N>1, weak scaling): ViT-Tiny with ConvNN-Attention layers,
+bfloat16 inference, batch 256 x 3 x 224 x 224 synthetic N(0,1) images, patch 16 -> 197
+tokens, d=192, 12 layers, 1000 classes, K=9, cosine similarity, sampling 'all', depthwise
+conv, random-init weights.  A step is one forward of the whole model on one batch per GPU.
+
+One JSON line on stdout (rank 0).  `value` = images/s with inputs resident in HBM, timed
+with CUDA events on the launching stream, max over ranks.  `e2e` = the same through the
+public module call with HOST (pinned) images: the host->device copy and the device->host
+read of the logits are inside the timed region.  `roofline` describes the layer kernel
+with the largest share of device time, timed with CUDA events around the stage calls.
+`cpu_baseline` / `--impl reference` time the CPU oracle port of the same model on the host
+cores (the reference is eager PyTorch; its checkout does not travel to the GPU box).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+WORKLOAD = dict(layer="ConvNNAttention", img_size=(3, 224, 224), patch_size=16, num_layers=12, num_heads=1,
+                d_hidden=192, d_mlp=768, num_classes=1000, K=9, magnitude_type="cosine", sampling_type="all",
+                convolution_type="depthwise", softmax_topk_val=True, dropout=0.0, attention_dropout=0.0)
+BATCH_PER_GPU = 256
+METRIC, UNIT = "ConvNN-ViT images/sec", "images/s"
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            m = json.load(f)
+        return dict(hbm=m["hbm_gbs"], tf_burst=m["bf16_tflops"], tf_sustained=m["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm=6650.0, tf_burst=1590.0, tf_sustained=1400.0, source="fallback")
+
+
+# ---------------------------------------------------------------------------------------
+# CPU arm: the oracle port of the reference model on the host cores
+# ---------------------------------------------------------------------------------------
+
+def cpu_model_throughput(batch: int, steps: int, warmup: int, budget_s: float = 30.0):
+    """images/s of the CPU oracle (fp32, all host threads) on ``batch`` images per step."""
+    from oracle.vit_oracle import ViTConfig, make_images, make_vit_weights, vit_forward
+    cfg = ViTConfig(**WORKLOAD)
+    sd = make_vit_weights(cfg, seed=1)
+    img = make_images(batch, cfg, seed=2)
+    cores = torch.get_num_threads()
+    with torch.no_grad():
+        for _ in range(warmup):
+            vit_forward(img, sd, cfg)
+        times = []
+        t_start = time.perf_counter()
+        for _ in range(steps):
+            t0 = time.perf_counter()
+            vit_forward(img, sd, cfg)
+            times.append(time.perf_counter() - t0)
+            if time.perf_counter() - t_start > budget_s:
+                break
+    per = sum(times) / len(times)
+    return batch / per, per, cores, len(times)
+
+
+def run_reference_arm(args) -> int:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    batch = 32
+    steps = max(1, min(args.steps, 10))
+    v, per, cores, done = cpu_model_throughput(batch, steps, max(1, min(args.warmup, 2)), budget_s=120.0)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": done,
+        "warmup": max(1, min(args.warmup, 2)), "ms_per_step": per * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "cfg-2 ViT-Tiny ConvNNAttention 224x224 patch16 K=9 cosine/all/depthwise",
+                   "batch_per_step": batch},
+        "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"{done} forwards of {batch} images (of the 256-image batch), fp32, torch CPU"},
+        "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+# ---------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------
+
+class ClockSampler:
+    """nvidia-smi clock / throttle samples taken while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                       "-lms", "100", "-i", str(index)], stdout=self.f, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.p = None
+
+    def stop(self) -> dict:
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.p.kill()
+        self.f.flush()
+        self.f.seek(0)
+        rows = [r.strip().split(", ") for r in self.f.read().strip().splitlines() if r.strip()]
+        self.f.close()
+        os.unlink(self.f.name)
+        sm, smax, reasons = [], None, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in rows:
+            if len(r) < 7:
+                continue
+            try:
+                sm.append(float(r[0]))
+                smax = float(r[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v.strip().lower() == "active":
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": smax, "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+class StageTimer:
+    """Collects CUDA events between the stage calls of every ConvNN layer."""
+
+    def __init__(self):
+        self.marks = []
+
+    def __call__(self, label):
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        self.marks.append((label, e))
+
+    def totals(self):
+        tot, cnt = {}, {}
+        for (l0, e0), (l1, e1) in zip(self.marks, self.marks[1:]):
+            if l1 == "begin":
+                continue
+            tot[l1] = tot.get(l1, 0.0) + e0.elapsed_time(e1)
+            cnt[l1] = cnt.get(l1, 0) + 1
+        return tot, cnt
+
+
+def algorithmic_work(B, T, S, D, H, K, elt=2):
+    """Compulsory bytes / flops per launch of each stage (one layer call)."""
+    idxval = 8 * B * H * T * K
+    return {
+        "qkv_proj": dict(bytes=elt * (B * T * D + 3 * D * D + B * (2 * T + S) * D) + 4 * B * H * (T + S),
+                         flops=2 * B * (2 * T + S) * D * D),
+        "sim_topk": dict(bytes=elt * (B * T * D + B * S * D) + idxval + 4 * B * H * (T + S), flops=2 * B * T * S * D),
+        "gather_conv": dict(bytes=elt * (2 * B * T * D + K * D) + idxval, flops=2 * B * T * D * K),
+        "out_proj": dict(bytes=elt * (2 * B * T * D + D * D), flops=2 * B * T * D * D),
+    }
+
+
+def run_ours(args) -> int:
+    import torch.distributed as dist
+    import convnn_b200
+    from convnn_b200 import _capi
+    from convnn_b200.sharded import gather_logits
+    from oracle.vit_oracle import ViTConfig, make_vit_weights  # seeded weights only (not on the timed path)
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the ConvNN path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _capi.lib()
+
+    cfg = ViTConfig(**WORKLOAD)
+    margs = convnn_b200.make_args(**WORKLOAD, device=dev)
+    model = convnn_b200.ViT(margs).eval()
+    model.load_state_dict(make_vit_weights(cfg, seed=1), strict=True)
+    model = model.to(dev, torch.bfloat16)
+    B = BATCH_PER_GPU
+    g = torch.Generator(device="cpu").manual_seed(100 + rank)
+    NBUF = 3   # 3 x 77 MB of distinct resident inputs > 126 MB L2
+    host = [torch.randn(B, 3, 224, 224, generator=g).to(torch.bfloat16).pin_memory() for _ in range(NBUF)]
+    resident = [h.to(dev) for h in host]
+    static_in = torch.empty_like(resident[0])
+    total = B * world
+
+    def step_eager(x):
+        logits = model(x)
+        return gather_logits(logits, total) if world > 1 else logits
+
+    # CUDA graph of the whole forward (ctypes launches on the capturing stream are captured)
+    graph, static_out, graph_note, per_forward = None, None, "eager", 0
+    with torch.no_grad():
+        for _ in range(2):
+            static_in.copy_(resident[0])
+            model(static_in)
+        torch.cuda.synchronize()
+        if not args.no_graph:
+            try:
+                n_cap = lib.convnn_b200_launch_count()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    static_out = model(static_in)
+                per_forward = lib.convnn_b200_launch_count() - n_cap
+                graph_note = "cuda_graph"
+            except Exception as e:  # noqa: BLE001
+                graph, graph_note = None, f"eager (graph capture failed: {type(e).__name__})"
+                torch.cuda.synchronize()
+
+    def step(x):
+        if graph is not None:
+            static_in.copy_(x, non_blocking=True)
+            graph.replay()
+            logits = static_out
+        else:
+            logits = model(x)
+        return gather_logits(logits, total) if world > 1 else logits
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.no_grad():
+        # ---- device-resident timing -------------------------------------------------------
+        for i in range(args.warmup):
+            step(resident[i % NBUF])
+        barrier()
+        sampler = ClockSampler(local) if rank == 0 else None
+        n0 = lib.convnn_b200_launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            step(resident[i % NBUF])
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        launches_eager = lib.convnn_b200_launch_count() - n0
+        clocks = sampler.stop() if sampler else None
+
+        # ---- end to end: pinned host images in, logits out ------------------------------------
+        copy_stream = torch.cuda.Stream(dev)
+        staging = [torch.empty_like(resident[0]) for _ in range(2)]
+        out_host = torch.empty(total if world > 1 else B, WORKLOAD["num_classes"], dtype=torch.bfloat16).pin_memory()
+        ready = [torch.cuda.Event() for _ in range(2)]
+        freed = [torch.cuda.Event() for _ in range(2)]
+
+        def e2e_run(n):
+            cur = torch.cuda.current_stream()
+            for f in freed:
+                f.record(cur)
+            for i in range(n):
+                s = i % 2
+                with torch.cuda.stream(copy_stream):
+                    copy_stream.wait_event(freed[s])
+                    staging[s].copy_(host[i % NBUF], non_blocking=True)
+                    ready[s].record(copy_stream)
+                cur.wait_event(ready[s])
+                logits = step(staging[s])
+                freed[s].record(cur)
+                out_host.copy_(logits, non_blocking=True)
+
+        e2e_run(max(2, args.warmup))
+        barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        e2e_run(args.steps)
+        f1.record()
+        barrier()
+        ms_e2e = f0.elapsed_time(f1)
+
+        # ---- per-stage events for the roofline (same kernels through the stage entry points) -----
+        timer = StageTimer()
+        convs = [m for m in model.modules() if isinstance(m, convnn_b200.MultiHeadConvNNAttention)]
+        for m in convs:
+            m.stage_timer = timer
+        for i in range(2):
+            model(resident[i % NBUF])
+        torch.cuda.synchronize()
+        timer.marks.clear()
+        nprof = max(3, min(args.steps, 10))
+        for i in range(nprof):
+            model(resident[i % NBUF])
+        torch.cuda.synchronize()
+        stage_ms, stage_n = timer.totals()
+        for m in convs:
+            m.stage_timer = None
+
+    t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, ms_e2e = float(t[0]), float(t[1])
+
+    if rank == 0:
+        pk = peaks()
+        T = cfg.seq_len
+        work = algorithmic_work(B, T, T, cfg.d_hidden, cfg.num_heads, cfg.K)
+        dom = max(stage_ms, key=stage_ms.get)
+        per_launch_ms = stage_ms[dom] / stage_n[dom]
+        ridge = pk["tf_sustained"] * 1e3 / pk["hbm"]
+        ai = work[dom]["flops"] / work[dom]["bytes"]
+        if ai > ridge:
+            bound, ach, peak, unit = "tensor", work[dom]["flops"] / per_launch_ms / 1e9, pk["tf_sustained"], "TFLOP/s"
+        else:
+            bound, ach, peak, unit = "hbm", work[dom]["bytes"] / per_launch_ms / 1e6, pk["hbm"], "GB/s"
+        stages = {k: {"ms_per_launch": stage_ms[k] / stage_n[k],
+                      "GBps": work[k]["bytes"] / (stage_ms[k] / stage_n[k]) / 1e6,
+                      "TFLOPs": work[k]["flops"] / (stage_ms[k] / stage_n[k]) / 1e9} for k in stage_ms}
+        cpu_v, cpu_per, cores, cpu_done = (None, None, None, 0)
+        cpu = None
+        if world == 1 and not args.no_cpu:
+            cpu_v, cpu_per, cores, cpu_done = cpu_model_throughput(32, 8, 1, budget_s=20.0)
+            cpu = {"value": cpu_v, "unit": UNIT, "cores": cores, "kind": "port",
+                   "sample": f"{cpu_done} forwards of 32 images (of the 256-image batch), fp32, torch CPU oracle"}
+        h2d = B * 3 * 224 * 224 * 2
+        d2h = out_host.numel() * 2
+        line = {
+            "metric": METRIC, "value": total * args.steps / (ms / 1e3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "cfg-2 ViT-Tiny ConvNNAttention bf16 inference 224x224 patch16 (197 tokens) "
+                                   "d=192 12 layers 1000 classes K=9 cosine/all/depthwise",
+                       "batch_per_gpu": B, "global_batch": total, "parallelism": f"batch-shard x{world}",
+                       "l2": f"{NBUF} distinct resident input batches (231 MB) rotate, larger than L2",
+                       "launch": graph_note},
+            "e2e": {"value": total * args.steps / (ms_e2e / 1e3), "unit": UNIT, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": int(launches_eager) if graph is None else int(per_forward * args.steps),
+            "roofline": {"bound": bound, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak,
+                         "traffic": None, "kernel": dom, "peak_source": pk["source"],
+                         "ms_per_launch": per_launch_ms, "stages": stages},
+            "cpu_baseline": cpu,
+            "clocks": clocks,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        return run_reference_arm(args)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,239 @@
+// extern "C" surface of libconvnn_b200: argument validation, workspace carving and the
+// chaining of the stage kernels on the caller's stream.
+#include <atomic>
+#include <stdarg.h>
+#include <string.h>
+
+#include "common.cuh"
+
+namespace convnn {
+
+static thread_local char g_err[512] = "";
+
+int set_error(int status, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return status;
+}
+void clear_error() { g_err[0] = 0; }
+
+static std::atomic<unsigned long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+int validate(const convnn_desc* d, Dims* out) {
+    if (!d) return set_error(CONVNN_E_NULL, "descriptor is NULL");
+    if (d->B < 1 || d->T < 1 || d->S < 1 || d->D < 1 || d->H < 1 || d->K < 1)
+        return set_error(CONVNN_E_INVALID, "B, T, S, D, H, K must be positive (got %d %d %d %d %d %d)", d->B, d->T,
+                         d->S, d->D, d->H, d->K);
+    if (d->D % d->H != 0) return set_error(CONVNN_E_INVALID, "d_hidden must be divisible by num_heads");
+    if (d->dtype != CONVNN_F32 && d->dtype != CONVNN_BF16) return set_error(CONVNN_E_INVALID, "unknown dtype %d", d->dtype);
+    if (d->metric < 0 || d->metric > 2) return set_error(CONVNN_E_INVALID, "unknown metric %d", d->metric);
+    if (d->conv_type < 0 || d->conv_type > 2) return set_error(CONVNN_E_INVALID, "unknown conv_type %d", d->conv_type);
+    if (d->reserved != 0) return set_error(CONVNN_E_INVALID, "reserved field must be 0");
+    if (!d->sampled && d->S != d->T)
+        return set_error(CONVNN_E_INVALID, "sampling 'all' needs S == T (got S=%d, T=%d)", d->S, d->T);
+    if (d->coord && d->conv_type == CONVNN_DEPTHWISE)
+        return set_error(CONVNN_E_INVALID, "coordinate_encoding with a depthwise conv is rejected by the reference "
+                                           "(out_channels not divisible by groups)");
+    const int nsel = d->sampled ? d->K - 1 : d->K;
+    if (nsel > d->S) return set_error(CONVNN_E_TOPK_RANGE, "selected index k out of range");
+    if (d->K > kMaxK) return set_error(CONVNN_E_UNSUPPORTED, "K=%d exceeds this build's limit of %d", d->K, kMaxK);
+    if (d->H > 1 && d->T != d->seq_length)
+        return set_error(CONVNN_E_SEQ_LENGTH, "shape '[%d, -1, %d, %d]' is invalid for input of size %lld", d->B,
+                         d->D / d->H, d->seq_length, (long long)d->B * d->T * d->D);
+    if ((long long)d->B * d->T * d->D >= (1ll << 31) || (long long)d->B * d->H * d->T * d->K >= (1ll << 31))
+        return set_error(CONVNN_E_UNSUPPORTED, "tensor exceeds 2^31 elements");
+    if (out) {
+        out->B = d->B; out->T = d->T; out->S = d->S; out->D = d->D; out->H = d->H; out->K = d->K;
+        out->dk = d->D / d->H;
+        out->C = out->dk + (d->coord ? 1 : 0);
+        out->Cp = d->coord ? ((out->dk + 1 + 7) / 8) * 8 : out->dk;
+        out->nsel = nsel;
+        out->elt = d->dtype == CONVNN_F32 ? 4 : 2;
+    }
+    return CONVNN_OK;
+}
+
+namespace {
+
+int check_device() {
+    static std::atomic<int> ok_mask[64];
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) {
+        cudaGetLastError();
+        return set_error(CONVNN_E_DEVICE, "no CUDA device is current");
+    }
+    if (dev < 64 && ok_mask[dev].load(std::memory_order_relaxed) == 1) return CONVNN_OK;
+    int major = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess || major != 10)
+        return set_error(CONVNN_E_DEVICE, "device %d is compute capability %d.x; this library is built for sm_100a only", dev, major);
+    if (dev < 64) ok_mask[dev].store(1, std::memory_order_relaxed);
+    return CONVNN_OK;
+}
+
+struct Workspace {
+    char *q, *k, *v, *o;
+    float *qstat, *kstat, *val;
+    int32_t* idx;
+    size_t total;
+};
+
+size_t up256(size_t n) { return (n + 255) & ~(size_t)255; }
+
+Workspace carve(const Dims& dm, void* base) {
+    Workspace w;
+    char* p = static_cast<char*>(base);
+    size_t off = 0;
+    auto take = [&](size_t bytes) { char* r = p ? p + off : nullptr; off += up256(bytes); return r; };
+    w.q = take((size_t)dm.B * dm.S * dm.H * dm.Cp * dm.elt);
+    w.k = take((size_t)dm.B * dm.T * dm.H * dm.Cp * dm.elt);
+    w.v = take((size_t)dm.B * dm.T * dm.H * dm.Cp * dm.elt);
+    w.o = take((size_t)dm.B * dm.H * dm.T * dm.dk * dm.elt);
+    w.qstat = reinterpret_cast<float*>(take((size_t)dm.B * dm.H * dm.S * 4));
+    w.kstat = reinterpret_cast<float*>(take((size_t)dm.B * dm.H * dm.T * 4));
+    w.val = reinterpret_cast<float*>(take((size_t)dm.B * dm.H * dm.T * dm.K * 4));
+    w.idx = reinterpret_cast<int32_t*>(take((size_t)dm.B * dm.H * dm.T * dm.K * 4));
+    w.total = off;
+    return w;
+}
+
+}  // namespace
+}  // namespace convnn
+
+using namespace convnn;
+
+#define REQUIRE_PTR(p)                                                               \
+    do {                                                                             \
+        if (!(p)) return set_error(CONVNN_E_NULL, "%s: argument '%s' is NULL", __func__, #p); \
+    } while (0)
+
+extern "C" {
+
+int convnn_b200_abi_version(void) { return CONVNN_B200_ABI_VERSION; }
+
+const char* convnn_b200_status_string(int s) {
+    switch (s) {
+        case CONVNN_OK: return "ok";
+        case CONVNN_E_INVALID: return "invalid argument";
+        case CONVNN_E_UNSUPPORTED: return "unsupported configuration";
+        case CONVNN_E_NULL: return "null pointer";
+        case CONVNN_E_ALIGN: return "misaligned pointer or leading dimension";
+        case CONVNN_E_WORKSPACE: return "workspace too small";
+        case CONVNN_E_CUDA: return "CUDA launch failure";
+        case CONVNN_E_DEVICE: return "not an sm_100 device";
+        case CONVNN_E_TOPK_RANGE: return "selected index k out of range";
+        case CONVNN_E_SEQ_LENGTH: return "T != seq_length with num_heads > 1";
+        default: return "unknown status";
+    }
+}
+
+const char* convnn_b200_last_error(void) { return g_err; }
+
+uint64_t convnn_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int convnn_b200_head_channels(const convnn_desc* d) {
+    Dims dm;
+    int rc = validate(d, &dm);
+    return rc != CONVNN_OK ? rc : dm.Cp;
+}
+
+size_t convnn_b200_workspace_bytes(const convnn_desc* d) {
+    Dims dm;
+    if (validate(d, &dm) != CONVNN_OK) return 0;
+    return carve(dm, nullptr).total;
+}
+
+int convnn_b200_qkv_proj(const convnn_desc* d, const void* x, int64_t ldx, const void* w_qkv,
+                         const int32_t* cand, void* q, void* k, void* v, float* qstat, float* kstat,
+                         void* stream) {
+    Dims dm;
+    int rc = validate(d, &dm);
+    if (rc) return rc;
+    REQUIRE_PTR(x); REQUIRE_PTR(w_qkv); REQUIRE_PTR(q); REQUIRE_PTR(k); REQUIRE_PTR(v);
+    if (d->sampled) REQUIRE_PTR(cand);
+    if (d->metric != CONVNN_MATMUL) { REQUIRE_PTR(qstat); REQUIRE_PTR(kstat); }
+    if (ldx < dm.D) return set_error(CONVNN_E_INVALID, "ldx=%lld is smaller than D=%d", (long long)ldx, dm.D);
+    if ((rc = check_device())) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t wsz = (size_t)dm.D * dm.D * dm.elt;
+    GemmParams p{};
+    p.a = x; p.lda = ldx; p.bias = nullptr; p.N = dm.D; p.Kd = dm.D;
+    p.a_mode = A_TOKENS; p.c_mode = C_HEADS; p.T = dm.T; p.H = dm.H; p.dk = dm.dk; p.Cp = dm.Cp; p.gelu = 0;
+    // keys and values: every token
+    p.cand = nullptr; p.rows_per_batch = dm.T; p.M = dm.B * dm.T;
+    p.w = static_cast<const char*>(w_qkv); p.c = k;
+    if ((rc = launch_gemm_simt(d->dtype, p, st))) return rc;
+    p.w = static_cast<const char*>(w_qkv) + wsz; p.c = v;
+    if ((rc = launch_gemm_simt(d->dtype, p, st))) return rc;
+    // queries: candidate tokens only
+    p.cand = d->sampled ? cand : nullptr; p.rows_per_batch = dm.S; p.M = dm.B * dm.S;
+    p.w = static_cast<const char*>(w_qkv) + 2 * wsz; p.c = q;
+    if ((rc = launch_gemm_simt(d->dtype, p, st))) return rc;
+    const bool stats = d->metric != CONVNN_MATMUL;
+    if ((rc = launch_head_fill_and_stats(d, dm, q, dm.S, stats ? qstat : nullptr, st))) return rc;
+    if ((rc = launch_head_fill_and_stats(d, dm, k, dm.T, stats ? kstat : nullptr, st))) return rc;
+    if ((rc = launch_head_fill_and_stats(d, dm, v, dm.T, nullptr, st))) return rc;
+    return CONVNN_OK;
+}
+
+int convnn_b200_sim_topk(const convnn_desc* d, const void* q, const void* k, const float* qstat,
+                         const float* kstat, const int32_t* cand, int32_t* idx, float* val, void* stream) {
+    Dims dm;
+    int rc = validate(d, &dm);
+    if (rc) return rc;
+    REQUIRE_PTR(q); REQUIRE_PTR(k); REQUIRE_PTR(idx); REQUIRE_PTR(val);
+    if (d->sampled) REQUIRE_PTR(cand);
+    if (d->metric != CONVNN_MATMUL) { REQUIRE_PTR(qstat); REQUIRE_PTR(kstat); }
+    if ((rc = check_device())) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (d->dtype == CONVNN_F32) return launch_sim_topk_simt_f32(d, dm, q, k, qstat, kstat, cand, idx, val, st);
+    return launch_sim_topk_simt_bf16(d, dm, q, k, qstat, kstat, cand, idx, val, st);
+}
+
+int convnn_b200_gather_conv(const convnn_desc* d, const void* v, const int32_t* idx, const float* val,
+                            const void* w_conv, const void* w_pw, void* o, void* stream) {
+    Dims dm;
+    int rc = validate(d, &dm);
+    if (rc) return rc;
+    REQUIRE_PTR(v); REQUIRE_PTR(idx); REQUIRE_PTR(val); REQUIRE_PTR(w_conv); REQUIRE_PTR(o);
+    if (d->conv_type == CONVNN_DEPTHWISE_SEPARABLE) REQUIRE_PTR(w_pw);
+    if ((rc = check_device())) return rc;
+    return launch_gather_conv_simt(d, dm, v, idx, val, w_conv, w_pw, o, static_cast<cudaStream_t>(stream));
+}
+
+int convnn_b200_out_proj(const convnn_desc* d, const void* o, const void* w_o, void* out, int64_t ldo,
+                         void* stream) {
+    Dims dm;
+    int rc = validate(d, &dm);
+    if (rc) return rc;
+    REQUIRE_PTR(o); REQUIRE_PTR(w_o); REQUIRE_PTR(out);
+    if (ldo < dm.D) return set_error(CONVNN_E_INVALID, "ldo=%lld is smaller than D=%d", (long long)ldo, dm.D);
+    if ((rc = check_device())) return rc;
+    GemmParams p{};
+    p.a = o; p.w = w_o; p.bias = nullptr; p.c = out; p.cand = nullptr;
+    p.lda = dm.D; p.ldc = ldo; p.M = dm.B * dm.T; p.N = dm.D; p.Kd = dm.D;
+    p.a_mode = dm.H == 1 ? A_ROWS : A_HEAD_QUIRK; p.c_mode = C_ROWS;
+    p.rows_per_batch = dm.T; p.T = dm.T; p.H = dm.H; p.dk = dm.dk; p.Cp = dm.Cp; p.gelu = 0;
+    return launch_gemm_simt(d->dtype, p, static_cast<cudaStream_t>(stream));
+}
+
+int convnn_b200_forward(const convnn_desc* d, const void* x, int64_t ldx, const void* w_qkv,
+                        const void* w_conv, const void* w_pw, const void* w_o, const int32_t* cand,
+                        void* out, int64_t ldo, void* workspace, size_t workspace_bytes, void* stream) {
+    Dims dm;
+    int rc = validate(d, &dm);
+    if (rc) return rc;
+    REQUIRE_PTR(workspace);
+    if (!aligned16(workspace)) return set_error(CONVNN_E_ALIGN, "workspace must be 16-byte aligned");
+    Workspace w = carve(dm, workspace);
+    if (workspace_bytes < w.total)
+        return set_error(CONVNN_E_WORKSPACE, "workspace has %zu bytes, %zu needed", workspace_bytes, w.total);
+    if ((rc = convnn_b200_qkv_proj(d, x, ldx, w_qkv, cand, w.q, w.k, w.v, w.qstat, w.kstat, stream))) return rc;
+    if ((rc = convnn_b200_sim_topk(d, w.q, w.k, w.qstat, w.kstat, cand, w.idx, w.val, stream))) return rc;
+    if ((rc = convnn_b200_gather_conv(d, w.v, w.idx, w.val, w_conv, w_pw, w.o, stream))) return rc;
+    return convnn_b200_out_proj(d, w.o, w_o, out, ldo, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,92 @@
+// Shared host/device helpers of the convnn_b200 library.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/convnn_b200.h"
+
+namespace convnn {
+
+// ---- error reporting -------------------------------------------------------------
+int set_error(int status, const char* fmt, ...);
+void clear_error();
+
+void count_launch();
+
+#define CONVNN_CHECK_LAUNCH(what)                                                    \
+    do {                                                                             \
+        ::convnn::count_launch();                                                    \
+        cudaError_t e__ = cudaGetLastError();                                        \
+        if (e__ != cudaSuccess)                                                      \
+            return ::convnn::set_error(CONVNN_E_CUDA, "%s: %s", what, cudaGetErrorString(e__)); \
+    } while (0)
+
+// ---- descriptor-derived quantities -------------------------------------------------
+struct Dims {
+    int B, T, S, D, H, K, dk, C, Cp;   // C = input channels per head, Cp = stored channels
+    int nsel;                          // neighbours picked from the candidates: K or K-1
+    size_t elt;                        // bytes per element of dtype
+};
+
+// Validates the descriptor the way the reference would fail (or this build refuses)
+// and fills Dims.  Returns CONVNN_OK or a negative status with last_error set.
+int validate(const convnn_desc* d, Dims* out);
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+constexpr int kMaxK = 32;              // register-resident sorted list per row
+
+// ---- dtype helpers -----------------------------------------------------------------
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// ---- kernel launchers (one translation unit each) ------------------------------------
+// A operand addressing of the SIMT GEMM.
+enum AMode : int {
+    A_ROWS = 0,       // A[m, kk] = a[m * lda + kk]
+    A_TOKENS = 1,     // m = (b, r): token = cand ? cand[r] : r; a[(b*T + token) * lda + kk]
+    A_HEAD_QUIRK = 2  // m = (b, t'), kk = h*dk + c': a[((b*H + h) * T) * dk + c' * T + t']
+};
+// C placement of the SIMT GEMM.
+enum CMode : int {
+    C_ROWS = 0,       // c[m * ldc + n]
+    C_HEADS = 1       // n = h*dk + c: c[m * H*Cp + h*Cp + c]
+};
+
+struct GemmParams {
+    const void* a;
+    const void* w;        // (N, Kd) row-major: C = A * W^T
+    const void* bias;     // (N) in dtype or nullptr
+    void* c;
+    const int32_t* cand;  // A_TOKENS only
+    long long lda, ldc;
+    int M, N, Kd;
+    int a_mode, c_mode;
+    int rows_per_batch;   // A_TOKENS: rows per batch item (T or S); A_HEAD_QUIRK: T
+    int T, H, dk, Cp;     // geometry for A_TOKENS / A_HEAD_QUIRK / C_HEADS
+    int gelu;             // apply exact GELU after bias
+};
+
+int launch_gemm_simt(int dtype, const GemmParams& p, cudaStream_t st);
+
+int launch_head_fill_and_stats(const convnn_desc* d, const Dims& dm, void* t, int rows, float* stat,
+                               cudaStream_t st);
+int launch_sim_topk_simt_f32(const convnn_desc* d, const Dims& dm, const void* q, const void* k,
+                             const float* qstat, const float* kstat, const int32_t* cand,
+                             int32_t* idx, float* val, cudaStream_t st);
+int launch_sim_topk_simt_bf16(const convnn_desc* d, const Dims& dm, const void* q, const void* k,
+                              const float* qstat, const float* kstat, const int32_t* cand,
+                              int32_t* idx, float* val, cudaStream_t st);
+int launch_gather_conv_simt(const convnn_desc* d, const Dims& dm, const void* v, const int32_t* idx,
+                            const float* val, const void* w_conv, const void* w_pw, void* o,
+                            cudaStream_t st);
+
+}  // namespace convnn

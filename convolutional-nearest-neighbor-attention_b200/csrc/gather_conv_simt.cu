@@ -1,0 +1,253 @@
+// Neighbour weighting + gather + K-tap stride-K Conv1d (reference layers.py:389-406, 313).
+//
+// A CTA owns a tile of consecutive tokens of one (batch, head).  Weights over the K
+// selected values (softmax, raw value, or reciprocal distance) are computed once per
+// token into shared memory; the K neighbour rows of V are then read straight from
+// global memory (they are L2-resident: every row is re-read K times on average but
+// fetched from HBM once) with 16-byte loads along the channel dimension.
+//   depthwise            o[t, c] = sum_j w[j, c] * p[t, j] * v[idx[t, j], c]
+//   standard             o[t, o] = sum_{j, c} w[j, c, o] * p[t, j] * v[idx[t, j], c]
+//   depthwise-separable  depthwise (kept in fp32 in shared memory) then a C x d_k matrix
+// The K-times expanded tensor the reference builds three times never exists.
+#include "common.cuh"
+
+namespace convnn {
+namespace {
+
+constexpr int THREADS = 256;
+
+// p[j] for one token (layers.py:352-355, 394-397): softmax(+-val), val, or 1/(val+1e-8).
+__device__ __forceinline__ void token_weights(const float* __restrict__ val, float* __restrict__ p, int K,
+                                              bool maximum, bool softmax) {
+    if (softmax) {
+        float m = -3.402823466e38f;
+        for (int j = 0; j < K; ++j) {
+            float x = maximum ? val[j] : -val[j];
+            m = fmaxf(m, x);
+        }
+        float s = 0.f;
+        for (int j = 0; j < K; ++j) {
+            float e = expf((maximum ? val[j] : -val[j]) - m);
+            p[j] = e;
+            s += e;
+        }
+        for (int j = 0; j < K; ++j) p[j] = p[j] / s;
+    } else {
+        for (int j = 0; j < K; ++j) p[j] = maximum ? val[j] : 1.0f / (val[j] + 1e-8f);
+    }
+}
+
+template <typename T, int VEC> struct VecLoad;
+template <> struct VecLoad<float, 4> {
+    static __device__ __forceinline__ void load(const float* p, float* out) {
+        float4 v = *reinterpret_cast<const float4*>(p);
+        out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float* in) {
+        *reinterpret_cast<float4*>(p) = make_float4(in[0], in[1], in[2], in[3]);
+    }
+};
+template <> struct VecLoad<__nv_bfloat16, 8> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* out) {
+        uint4 v = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float2 f = __bfloat1622float2(h[e]);
+            out[2 * e] = f.x; out[2 * e + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* in) {
+        uint4 v;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(in[2 * e], in[2 * e + 1]);
+        *reinterpret_cast<uint4*>(p) = v;
+    }
+};
+template <typename T> struct VecLoad<T, 1> {
+    static __device__ __forceinline__ void load(const T* p, float* out) { out[0] = to_f32<T>(*p); }
+    static __device__ __forceinline__ void store(T* p, const float* in) { *p = from_f32<T>(in[0]); }
+};
+
+// ---- depthwise ---------------------------------------------------------------------
+template <typename T, int VEC, int TT>
+__global__ void __launch_bounds__(THREADS) gather_conv_dw_kernel(
+    const T* __restrict__ v, const int32_t* __restrict__ idx, const float* __restrict__ val,
+    const T* __restrict__ wconv, T* __restrict__ o, int T_, int H, int dk, int Cp, int K, int maximum,
+    int softmax) {
+    __shared__ float ps[TT][kMaxK];
+    __shared__ int ns[TT][kMaxK];
+    const int bh = blockIdx.y;
+    const int b = bh / H, h = bh - b * H;
+    const int t0 = blockIdx.x * TT;
+    const int nt = min(TT, T_ - t0);
+    const long long nbase = ((long long)bh * T_ + t0) * K;
+    for (int e = threadIdx.x; e < nt * K; e += THREADS) ns[e / K][e % K] = idx[nbase + e];
+    if (threadIdx.x < nt) token_weights(val + nbase + (long long)threadIdx.x * K, ps[threadIdx.x], K, maximum, softmax);
+    __syncthreads();
+
+    const int groups = dk / VEC;
+    const T* vb = v + ((long long)b * T_ * H + h) * Cp;
+    const long long tstride = (long long)H * Cp;
+    for (int item = threadIdx.x; item < nt * groups; item += THREADS) {
+        const int tt = item / groups, c = (item - tt * groups) * VEC;
+        float acc[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
+        for (int j = 0; j < K; ++j) {
+            float x[VEC], w[VEC];
+            VecLoad<T, VEC>::load(vb + ns[tt][j] * tstride + c, x);
+            VecLoad<T, VEC>::load(wconv + j * dk + c, w);
+            const float pj = ps[tt][j];
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) acc[e] = fmaf(w[e], pj * x[e], acc[e]);
+        }
+        VecLoad<T, VEC>::store(o + ((long long)bh * T_ + t0 + tt) * dk + c, acc);
+    }
+}
+
+// ---- standard / depthwise-separable --------------------------------------------------
+// Dynamic shared memory: P[TT][JC * C] floats (weighted neighbour block for JC taps, or
+// the depthwise result with JC = 1 for the separable type).
+template <typename T, int ITEMS>
+__global__ void __launch_bounds__(THREADS) gather_conv_mat_kernel(
+    const T* __restrict__ v, const int32_t* __restrict__ idx, const float* __restrict__ val,
+    const T* __restrict__ wconv, const T* __restrict__ wpw, T* __restrict__ o, int T_, int H, int dk,
+    int C, int Cp, int K, int maximum, int softmax, int separable, int TT, int JC) {
+    extern __shared__ __align__(16) float P[];
+    __shared__ float ps[32][kMaxK];
+    __shared__ int ns[32][kMaxK];
+    const int bh = blockIdx.y;
+    const int b = bh / H, h = bh - b * H;
+    const int t0 = blockIdx.x * TT;
+    const int nt = min(TT, T_ - t0);
+    const long long nbase = ((long long)bh * T_ + t0) * K;
+    for (int e = threadIdx.x; e < nt * K; e += THREADS) ns[e / K][e % K] = idx[nbase + e];
+    if (threadIdx.x < nt) token_weights(val + nbase + (long long)threadIdx.x * K, ps[threadIdx.x], K, maximum, softmax);
+    __syncthreads();
+
+    const T* vb = v + ((long long)b * T_ * H + h) * Cp;
+    const long long tstride = (long long)H * Cp;
+    const int tgroups = (TT + 3) / 4;
+    const int n_items = dk * tgroups;
+    float acc[ITEMS][4];
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[it][e] = 0.f;
+
+    const int ntaps = separable ? 1 : K;
+    const int pstride = JC * C;
+    for (int j0 = 0; j0 < ntaps; j0 += JC) {
+        const int jn = min(JC, ntaps - j0);
+        // fill P (zero rows for tokens past the end so the matrix step needs no guard)
+        for (int e = threadIdx.x; e < TT * jn * C; e += THREADS) {
+            const int tt = e / (jn * C);
+            const int r = e - tt * jn * C;
+            const int jj = r / C, c = r - jj * C;
+            float x = 0.f;
+            if (tt < nt) {
+                if (separable) {
+                    for (int j = 0; j < K; ++j)
+                        x = fmaf(to_f32<T>(wconv[j * C + c]),
+                                 ps[tt][j] * to_f32<T>(vb[ns[tt][j] * tstride + c]), x);
+                } else {
+                    const int j = j0 + jj;
+                    x = ps[tt][j] * to_f32<T>(vb[ns[tt][j] * tstride + c]);
+                }
+            }
+            P[tt * pstride + r] = x;
+        }
+        __syncthreads();
+        const T* wm = separable ? wpw : wconv + (long long)j0 * C * dk;   // (rows = jn*C, dk)
+#pragma unroll
+        for (int it = 0; it < ITEMS; ++it) {
+            const int item = threadIdx.x + it * THREADS;
+            if (item < n_items) {
+                const int oc = item % dk, tg = item / dk;
+                const float* p0 = P + (tg * 4) * pstride;
+                for (int r = 0; r < jn * C; ++r) {
+                    const float w = to_f32<T>(wm[(long long)r * dk + oc]);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        if (tg * 4 + e < TT) acc[it][e] = fmaf(w, p0[e * pstride + r], acc[it][e]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it) {
+        const int item = threadIdx.x + it * THREADS;
+        if (item < n_items) {
+            const int oc = item % dk, tg = item / dk;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int tt = tg * 4 + e;
+                if (tt < nt) o[((long long)bh * T_ + t0 + tt) * dk + oc] = from_f32<T>(acc[it][e]);
+            }
+        }
+    }
+}
+
+template <typename T, int VEC>
+int launch_dw(const convnn_desc* d, const Dims& dm, const void* v, const int32_t* idx, const float* val,
+              const void* w_conv, void* o, cudaStream_t st) {
+    constexpr int TT = 16;
+    dim3 grid((dm.T + TT - 1) / TT, dm.B * dm.H);
+    gather_conv_dw_kernel<T, VEC, TT><<<grid, THREADS, 0, st>>>(
+        static_cast<const T*>(v), idx, val, static_cast<const T*>(w_conv), static_cast<T*>(o), dm.T, dm.H,
+        dm.dk, dm.Cp, dm.K, d->metric != CONVNN_EUCLIDEAN, d->softmax);
+    CONVNN_CHECK_LAUNCH("gather_conv_dw");
+    return CONVNN_OK;
+}
+
+template <typename T>
+int launch_mat(const convnn_desc* d, const Dims& dm, const void* v, const int32_t* idx, const float* val,
+               const void* w_conv, const void* w_pw, void* o, cudaStream_t st) {
+    constexpr int ITEMS = 4;
+    const int separable = d->conv_type == CONVNN_DEPTHWISE_SEPARABLE;
+    // token tile: dk * ceil(TT/4) work items must fit ITEMS passes of the CTA
+    int TT = (THREADS * ITEMS / dm.dk) * 4;
+    if (TT > 32) TT = 32;
+    if (TT < 4) return set_error(CONVNN_E_UNSUPPORTED, "d_k=%d too large for the matrix conv kernel", dm.dk);
+    const int ntaps = separable ? 1 : dm.K;
+    const size_t budget = 64 * 1024;
+    int JC = (int)(budget / ((size_t)TT * dm.C * sizeof(float)));
+    if (JC < 1) JC = 1;
+    if (JC > ntaps) JC = ntaps;
+    size_t smem = (size_t)TT * JC * dm.C * sizeof(float);
+    if (smem > 200 * 1024) return set_error(CONVNN_E_UNSUPPORTED, "conv tile needs %zu bytes of shared memory", smem);
+    auto kern = gather_conv_mat_kernel<T, ITEMS>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return set_error(CONVNN_E_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    }
+    dim3 grid((dm.T + TT - 1) / TT, dm.B * dm.H);
+    kern<<<grid, THREADS, smem, st>>>(static_cast<const T*>(v), idx, val, static_cast<const T*>(w_conv),
+                                      static_cast<const T*>(w_pw), static_cast<T*>(o), dm.T, dm.H, dm.dk, dm.C,
+                                      dm.Cp, dm.K, d->metric != CONVNN_EUCLIDEAN, d->softmax, separable, TT, JC);
+    CONVNN_CHECK_LAUNCH("gather_conv_mat");
+    return CONVNN_OK;
+}
+
+}  // namespace
+
+int launch_gather_conv_simt(const convnn_desc* d, const Dims& dm, const void* v, const int32_t* idx,
+                            const float* val, const void* w_conv, const void* w_pw, void* o,
+                            cudaStream_t st) {
+    const bool f32 = d->dtype == CONVNN_F32;
+    if (d->conv_type == CONVNN_DEPTHWISE) {
+        const int vec = f32 ? 4 : 8;
+        const bool vec_ok = dm.dk % vec == 0 && dm.Cp % vec == 0 && aligned16(v) && aligned16(o) && aligned16(w_conv);
+        if (f32) return vec_ok ? launch_dw<float, 4>(d, dm, v, idx, val, w_conv, o, st)
+                               : launch_dw<float, 1>(d, dm, v, idx, val, w_conv, o, st);
+        return vec_ok ? launch_dw<__nv_bfloat16, 8>(d, dm, v, idx, val, w_conv, o, st)
+                      : launch_dw<__nv_bfloat16, 1>(d, dm, v, idx, val, w_conv, o, st);
+    }
+    return f32 ? launch_mat<float>(d, dm, v, idx, val, w_conv, w_pw, o, st)
+               : launch_mat<__nv_bfloat16>(d, dm, v, idx, val, w_conv, w_pw, o, st);
+}
+
+}  // namespace convnn

@@ -1,0 +1,279 @@
+"""Drop-in ``nn.Module``s for the reference's ConvNN-Attention layers.
+
+Same constructor arguments, ``state_dict`` keys and ``forward(x)`` signature as
+``MultiHeadConvNNAttention`` (reference layers.py:132-321), ``MultiHeadBranchingAttention``
+(layers.py:580-652) and ``MultiHeadBranchingConv`` (layers.py:502-578), so a reference
+checkpoint loads with ``strict=True`` and the reference's ``vit.py`` can construct them
+in place of its own.  The ConvNN path runs in libconvnn_b200 (CUDA, sm_100a); it is
+forward-only (inference) and has no CPU implementation.  The non-ConvNN halves of the
+branching wrappers (softmax attention, Conv1d attention) and ``pointwise_linear`` are
+ordinary torch modules with the reference's parameter names.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import ops
+from .ops import LayerSpec
+
+
+class MultiHeadConvNNAttention(nn.Module):
+    def __init__(self, d_hidden, num_heads, attention_dropout, K, sampling_type, num_samples, sample_padding,
+                 magnitude_type, seq_length=197, coordinate_encoding=False, convolution_type='depthwise',
+                 softmax_topk_val=True):
+        super().__init__()
+        assert d_hidden % num_heads == 0, "d_hidden must be divisible by num_heads"
+        self.d_hidden = d_hidden
+        self.num_heads = num_heads
+        self.attention_dropout = attention_dropout
+        self.d_k = d_hidden // num_heads
+        self.K = K
+        self.seq_length = seq_length
+        self.sampling_type = sampling_type
+        self.num_samples = int(num_samples)
+        self.sample_padding = int(sample_padding) if sampling_type == 'spatial' else 0
+        self.magnitude_type = magnitude_type
+        self.maximum = magnitude_type in ('cosine', 'matmul')
+        self.coordinate_encoding = coordinate_encoding
+        self.convolution_type = convolution_type
+        self.softmax_topk_val = softmax_topk_val
+        self.INF = 1.1
+        self.NEG_INF = -0.1
+
+        self.W_q = nn.Linear(d_hidden, d_hidden, bias=False)
+        self.W_k = nn.Linear(d_hidden, d_hidden, bias=False)
+        self.W_v = nn.Linear(d_hidden, d_hidden, bias=False)
+        self.W_o = nn.Linear(d_hidden, d_hidden, bias=False)
+        self.dropout = nn.Dropout(attention_dropout)
+
+        self.in_channels = self.d_k + 1 if coordinate_encoding else self.d_k
+        self.out_channels = self.d_k
+        C, dk = self.in_channels, self.d_k
+        # Parameter containers only (never called): they give the reference's state_dict
+        # keys and its construction-time errors, e.g. depthwise + coordinate_encoding.
+        if convolution_type == 'standard':
+            self.conv = nn.Conv1d(C, dk, kernel_size=K, stride=K, padding=0, bias=False)
+        elif convolution_type == 'depthwise':
+            self.conv = nn.Conv1d(C, dk, kernel_size=K, stride=K, padding=0, groups=C, bias=False)
+            self.conv.weight.data.fill_(1.0)
+        elif convolution_type == 'depthwise-separable':
+            self.conv = nn.Sequential(
+                nn.Conv1d(C, C, kernel_size=K, stride=K, padding=0, groups=C, bias=False),
+                nn.Conv1d(C, dk, kernel_size=1, stride=1, padding=0, bias=False))
+        # (any other string leaves the module without a conv, as in the reference)
+
+        self.candidate_override: Optional[torch.Tensor] = None   # fixes the sampled candidate set
+        self.stage_timer = None   # callable(label): records a CUDA event between the stage calls
+        self._packed = None
+        self._packed_key = None
+        self._spatial_cache = {}
+
+    # -- host-side helpers --------------------------------------------------------------
+    def _spec(self) -> LayerSpec:
+        return LayerSpec(self.d_hidden, self.num_heads, self.K, self.sampling_type, self.magnitude_type,
+                         self.convolution_type, self.softmax_topk_val, self.coordinate_encoding,
+                         self.seq_length)
+
+    def _conv_params(self):
+        if self.convolution_type == 'depthwise-separable':
+            return (self.conv[0].weight, self.conv[1].weight)
+        return (self.conv.weight,)
+
+    def packed_weights(self, dtype, device):
+        params = (self.W_q.weight, self.W_k.weight, self.W_v.weight, self.W_o.weight) + self._conv_params()
+        key = (dtype, device) + tuple((p.data_ptr(), p._version) for p in params)
+        if self._packed_key != key:
+            self._packed = ops.pack_weights(self._spec(), self.W_q.weight, self.W_k.weight, self.W_v.weight,
+                                            self.W_o.weight, self._conv_params(), dtype, device)
+            self._packed_key = key
+        return self._packed
+
+    def candidates(self, T: int, device) -> Optional[torch.Tensor]:
+        """Candidate token indices for this call, drawn as the reference draws them
+        (layers.py:284, 297) unless ``candidate_override`` is set."""
+        if self.sampling_type == 'all':
+            return None
+        if self.candidate_override is not None:
+            return self.candidate_override.to(device)
+        if self.sampling_type == 'random':
+            return torch.randperm(T, device=device)[:self.num_samples]
+        if self.sampling_type == 'spatial':
+            key = (T, str(device))
+            if key not in self._spatial_cache:
+                self._spatial_cache[key] = torch.linspace(
+                    0 + self.sample_padding, T - self.sample_padding - 1, self.num_samples, device=device).long()
+            return self._spatial_cache[key]
+        raise ValueError("Invalid sampling_type. Must be one of ['all', 'random', 'spatial']")
+
+    def _check_mode(self, x):
+        if not x.is_cuda:
+            raise RuntimeError("convnn_b200.MultiHeadConvNNAttention runs on CUDA (sm_100a) only; "
+                               "there is no CPU path")
+        if torch.is_grad_enabled() and (x.requires_grad or any(p.requires_grad for p in self.parameters())):
+            raise RuntimeError("convnn_b200 is forward-only: call it under torch.no_grad() "
+                               "(training / backward is outside this library)")
+        if self.training and self.attention_dropout > 0:
+            raise RuntimeError("convnn_b200 is forward-only: dropout > 0 needs module.eval()")
+        if self.magnitude_type not in ('cosine', 'matmul', 'euclidean'):
+            raise ValueError(f"unknown magnitude_type {self.magnitude_type!r}")
+
+    def forward(self, x, out: Optional[torch.Tensor] = None):
+        self._check_mode(x)
+        B, T, D = x.shape
+        cand = self.candidates(T, x.device)
+        packed = self.packed_weights(x.dtype, x.device)
+        if self.stage_timer is not None:
+            return self._forward_staged(x, packed, cand, out)
+        return ops.forward(self._spec(), x, packed, cand, out=out)
+
+    def _forward_staged(self, x, packed, cand, out):
+        """The same kernels in the same order as ``convnn_b200_forward``, issued through the
+        four stage entry points so a profiler hook can bracket each with CUDA events."""
+        spec, mark = self._spec(), self.stage_timer
+        w_qkv, w_conv, w_pw, w_o = packed
+        mark("begin")
+        q, k, v, qs, ks = ops.qkv_proj(spec, x, w_qkv, cand)
+        mark("qkv_proj")
+        idx, val = ops.sim_topk(spec, q, k, qs, ks, cand)
+        mark("sim_topk")
+        o = ops.gather_conv(spec, v, idx, val, w_conv, w_pw, S=q.shape[1])
+        mark("gather_conv")
+        y = ops.out_proj(spec, o, w_o, out=out, S=q.shape[1])
+        mark("out_proj")
+        return y
+
+
+class MultiHeadAttention(nn.Module):
+    """Softmax attention half of MultiHeadBranchingAttention (reference layers.py:90-130):
+    bias-free W_q/W_k/W_v/W_o, softmax(QK^T / sqrt(d_k)) V.  Host-side torch module."""
+
+    def __init__(self, d_hidden, num_heads, attention_dropout):
+        super().__init__()
+        assert d_hidden % num_heads == 0, "d_hidden must be divisible by num_heads"
+        self.d_hidden, self.num_heads, self.d_k = d_hidden, num_heads, d_hidden // num_heads
+        self.dropout = nn.Dropout(attention_dropout)
+        self.W_q = nn.Linear(d_hidden, d_hidden, bias=False)
+        self.W_k = nn.Linear(d_hidden, d_hidden, bias=False)
+        self.W_v = nn.Linear(d_hidden, d_hidden, bias=False)
+        self.W_o = nn.Linear(d_hidden, d_hidden, bias=False)
+
+    def forward(self, x, mask=None):
+        B, T, _ = x.shape
+        H, dk = self.num_heads, self.d_k
+        q = self.W_q(x).view(B, T, H, dk).transpose(1, 2)
+        k = self.W_k(x).view(B, T, H, dk).transpose(1, 2)
+        v = self.W_v(x).view(B, T, H, dk).transpose(1, 2)
+        s = torch.matmul(q, k.transpose(-2, -1)) / math.sqrt(dk)
+        if mask is not None:
+            s = s.masked_fill(mask == 0, -1e9)
+        a = self.dropout(torch.softmax(s, dim=-1))
+        o = torch.matmul(a, v).transpose(1, 2).reshape(B, T, self.d_hidden)
+        return self.W_o(o)
+
+
+class MultiHeadConv1dAttention(nn.Module):
+    """Conv1d half of MultiHeadBranchingConv (reference layers.py:452-500), including its
+    flat head reinterpretation.  Host-side torch module."""
+
+    def __init__(self, d_hidden, num_heads, kernel_size):
+        super().__init__()
+        assert d_hidden % num_heads == 0, "d_hidden must be divisible by num_heads"
+        self.d_hidden, self.num_heads, self.d_k = d_hidden, num_heads, d_hidden // num_heads
+        self.kernel_size, self.stride = kernel_size, 1
+        self.W_x = nn.Linear(d_hidden, d_hidden)
+        self.W_o = nn.Linear(d_hidden, d_hidden)
+        self.in_channels = self.out_channels = self.d_k
+        self.conv = nn.Conv1d(self.d_k, self.d_k, kernel_size=kernel_size, stride=1, padding="same")
+
+    def forward(self, x):
+        B, T, D = x.shape
+        H, dk = self.num_heads, self.d_k
+        y = self.W_x(x).view(B, T, H, dk).permute(0, 2, 3, 1).reshape(B * H, dk, T)
+        z = self.conv(y)                                       # (B*H, dk, T)
+        o = z.permute(0, 2, 1).reshape(B, H, T * dk)           # token-major per head, flat
+        y = o.view(B, H, dk, T).permute(0, 3, 1, 2).reshape(B, T, D)
+        return self.W_o(y)
+
+
+class _Branching(nn.Module):
+    def _init_common(self, d_hidden, num_heads, attention_dropout, K, sampling_type, num_samples,
+                     sample_padding, magnitude_type, seq_length, coordinate_encoding, convolution_type,
+                     softmax_topk_val, branch_ratio):
+        self.d_hidden = d_hidden
+        self.num_heads = num_heads
+        self.attention_dropout = attention_dropout
+        self.K = K
+        self.sampling_type = sampling_type
+        self.num_samples = int(num_samples)
+        self.sample_padding = int(sample_padding) if sampling_type == 'spatial' else 0
+        self.magnitude_type = magnitude_type
+        self.seq_length = seq_length
+        self.coordinate_encoding = coordinate_encoding
+        self.branch_ratio = branch_ratio
+        self.d_hidden_convnn = int(branch_ratio * d_hidden)
+        if branch_ratio != 0:
+            self.convnn = MultiHeadConvNNAttention(
+                d_hidden=self.d_hidden_convnn, num_heads=num_heads, attention_dropout=attention_dropout, K=K,
+                sampling_type=sampling_type, num_samples=num_samples, sample_padding=sample_padding,
+                magnitude_type=magnitude_type, seq_length=seq_length, coordinate_encoding=coordinate_encoding,
+                convolution_type=convolution_type, softmax_topk_val=softmax_topk_val)
+
+    def _two_branches(self, x, other):
+        """ConvNN on x[..., :d_convnn] written straight into the concat buffer (no slice
+        copy in, no cat copy out), the other branch on the rest, then pointwise_linear
+        (reference layers.py:574-577, 648-651)."""
+        dc = self.d_hidden_convnn
+        cat = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+        self.convnn(x[:, :, :dc], out=cat[:, :, :dc])
+        cat[:, :, dc:] = other(x[:, :, dc:])
+        return self.pointwise_linear(cat)
+
+
+class MultiHeadBranchingAttention(_Branching):
+    def __init__(self, d_hidden, num_heads, attention_dropout, K, sampling_type, num_samples, sample_padding,
+                 magnitude_type, seq_length=197, coordinate_encoding=False, convolution_type='depthwise',
+                 softmax_topk_val=True, branch_ratio=0.5):
+        super().__init__()
+        self._init_common(d_hidden, num_heads, attention_dropout, K, sampling_type, num_samples, sample_padding,
+                          magnitude_type, seq_length, coordinate_encoding, convolution_type, softmax_topk_val,
+                          branch_ratio)
+        self.d_hidden_attention = d_hidden - self.d_hidden_convnn
+        if branch_ratio != 1:
+            self.attention = MultiHeadAttention(self.d_hidden_attention, num_heads, attention_dropout)
+        self.pointwise_linear = nn.Linear(d_hidden, d_hidden)
+
+    def forward(self, x):
+        # The reference swaps the degenerate cases (ratio 0 calls the ConvNN branch that was
+        # not built and vice versa, layers.py:643-646) and fails with AttributeError; so do we.
+        if self.branch_ratio == 0:
+            return self.convnn(x)
+        if self.branch_ratio == 1:
+            return self.attention(x)
+        return self._two_branches(x, self.attention)
+
+
+class MultiHeadBranchingConv(_Branching):
+    def __init__(self, d_hidden, num_heads, attention_dropout, kernel_size, K, sampling_type, num_samples,
+                 sample_padding, magnitude_type, seq_length=197, coordinate_encoding=False,
+                 convolution_type='depthwise', softmax_topk_val=True, branch_ratio=0.5):
+        super().__init__()
+        self.kernel_size = kernel_size
+        self._init_common(d_hidden, num_heads, attention_dropout, K, sampling_type, num_samples, sample_padding,
+                          magnitude_type, seq_length, coordinate_encoding, convolution_type, softmax_topk_val,
+                          branch_ratio)
+        self.d_hidden_conv1d = d_hidden - self.d_hidden_convnn
+        if branch_ratio != 1:
+            self.conv1d = MultiHeadConv1dAttention(self.d_hidden_conv1d, num_heads, kernel_size)
+        self.pointwise_linear = nn.Linear(d_hidden, d_hidden)
+
+    def forward(self, x):
+        if self.branch_ratio == 0:
+            return self.conv1d(x)
+        if self.branch_ratio == 1:
+            return self.convnn(x)
+        return self._two_branches(x, self.conv1d)

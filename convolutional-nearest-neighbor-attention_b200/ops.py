@@ -1,0 +1,198 @@
+"""Stage-level and whole-layer calls into libconvnn_b200 on torch CUDA tensors.
+
+torch is plumbing here: it owns device memory and the current stream.  All arithmetic
+happens in the library's kernels; nothing in this file computes on the host or falls
+back to torch ops.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+
+from . import _capi
+
+
+@dataclass(frozen=True)
+class LayerSpec:
+    """Static configuration of one ConvNN-Attention layer (reference layers.py:133-146)."""
+    d_hidden: int
+    num_heads: int
+    K: int
+    sampling_type: str = "all"
+    magnitude_type: str = "cosine"
+    convolution_type: str = "depthwise"
+    softmax_topk_val: bool = True
+    coordinate_encoding: bool = False
+    seq_length: int = 197
+
+    @property
+    def d_k(self) -> int:
+        return self.d_hidden // self.num_heads
+
+    @property
+    def in_channels(self) -> int:
+        return self.d_k + (1 if self.coordinate_encoding else 0)
+
+
+def _dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return _capi.F32
+    if dt == torch.bfloat16:
+        return _capi.BF16
+    raise TypeError(f"convnn_b200 computes in float32 or bfloat16, got {dt}")
+
+
+def _require_cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("convnn_b200 runs on CUDA tensors only: there is no CPU path")
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def descriptor(spec: LayerSpec, B: int, T: int, S: int, dtype: torch.dtype) -> _capi.ConvnnDesc:
+    return _capi.make_desc(B, T, S, spec.d_hidden, spec.num_heads, spec.K, _dtype_code(dtype),
+                           spec.magnitude_type, spec.sampling_type != "all", spec.convolution_type,
+                           spec.softmax_topk_val, spec.coordinate_encoding, spec.seq_length)
+
+
+def _rows_view(x: torch.Tensor) -> Tuple[torch.Tensor, int]:
+    """(B, T, D) tensor whose rows are contiguous and evenly strided -> (tensor, ld).
+    A channel slice x[:, :, :d] of a wider contiguous tensor qualifies as it is."""
+    B, T, D = x.shape
+    if x.stride(2) == 1 and x.stride(0) == T * x.stride(1) and x.stride(1) >= D:
+        return x, x.stride(1)
+    x = x.contiguous()
+    return x, D
+
+
+def pack_weights(spec: LayerSpec, w_q, w_k, w_v, w_o, conv_weights, dtype, device):
+    """Re-layout the module parameters into what the kernels read (see the header):
+    w_qkv (3, D, D) = [W_k; W_v; W_q]; conv taps tap-major; all in ``dtype``."""
+    def cvt(t):
+        return t.detach().to(device=device, dtype=dtype).contiguous()
+    w_qkv = torch.stack([cvt(w_k), cvt(w_v), cvt(w_q)], dim=0).contiguous()
+    w_pw = None
+    if spec.convolution_type == "depthwise":
+        (wc,) = conv_weights                       # (C, 1, K) -> (K, C)
+        w_conv = cvt(wc[:, 0, :].t())
+    elif spec.convolution_type == "standard":
+        (wc,) = conv_weights                       # (d_k, C, K) -> (K, C, d_k)
+        w_conv = cvt(wc.permute(2, 1, 0))
+    elif spec.convolution_type == "depthwise-separable":
+        w0, w1 = conv_weights                      # (C, 1, K) -> (K, C); (d_k, C, 1) -> (C, d_k)
+        w_conv = cvt(w0[:, 0, :].t())
+        w_pw = cvt(w1[:, :, 0].t())
+    else:
+        raise ValueError(f"unknown convolution_type {spec.convolution_type!r}")
+    return w_qkv, w_conv, w_pw, cvt(w_o)
+
+
+def _cand_arg(spec: LayerSpec, cand: Optional[torch.Tensor], T: int, device) -> Tuple[Optional[torch.Tensor], int]:
+    if spec.sampling_type == "all":
+        return None, T
+    if cand is None:
+        raise ValueError("sampled modes need candidate indices")
+    cand = cand.to(device=device, dtype=torch.int32).contiguous()
+    return cand, int(cand.numel())
+
+
+def qkv_proj(spec: LayerSpec, x: torch.Tensor, w_qkv: torch.Tensor, cand: Optional[torch.Tensor] = None):
+    """-> q (B,S,H,Cp), k, v (B,T,H,Cp), qstat (B,H,S), kstat (B,H,T)."""
+    _require_cuda(x, w_qkv)
+    L = _capi.lib()
+    x, ldx = _rows_view(x)
+    B, T, _ = x.shape
+    cand, S = _cand_arg(spec, cand, T, x.device)
+    d = descriptor(spec, B, T, S, x.dtype)
+    Cp = L.convnn_b200_head_channels(d)
+    _capi.check(min(Cp, 0))
+    H = spec.num_heads
+    q = torch.empty(B, S, H, Cp, dtype=x.dtype, device=x.device)
+    k = torch.empty(B, T, H, Cp, dtype=x.dtype, device=x.device)
+    v = torch.empty(B, T, H, Cp, dtype=x.dtype, device=x.device)
+    qstat = torch.empty(B, H, S, dtype=torch.float32, device=x.device)
+    kstat = torch.empty(B, H, T, dtype=torch.float32, device=x.device)
+    _capi.check(L.convnn_b200_qkv_proj(d, x.data_ptr(), ldx, w_qkv.data_ptr(), _capi.ptr(cand), q.data_ptr(),
+                                       k.data_ptr(), v.data_ptr(), qstat.data_ptr(), kstat.data_ptr(), _stream(x)))
+    return q, k, v, qstat, kstat
+
+
+def sim_topk(spec: LayerSpec, q, k, qstat, kstat, cand: Optional[torch.Tensor] = None):
+    """-> idx int32 (B,H,T,K), val float32 (B,H,T,K), best first."""
+    _require_cuda(q, k)
+    L = _capi.lib()
+    B, T, H, _ = k.shape
+    cand, S = _cand_arg(spec, cand, T, k.device)
+    d = descriptor(spec, B, T, q.shape[1], k.dtype)
+    idx = torch.empty(B, H, T, spec.K, dtype=torch.int32, device=k.device)
+    val = torch.empty(B, H, T, spec.K, dtype=torch.float32, device=k.device)
+    _capi.check(L.convnn_b200_sim_topk(d, q.data_ptr(), k.data_ptr(), _capi.ptr(qstat), _capi.ptr(kstat),
+                                       _capi.ptr(cand), idx.data_ptr(), val.data_ptr(), _stream(k)))
+    return idx, val
+
+
+def gather_conv(spec: LayerSpec, v, idx, val, w_conv, w_pw=None, S: Optional[int] = None):
+    """-> o (B,H,T,d_k)."""
+    _require_cuda(v, idx, val, w_conv)
+    L = _capi.lib()
+    B, T, H, _ = v.shape
+    d = descriptor(spec, B, T, T if spec.sampling_type == "all" else (S or T), v.dtype)
+    o = torch.empty(B, H, T, spec.d_k, dtype=v.dtype, device=v.device)
+    _capi.check(L.convnn_b200_gather_conv(d, v.data_ptr(), idx.data_ptr(), val.data_ptr(), w_conv.data_ptr(),
+                                          _capi.ptr(w_pw), o.data_ptr(), _stream(v)))
+    return o
+
+
+def out_proj(spec: LayerSpec, o, w_o, out: Optional[torch.Tensor] = None, S: Optional[int] = None):
+    """-> out (B,T,D); ``out`` may be a channel slice of a wider tensor."""
+    _require_cuda(o, w_o)
+    L = _capi.lib()
+    B, H, T, dk = o.shape
+    d = descriptor(spec, B, T, T if spec.sampling_type == "all" else (S or T), o.dtype)
+    if out is None:
+        out = torch.empty(B, T, spec.d_hidden, dtype=o.dtype, device=o.device)
+    view, ldo = _rows_view(out)
+    if view is not out:
+        raise ValueError("out must have unit channel stride and evenly strided rows")
+    _capi.check(L.convnn_b200_out_proj(d, o.data_ptr(), w_o.data_ptr(), out.data_ptr(), ldo, _stream(o)))
+    return out
+
+
+def workspace_bytes(spec: LayerSpec, B: int, T: int, S: int, dtype: torch.dtype) -> int:
+    d = descriptor(spec, B, T, S, dtype)
+    n = _capi.lib().convnn_b200_workspace_bytes(d)
+    if n == 0:
+        # re-run validation through an entry point that reports the reason
+        _capi.check(min(_capi.lib().convnn_b200_head_channels(d), 0))
+    return int(n)
+
+
+def forward(spec: LayerSpec, x: torch.Tensor, packed, cand: Optional[torch.Tensor] = None,
+            out: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Whole-layer forward through ``convnn_b200_forward``."""
+    w_qkv, w_conv, w_pw, w_o = packed
+    _require_cuda(x, w_qkv)
+    L = _capi.lib()
+    x, ldx = _rows_view(x)
+    B, T, D = x.shape
+    cand, S = _cand_arg(spec, cand, T, x.device)
+    d = descriptor(spec, B, T, S, x.dtype)
+    need = L.convnn_b200_workspace_bytes(d)
+    if need == 0:
+        _capi.check(min(L.convnn_b200_head_channels(d), 0))
+    if workspace is None or workspace.numel() < need:
+        workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+    if out is None:
+        out = torch.empty(B, T, D, dtype=x.dtype, device=x.device)
+    oview, ldo = _rows_view(out)
+    if oview is not out:
+        raise ValueError("out must have unit channel stride and evenly strided rows")
+    _capi.check(L.convnn_b200_forward(d, x.data_ptr(), ldx, w_qkv.data_ptr(), w_conv.data_ptr(), _capi.ptr(w_pw),
+                                      w_o.data_ptr(), _capi.ptr(cand), out.data_ptr(), ldo,
+                                      workspace.data_ptr(), workspace.numel(), _stream(x)))
+    return out

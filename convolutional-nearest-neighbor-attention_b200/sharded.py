@@ -1,0 +1,58 @@
+"""Batch-sharded inference over the GPUs of one node (one process per GPU).
+
+Every operation of the ConvNN path is per image, so ranks take contiguous slices of the
+batch with replicated weights and no collective inside the model; the only exchange is
+one all-gather of the logits (reference has no multi-GPU code at all).
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def shard_bounds(n: int, world: int, rank: int) -> Tuple[int, int]:
+    """Contiguous, balanced split of ``n`` items: the first ``n % world`` ranks get one more."""
+    base, extra = divmod(n, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def shared_candidates(T: int, num_samples: int, device, seed: int = 0, group=None) -> torch.Tensor:
+    """One random candidate set for all ranks (rank 0 draws, everyone receives it), so a
+    sharded run selects from the same candidates as a single-GPU run of the whole batch."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    cand = torch.randperm(T, generator=g)[:num_samples].to(device)
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.broadcast(cand, src=0, group=group)
+    return cand
+
+
+def gather_logits(local: torch.Tensor, total: int, group=None) -> torch.Tensor:
+    """All-gather per-rank logits (n_r, classes) into (total, classes) in batch order."""
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        return local
+    world = dist.get_world_size(group)
+    sizes = [shard_bounds(total, world, r) for r in range(world)]
+    nmax = max(hi - lo for lo, hi in sizes)
+    pad = local
+    if local.shape[0] < nmax:
+        pad = torch.zeros(nmax, local.shape[1], dtype=local.dtype, device=local.device)
+        pad[: local.shape[0]] = local
+    out = torch.empty(world * nmax, local.shape[1], dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(out, pad.contiguous(), group=group)
+    if all(hi - lo == nmax for lo, hi in sizes):
+        return out
+    return torch.cat([out[r * nmax: r * nmax + (hi - lo)] for r, (lo, hi) in enumerate(sizes)], dim=0)
+
+
+@torch.no_grad()
+def sharded_forward(model, images: torch.Tensor, group=None, gather: bool = True) -> torch.Tensor:
+    """Run ``model`` on this rank's slice of ``images`` (the full batch, same on every rank)
+    and return the full logits (or the local slice when ``gather`` is False)."""
+    world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+    rank = dist.get_rank(group) if world > 1 else 0
+    lo, hi = shard_bounds(images.shape[0], world, rank)
+    local = model(images[lo:hi])
+    return gather_logits(local, images.shape[0], group) if gather else local

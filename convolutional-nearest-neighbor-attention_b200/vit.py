@@ -1,0 +1,121 @@
+"""ViT harness around the ConvNN-Attention layers.
+
+Mirrors the reference model's module tree and ``state_dict`` keys (reference vit.py:22-270)
+so that a reference checkpoint loads with ``strict=True`` and whole-model throughput can be
+measured without the reference checkout.  Only the attention block runs in libconvnn_b200;
+patch embedding, LayerNorm, MLP and the classifier head are plain torch modules (they are
+the callers of the hot path, not part of it).
+"""
+from __future__ import annotations
+
+import math
+from types import SimpleNamespace
+
+import torch
+import torch.nn as nn
+
+from .layers import MultiHeadBranchingAttention, MultiHeadBranchingConv, MultiHeadConvNNAttention
+
+_DEFAULTS = dict(layer="ConvNNAttention", patch_size=16, num_layers=12, num_heads=3, d_hidden=192, d_mlp=768,
+                 dropout=0.1, attention_dropout=0.1, convolution_type="depthwise", softmax_topk_val=True, K=9,
+                 sampling_type="all", num_samples=-1, sample_padding=0, magnitude_type="matmul",
+                 coordinate_encoding=False, branch_ratio=0.5, kernel_size=9, device="cuda",
+                 img_size=(3, 224, 224), num_classes=1000)
+
+
+def make_args(**overrides) -> SimpleNamespace:
+    """Namespace with the reference CLI's defaults (main.py:28-113) plus overrides."""
+    a = dict(_DEFAULTS)
+    a.update(overrides)
+    return SimpleNamespace(**a)
+
+
+class PatchEmbedding(nn.Module):
+    def __init__(self, d_hidden, img_size, patch_size, n_channels=3):
+        super().__init__()
+        self.linear_projection = nn.Conv2d(n_channels, d_hidden, kernel_size=patch_size, stride=patch_size)
+        self.norm = nn.LayerNorm(d_hidden)
+
+    def forward(self, x):
+        return self.norm(self.linear_projection(x).flatten(2).transpose(1, 2))
+
+
+class PositionalEncoding(nn.Module):
+    def __init__(self, d_hidden, max_seq_length):
+        super().__init__()
+        self.cls_tokens = nn.Parameter(torch.randn(1, 1, d_hidden))
+        pos = torch.arange(0, max_seq_length, dtype=torch.float).unsqueeze(1)
+        div = torch.exp(torch.arange(0, d_hidden, 2).float() * (-math.log(10000.0) / d_hidden))
+        pe = torch.zeros(max_seq_length, d_hidden)
+        pe[:, 0::2] = torch.sin(pos * div)
+        pe[:, 1::2] = torch.cos(pos * div)
+        self.register_buffer('pe', pe.unsqueeze(0))
+
+    def forward(self, x):
+        x = torch.cat((self.cls_tokens.expand(x.shape[0], -1, -1), x), dim=1)
+        return x + self.pe[:, :x.size(1)]
+
+
+class TransformerEncoder(nn.Module):
+    def __init__(self, args, d_hidden, d_mlp, num_heads, dropout, attention_dropout):
+        super().__init__()
+        common = dict(K=args.K, sampling_type=args.sampling_type, num_samples=args.num_samples,
+                      sample_padding=args.sample_padding, magnitude_type=args.magnitude_type,
+                      coordinate_encoding=args.coordinate_encoding, convolution_type=args.convolution_type,
+                      softmax_topk_val=args.softmax_topk_val)
+        if args.layer == "ConvNNAttention":
+            self.attention = MultiHeadConvNNAttention(d_hidden, num_heads, attention_dropout, **common)
+        elif args.layer == "BranchConv":
+            self.attention = MultiHeadBranchingConv(d_hidden, num_heads, attention_dropout,
+                                                    kernel_size=args.kernel_size, branch_ratio=args.branch_ratio,
+                                                    **common)
+        elif args.layer == "BranchAttention":
+            self.attention = MultiHeadBranchingAttention(d_hidden, num_heads, attention_dropout,
+                                                         branch_ratio=args.branch_ratio, **common)
+        else:
+            raise ValueError("Invalid layer type. convnn_b200 provides ['ConvNNAttention', 'BranchConv', "
+                             "'BranchAttention']")
+        self.norm1 = nn.LayerNorm(d_hidden)
+        self.norm2 = nn.LayerNorm(d_hidden)
+        self.dropout1 = nn.Dropout(dropout)
+        self.dropout2 = nn.Dropout(dropout)
+        self.mlp = nn.Sequential(nn.Linear(d_hidden, d_mlp), nn.GELU(), nn.Dropout(dropout),
+                                 nn.Linear(d_mlp, d_hidden))
+
+    def forward(self, x):
+        x = x + self.dropout1(self.attention(self.norm1(x)))
+        return x + self.dropout2(self.mlp(self.norm2(x)))
+
+
+class ViT(nn.Module):
+    def __init__(self, args):
+        super().__init__()
+        assert args.img_size[1] % args.patch_size == 0 and args.img_size[2] % args.patch_size == 0, \
+            "img_size dimensions must be divisible by patch_size dimensions"
+        assert args.d_hidden % args.num_heads == 0, "d_hidden must be divisible by n_heads"
+        self.args = args
+        self.d_hidden = args.d_hidden
+        self.n_patches = (args.img_size[1] * args.img_size[2]) // (args.patch_size * args.patch_size)
+        self.max_seq_length = self.n_patches + 1
+        self.patch_embedding = PatchEmbedding(args.d_hidden, args.img_size[1:], (args.patch_size, args.patch_size),
+                                              args.img_size[0])
+        self.positional_encoding = PositionalEncoding(args.d_hidden, self.max_seq_length)
+        self.transformer_encoder = nn.Sequential(*[
+            TransformerEncoder(args, args.d_hidden, args.d_mlp, args.num_heads, args.dropout,
+                               args.attention_dropout) for _ in range(args.num_layers)])
+        self.classifier = nn.Linear(args.d_hidden, args.num_classes)
+        self.device = getattr(args, "device", "cuda")
+        self.name = f"VIT {args.layer}"
+        self.to(self.device)
+
+    def forward(self, x):
+        x = self.positional_encoding(self.patch_embedding(x))
+        x = self.transformer_encoder(x)
+        return self.classifier(x[:, 0])
+
+    def set_candidates(self, cand):
+        """Fix the candidate set of every sampled-mode ConvNN layer (the reference redraws a
+        permutation per layer call; ranks of a batch-sharded run must share one set)."""
+        for m in self.modules():
+            if isinstance(m, MultiHeadConvNNAttention):
+                m.candidate_override = cand

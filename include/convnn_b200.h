@@ -1,0 +1,142 @@
+/*
+ * convnn_b200 — C ABI of the B200 (sm_100a) ConvNN-Attention forward path.
+ *
+ * The reference is eager PyTorch and has no native interface; each entry point below
+ * replaces a span of `MultiHeadConvNNAttention.forward` (reference layers.py:261-321)
+ * and is what a Python/ctypes (or C++) binding of that span binds to.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer owned by the caller.  The library allocates
+ *     nothing, frees nothing and keeps no pointer after the call returns.
+ *   - All work is enqueued on `stream` (a cudaStream_t passed as void*); no call
+ *     synchronises the host.  Calls are re-entrant; the only process-wide state is a
+ *     launch counter.
+ *   - Return value: CONVNN_OK or a negative convnn_status; a human-readable reason for
+ *     the last failure on the calling thread is in convnn_b200_last_error().
+ *   - `dtype` is the storage type of activations and weights (float32 or bfloat16);
+ *     accumulation, similarity values, softmax and statistics are always float32.
+ *
+ * Layouts (row-major, innermost last)
+ *   x        (B, T, D)       row stride `ldx` elements (>= D; lets a caller pass the
+ *                            channel slice x[:, :, :D] of a wider tensor, layers.py:648)
+ *   cand     (S) int32       candidate token indices of the sampled modes, else NULL
+ *   q        (B, S, H, Cp)   Cp = convnn_b200_head_channels(): d_k, or with the
+ *   k, v     (B, T, H, Cp)   coordinate channel d_k+1 rounded up to a multiple of 8
+ *                            (channel d_k holds the coordinate, the rest are zero)
+ *   qstat    (B, H, S) f32   cosine: 1/max(|q|,1e-12); euclidean: |q|^2; matmul: unused
+ *   kstat    (B, H, T) f32   same for k
+ *   idx, val (B, H, T, K)    int32 neighbour token indices / float32 pre-softmax
+ *                            values, best first (sampled modes: slot 0 = self, value 1)
+ *   o        (B, H, T, d_k)  per-head Conv1d output, token-major
+ *   out      (B, T, D)       row stride `ldo` elements
+ *
+ * Packed weights (all in `dtype`; the Python module packs and caches them)
+ *   w_qkv    (3, D, D)       [W_k; W_v; W_q], each (out, in) as nn.Linear stores it
+ *   w_conv   depthwise / depthwise-separable stage 0: (K, C) tap-major, from (C, 1, K)
+ *            standard: (K, C, d_k) from (d_k, C, K)
+ *   w_pw     depthwise-separable stage 1: (C, d_k) from (d_k, C, 1); else NULL
+ *   w_o      (D, D) (out, in)
+ */
+#ifndef CONVNN_B200_H
+#define CONVNN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CONVNN_B200_ABI_VERSION 1
+
+enum convnn_dtype { CONVNN_F32 = 0, CONVNN_BF16 = 1 };
+enum convnn_metric { CONVNN_COSINE = 0, CONVNN_MATMUL = 1, CONVNN_EUCLIDEAN = 2 };
+enum convnn_conv { CONVNN_DEPTHWISE = 0, CONVNN_STANDARD = 1, CONVNN_DEPTHWISE_SEPARABLE = 2 };
+
+enum convnn_status {
+    CONVNN_OK = 0,
+    CONVNN_E_INVALID = -1,      /* argument out of range / inconsistent descriptor     */
+    CONVNN_E_UNSUPPORTED = -2,  /* legal in the reference but outside this build        */
+    CONVNN_E_NULL = -3,         /* a required pointer is NULL                            */
+    CONVNN_E_ALIGN = -4,        /* pointer or leading dimension not 16-byte aligned      */
+    CONVNN_E_WORKSPACE = -5,    /* workspace smaller than convnn_b200_workspace_bytes()  */
+    CONVNN_E_CUDA = -6,         /* launch failed (cudaGetLastError)                      */
+    CONVNN_E_DEVICE = -7,       /* current device is not sm_100                          */
+    CONVNN_E_TOPK_RANGE = -8,   /* K exceeds the candidate count (torch.topk would raise)*/
+    CONVNN_E_SEQ_LENGTH = -9    /* H > 1 and T != seq_length (reference reshape raises)  */
+};
+
+/* Problem descriptor: the constructor arguments of the reference layer
+ * (layers.py:133-146) plus the shapes of this call. */
+typedef struct convnn_desc {
+    int32_t B;           /* batch                                                        */
+    int32_t T;           /* tokens per sequence                                          */
+    int32_t S;           /* candidates: T for sampling 'all', len(cand) otherwise        */
+    int32_t D;           /* d_hidden = H * d_k                                           */
+    int32_t H;           /* num_heads                                                    */
+    int32_t K;           /* neighbours per token (Conv1d kernel size and stride)         */
+    int32_t dtype;       /* convnn_dtype                                                 */
+    int32_t metric;      /* convnn_metric (magnitude_type)                               */
+    int32_t sampled;     /* 0: sampling_type 'all'; 1: 'random' / 'spatial' via cand[]   */
+    int32_t conv_type;   /* convnn_conv                                                  */
+    int32_t softmax;     /* softmax_topk_val                                             */
+    int32_t coord;       /* coordinate_encoding                                          */
+    int32_t seq_length;  /* ctor seq_length; H > 1 requires T == seq_length              */
+    int32_t reserved;    /* must be 0                                                    */
+} convnn_desc;
+
+/* No reference counterpart: ABI guard for bindings. */
+int convnn_b200_abi_version(void);
+const char* convnn_b200_status_string(int status);
+const char* convnn_b200_last_error(void);
+/* No reference counterpart: number of kernels this library has launched in the process so
+ * far (a monotonically increasing statistic; the only process-wide state it keeps). */
+uint64_t convnn_b200_launch_count(void);
+
+/* Channels per head as stored in q/k/v (Cp above). Negative status on a bad descriptor. */
+int convnn_b200_head_channels(const convnn_desc* d);
+
+/* Bytes of scratch convnn_b200_forward() needs for this descriptor (q, k, v, qstat,
+ * kstat, idx, val, o).  Replaces the temporaries the reference allocates implicitly
+ * along layers.py:264-313. 0 on a bad descriptor. */
+size_t convnn_b200_workspace_bytes(const convnn_desc* d);
+
+/* K/V/Q projections, head split and (optional) coordinate channel, plus the per-row
+ * statistics the similarity needs.  Replaces layers.py:264-265, 269-270, 274-276,
+ * 285-287, 298-300 and the norm terms of layers.py:328-329, 337-338. */
+int convnn_b200_qkv_proj(const convnn_desc* d, const void* x, int64_t ldx, const void* w_qkv,
+                         const int32_t* cand, void* q, void* k, void* v,
+                         float* qstat, float* kstat, void* stream);
+
+/* Similarity (cosine / matmul / euclidean), sampled-mode self mask and sorted top-K
+ * without materialising the T x S matrix.  Replaces layers.py:278/289/302 (323-340),
+ * 291-292, 304-305 and the torch.topk + index mapping of layers.py:344, 363-376, 391,
+ * 410-423.  Exact ties keep the lower candidate column. */
+int convnn_b200_sim_topk(const convnn_desc* d, const void* q, const void* k,
+                         const float* qstat, const float* kstat, const int32_t* cand,
+                         int32_t* idx, float* val, void* stream);
+
+/* Softmax (or raw / reciprocal) weights over the K values, neighbour gather of V and the
+ * K-tap stride-K Conv1d.  Replaces layers.py:345-357, 378-386, 394-405, 425-436 and
+ * self.conv (layers.py:313, 187-228). */
+int convnn_b200_gather_conv(const convnn_desc* d, const void* v, const int32_t* idx,
+                            const float* val, const void* w_conv, const void* w_pw,
+                            void* o, void* stream);
+
+/* Head merge (including the reference's flat reinterpretation for H > 1) and the W_o
+ * projection.  Replaces layers.py:317, 320 (247-259). */
+int convnn_b200_out_proj(const convnn_desc* d, const void* o, const void* w_o,
+                         void* out, int64_t ldo, void* stream);
+
+/* The whole layer forward: the four calls above chained on `stream` with their
+ * intermediates placed in `workspace`.  Replaces MultiHeadConvNNAttention.forward
+ * (layers.py:261-321), eval mode. */
+int convnn_b200_forward(const convnn_desc* d, const void* x, int64_t ldx, const void* w_qkv,
+                        const void* w_conv, const void* w_pw, const void* w_o,
+                        const int32_t* cand, void* out, int64_t ldo,
+                        void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CONVNN_B200_H */

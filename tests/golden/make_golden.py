@@ -109,6 +109,18 @@ def main() -> int:
         kwj["img_size"] = list(kw["img_size"])
         manifest["vit"][name] = {"B": B, "cfg": kwj, "x_sum": checksum(img), "w_sum": weights_checksum(sd)}
         print(name, tuple(y.shape), float(y.abs().mean()))
+    # state_dict layouts of the reference modules (key -> shape) for the drop-in contract
+    L = ref_layers
+    sd_cases = {
+        "convnn_depthwise": L.MultiHeadConvNNAttention(48, 3, 0.0, 9, "all", -1, 0, "cosine"),
+        "convnn_standard_coord": L.MultiHeadConvNNAttention(48, 3, 0.0, 9, "all", -1, 0, "cosine", 197, True, "standard"),
+        "convnn_dwsep": L.MultiHeadConvNNAttention(48, 3, 0.0, 9, "all", -1, 0, "cosine", 197, False, "depthwise-separable"),
+        "branch_attention": L.MultiHeadBranchingAttention(96, 3, 0.0, 9, "all", -1, 0, "cosine", 197, False, "standard", True, 0.5),
+        "branch_conv": L.MultiHeadBranchingConv(96, 3, 0.0, 5, 9, "all", -1, 0, "cosine", 197, False, "depthwise", True, 0.5),
+        "vit_tiny_convnn": reference_vit(ref_vit, ViTConfig(**VIT_CASES["vit_tiny_cifar_convnn"][1]),
+                                         make_vit_weights(ViTConfig(**VIT_CASES["vit_tiny_cifar_convnn"][1]), seed=1)),
+    }
+    manifest["state_dict"] = {n: {k: list(v.shape) for k, v in m.state_dict().items()} for n, m in sd_cases.items()}
     np.savez_compressed(os.path.join(HERE, "reference_outputs.npz"), **arrays)
     with open(os.path.join(HERE, "manifest.json"), "w") as f:
         json.dump(manifest, f, indent=1, sort_keys=True)
