@@ -108,10 +108,10 @@ def project_qkv(x: torch.Tensor, w: Dict[str, torch.Tensor], cfg: ConvNNConfig,
     v = _split_heads(x @ w["W_v.weight"].t(), H)
     xq = x if cand is None else x[:, cand, :]
     q = _split_heads(xq @ w["W_q.weight"].t(), H)
-    if policy == "bf16":
-        q, k, v = bf16_round(q), bf16_round(k), bf16_round(v)
     if cfg.coordinate_encoding:
         q, k, v = _append_coordinate(q), _append_coordinate(k), _append_coordinate(v)
+    if policy == "bf16":   # the stored tensors, coordinate channel included, are bfloat16
+        q, k, v = bf16_round(q), bf16_round(k), bf16_round(v)
     return q, k, v
 
 

@@ -40,6 +40,7 @@ def run_stages(cfg, w, x, cand, dtype):
 def test_fp32_stages_against_oracle_and_reference(name):
     cfg, w, x, want, cand = layer_case(name)
     tr = convnn_attention(x, w, cfg, cand=cand)
+    cand = tr.cand                     # spatial candidates are resolved by the oracle
     q, k, v, qs, ks, idx, val, o, out = run_stages(cfg, w, x, cand, torch.float32)
     C = cfg.in_channels
     assert rel_err(heads_to_oracle(q, C), tr.q) < 1e-5
@@ -69,7 +70,7 @@ def test_fp32_module_forward_equals_staged_calls(name):
     with torch.no_grad():
         y1 = m(x.to(DEV))
         y2 = m(x.to(DEV))
-    out = run_stages(cfg, w, x, cand, torch.float32)[-1]
+    out = run_stages(cfg, w, x, m.candidates(x.shape[1], torch.device(DEV)), torch.float32)[-1]
     assert torch.equal(y1, y2), "two runs differ bit-wise"
     assert torch.equal(y1, out)
 
@@ -80,6 +81,7 @@ def test_bf16_stages_against_oracle(name):
     x = bf16_round(x)
     w = {n: bf16_round(t) for n, t in w.items()}
     tr = convnn_attention(x, w, cfg, cand=cand, policy="bf16")
+    cand = tr.cand
     q, k, v, qs, ks, idx, val, o, out = run_stages(cfg, w, x, cand, torch.bfloat16)
     C, dk = cfg.in_channels, cfg.d_k
     # projections: equal up to one bfloat16 rounding step where the fp32 sums differ in order
