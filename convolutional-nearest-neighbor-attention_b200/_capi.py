@@ -34,6 +34,7 @@ SIGNATURES = {
     "convnn_b200_status_string": (ctypes.c_char_p, [ctypes.c_int]),
     "convnn_b200_last_error": (ctypes.c_char_p, []),
     "convnn_b200_launch_count": (ctypes.c_uint64, []),
+    "convnn_b200_device_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_int)]),
     "convnn_b200_head_channels": (ctypes.c_int, [ctypes.POINTER(ConvnnDesc)]),
     "convnn_b200_workspace_bytes": (c_size, [ctypes.POINTER(ConvnnDesc)]),
     "convnn_b200_qkv_proj": (ctypes.c_int, [ctypes.POINTER(ConvnnDesc), c_void, c_i64, c_void, c_void, c_void,
@@ -111,3 +112,10 @@ def make_desc(B, T, S, D, H, K, dtype, metric, sampled, conv_type, softmax, coor
 def ptr(t) -> int:
     """Device pointer of a torch tensor (None -> NULL)."""
     return None if t is None else t.data_ptr()
+
+
+def device_status() -> int:
+    """Error latch of the tensor-core kernels (0 = clean); synchronises the device."""
+    code = ctypes.c_int(0)
+    check(lib().convnn_b200_device_status(ctypes.byref(code)))
+    return code.value

@@ -2,6 +2,7 @@
 // chaining of the stage kernels on the caller's stream.
 #include <atomic>
 #include <stdarg.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -18,6 +19,14 @@ int set_error(int status, const char* fmt, ...) {
     return status;
 }
 void clear_error() { g_err[0] = 0; }
+
+bool force_simt() {
+    static const bool v = [] {
+        const char* e = getenv("CONVNN_B200_FORCE_SIMT");
+        return e && e[0] == '1';
+    }();
+    return v;
+}
 
 static std::atomic<unsigned long long> g_launches{0};
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
@@ -131,6 +140,11 @@ const char* convnn_b200_status_string(int s) {
 
 const char* convnn_b200_last_error(void) { return g_err; }
 
+int convnn_b200_device_status(int* code) {
+    if (!code) return set_error(CONVNN_E_NULL, "convnn_b200_device_status: argument 'code' is NULL");
+    return read_sim_topk_status(code);
+}
+
 uint64_t convnn_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int convnn_b200_head_channels(const convnn_desc* d) {
@@ -188,6 +202,8 @@ int convnn_b200_sim_topk(const convnn_desc* d, const void* q, const void* k, con
     if (d->metric != CONVNN_MATMUL) { REQUIRE_PTR(qstat); REQUIRE_PTR(kstat); }
     if ((rc = check_device())) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!force_simt() && sim_topk_tc_supported(d, dm, q, k))
+        return launch_sim_topk_tc(d, dm, q, k, qstat, kstat, cand, idx, val, st);
     if (d->dtype == CONVNN_F32) return launch_sim_topk_simt_f32(d, dm, q, k, qstat, kstat, cand, idx, val, st);
     return launch_sim_topk_simt_bf16(d, dm, q, k, qstat, kstat, cand, idx, val, st);
 }

@@ -85,6 +85,11 @@ int launch_sim_topk_simt_f32(const convnn_desc* d, const Dims& dm, const void* q
 int launch_sim_topk_simt_bf16(const convnn_desc* d, const Dims& dm, const void* q, const void* k,
                               const float* qstat, const float* kstat, const int32_t* cand,
                               int32_t* idx, float* val, cudaStream_t st);
+bool sim_topk_tc_supported(const convnn_desc* d, const Dims& dm, const void* q, const void* k);
+int launch_sim_topk_tc(const convnn_desc* d, const Dims& dm, const void* q, const void* k, const float* qstat,
+                       const float* kstat, const int32_t* cand, int32_t* idx, float* val, cudaStream_t st);
+int read_sim_topk_status(int* out);
+bool force_simt();   // debugging switch: environment variable CONVNN_B200_FORCE_SIMT=1
 int launch_gather_conv_simt(const convnn_desc* d, const Dims& dm, const void* v, const int32_t* idx,
                             const float* val, const void* w_conv, const void* w_pw, void* o,
                             cudaStream_t st);

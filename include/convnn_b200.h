@@ -93,6 +93,12 @@ const char* convnn_b200_last_error(void);
  * far (a monotonically increasing statistic; the only process-wide state it keeps). */
 uint64_t convnn_b200_launch_count(void);
 
+/* No reference counterpart: reads the device-side error latch (synchronises the device).
+ * 0 = no kernel gave up; otherwise the code of the first bounded wait that expired inside
+ * a tensor-core kernel (1 producer, 2/3 MMA issuer, 4 epilogue).  Results of a call that
+ * latched a code are undefined. */
+int convnn_b200_device_status(int* code);
+
 /* Channels per head as stored in q/k/v (Cp above). Negative status on a bad descriptor. */
 int convnn_b200_head_channels(const convnn_desc* d);
 

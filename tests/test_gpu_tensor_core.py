@@ -1,0 +1,69 @@
+"""The tcgen05 similarity/top-K kernel on shapes that exercise every tiling path:
+several row tiles, several column tiles with a ragged last tile, the 128/64/32-byte
+swizzle chunkings (d_k multiple of 64 / 32 / 16), K up to 32, sampled masks."""
+import pytest
+import torch
+
+from convnn_b200 import _capi, ops
+from oracle.convnn_oracle import ConvNNConfig, near_tie_rows, select_neighbours, similarity
+from gpu_util import DEV, spec_of
+
+pytestmark = pytest.mark.gpu
+
+CASES = [
+    # B, T, S, D, H, K, metric, sampling
+    (3, 197, 197, 192, 1, 9, "cosine", "all"),
+    (2, 300, 300, 64, 1, 25, "cosine", "all"),
+    (2, 700, 700, 128, 2, 9, "matmul", "all"),
+    (2, 197, 64, 384, 1, 9, "euclidean", "random"),
+    (1, 1024, 256, 96, 1, 9, "cosine", "spatial"),
+    (2, 197, 197, 384, 12, 9, "cosine", "all"),
+    (1, 130, 130, 48, 1, 32, "euclidean", "all"),
+    (1, 1030, 1030, 64, 1, 4, "cosine", "all"),
+    (2, 50, 17, 32, 1, 16, "matmul", "random"),
+]
+
+
+@pytest.mark.parametrize("B,T,S,D,H,K,metric,sampling", CASES)
+def test_tensor_core_topk_matches_oracle(B, T, S, D, H, K, metric, sampling):
+    g = torch.Generator().manual_seed(B * 1000 + T)
+    dk = D // H
+    q = torch.randn(B, S, H, dk, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, T, H, dk, generator=g).to(torch.bfloat16)
+    cand = None
+    if sampling != "all":
+        cand = torch.randperm(T, generator=g)[:S] if sampling == "random" else torch.linspace(0, T - 1, S).long()
+    cfg = ConvNNConfig(d_hidden=D, num_heads=H, K=K, sampling_type=sampling, num_samples=S, magnitude_type=metric,
+                       seq_length=T)
+    qo, ko = q.float().permute(0, 2, 1, 3), k.float().permute(0, 2, 1, 3)     # (B,H,rows,dk)
+    if metric == "cosine":
+        qstat, kstat = 1.0 / qo.norm(dim=-1).clamp_min(1e-12), 1.0 / ko.norm(dim=-1).clamp_min(1e-12)
+    else:
+        qstat, kstat = (qo * qo).sum(-1), (ko * ko).sum(-1)
+    sim = similarity(qo, ko, cfg, cand, dtype=torch.float64)
+    idx_want, val_want = select_neighbours(sim, cfg, cand)
+    spec = spec_of(cfg)
+    idx, val = ops.sim_topk(spec, q.to(DEV), k.to(DEV), qstat.contiguous().to(DEV), kstat.contiguous().to(DEV),
+                            None if cand is None else cand.to(DEV))
+    torch.cuda.synchronize()
+    assert _capi.device_status() == 0
+    ties = near_tie_rows(sim, cfg, cand is not None, 2e-6)
+    same = (idx.cpu().long() == idx_want).all(-1)
+    assert bool((same | ties).all()), f"{int((~(same | ties)).sum())} rows differ without a near-tie"
+    assert float(ties.float().mean()) < 0.05
+    dv = (val.cpu().double() - val_want).abs() / val_want.abs().clamp_min(1.0)
+    assert float(dv[same].max()) < 1e-5
+
+
+def test_tensor_core_and_simt_kernels_agree_bitwise_on_indices():
+    """Same q / k through the SIMT float path (q, k upcast) and the tensor-core path."""
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(2, 197, 1, 192, generator=g).to(torch.bfloat16)
+    k = torch.randn(2, 197, 1, 192, generator=g).to(torch.bfloat16)
+    cfg = ConvNNConfig(d_hidden=192, num_heads=1, K=9, magnitude_type="matmul")
+    spec = spec_of(cfg)
+    i16, v16 = ops.sim_topk(spec, q.to(DEV), k.to(DEV), None, None)
+    i32, v32 = ops.sim_topk(spec, q.float().to(DEV), k.float().to(DEV), None, None)
+    same = (i16 == i32).all(-1)
+    assert float(same.float().mean()) > 0.999
+    assert float((v16 - v32).abs().max()) < 1e-4
