@@ -37,13 +37,15 @@ SIGNATURES = {
     "convnn_b200_device_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_int)]),
     "convnn_b200_head_channels": (ctypes.c_int, [ctypes.POINTER(ConvnnDesc)]),
     "convnn_b200_workspace_bytes": (c_size, [ctypes.POINTER(ConvnnDesc)]),
+    "convnn_b200_stage_scratch_bytes": (c_size, [ctypes.POINTER(ConvnnDesc)]),
     "convnn_b200_qkv_proj": (ctypes.c_int, [ctypes.POINTER(ConvnnDesc), c_void, c_i64, c_void, c_void, c_void,
-                                            c_void, c_void, c_void, c_void, c_void]),
+                                            c_void, c_void, c_void, c_void, c_void, c_void]),
     "convnn_b200_sim_topk": (ctypes.c_int, [ctypes.POINTER(ConvnnDesc), c_void, c_void, c_void, c_void, c_void,
                                             c_void, c_void, c_void]),
     "convnn_b200_gather_conv": (ctypes.c_int, [ctypes.POINTER(ConvnnDesc), c_void, c_void, c_void, c_void, c_void,
                                                c_void, c_void]),
-    "convnn_b200_out_proj": (ctypes.c_int, [ctypes.POINTER(ConvnnDesc), c_void, c_void, c_void, c_i64, c_void]),
+    "convnn_b200_out_proj": (ctypes.c_int, [ctypes.POINTER(ConvnnDesc), c_void, c_void, c_void, c_i64, c_void,
+                                            c_void]),
     "convnn_b200_forward": (ctypes.c_int, [ctypes.POINTER(ConvnnDesc), c_void, c_i64, c_void, c_void, c_void, c_void,
                                            c_void, c_void, c_i64, c_void, c_size, c_void]),
 }

@@ -83,13 +83,17 @@ int check_device() {
 }
 
 struct Workspace {
-    char *q, *k, *v, *o;
+    char *q, *k, *v, *o, *scratch;
     float *qstat, *kstat, *val;
     int32_t* idx;
     size_t total;
 };
 
 size_t up256(size_t n) { return (n + 255) & ~(size_t)255; }
+
+// Gathered candidate rows of x (B, S, D) for the query projection, later reused for the
+// head-merged (B, T, D) operand of the output projection.
+size_t stage_scratch(const Dims& dm) { return (size_t)dm.B * (dm.T > dm.S ? dm.T : dm.S) * dm.D * dm.elt; }
 
 Workspace carve(const Dims& dm, void* base) {
     Workspace w;
@@ -104,6 +108,7 @@ Workspace carve(const Dims& dm, void* base) {
     w.kstat = reinterpret_cast<float*>(take((size_t)dm.B * dm.H * dm.T * 4));
     w.val = reinterpret_cast<float*>(take((size_t)dm.B * dm.H * dm.T * dm.K * 4));
     w.idx = reinterpret_cast<int32_t*>(take((size_t)dm.B * dm.H * dm.T * dm.K * 4));
+    w.scratch = take(stage_scratch(dm));
     w.total = off;
     return w;
 }
@@ -142,7 +147,11 @@ const char* convnn_b200_last_error(void) { return g_err; }
 
 int convnn_b200_device_status(int* code) {
     if (!code) return set_error(CONVNN_E_NULL, "convnn_b200_device_status: argument 'code' is NULL");
-    return read_sim_topk_status(code);
+    int a = 0, b = 0, rc;
+    if ((rc = read_sim_topk_status(&a))) return rc;
+    if ((rc = read_gemm_tc_status(&b))) return rc;
+    *code = a ? a : b;
+    return CONVNN_OK;
 }
 
 uint64_t convnn_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
@@ -153,6 +162,12 @@ int convnn_b200_head_channels(const convnn_desc* d) {
     return rc != CONVNN_OK ? rc : dm.Cp;
 }
 
+size_t convnn_b200_stage_scratch_bytes(const convnn_desc* d) {
+    Dims dm;
+    if (validate(d, &dm) != CONVNN_OK) return 0;
+    return stage_scratch(dm);
+}
+
 size_t convnn_b200_workspace_bytes(const convnn_desc* d) {
     Dims dm;
     if (validate(d, &dm) != CONVNN_OK) return 0;
@@ -161,7 +176,7 @@ size_t convnn_b200_workspace_bytes(const convnn_desc* d) {
 
 int convnn_b200_qkv_proj(const convnn_desc* d, const void* x, int64_t ldx, const void* w_qkv,
                          const int32_t* cand, void* q, void* k, void* v, float* qstat, float* kstat,
-                         void* stream) {
+                         void* scratch, void* stream) {
     Dims dm;
     int rc = validate(d, &dm);
     if (rc) return rc;
@@ -172,6 +187,29 @@ int convnn_b200_qkv_proj(const convnn_desc* d, const void* x, int64_t ldx, const
     if ((rc = check_device())) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t wsz = (size_t)dm.D * dm.D * dm.elt;
+    const bool stats = d->metric != CONVNN_MATMUL;
+    // bfloat16 without the coordinate channel: (B, rows, H, d_k) is plain (B*rows, D), so the
+    // projections are ordinary GEMMs for the tensor cores
+    if (d->dtype == CONVNN_BF16 && !d->coord && !force_simt()) {
+        const char* wb = static_cast<const char*>(w_qkv);
+        void* kvq[3] = {k, v, q};
+        bool done = false;
+        if (!d->sampled && gemm_tc_supported(x, ldx, w_qkv, dm.D, 3 * dm.D, 3, kvq, dm.D)) {
+            if ((rc = launch_gemm_tc(x, ldx, w_qkv, nullptr, dm.B * dm.T, 3 * dm.D, dm.D, 3, kvq, dm.D, 0, st))) return rc;
+            done = true;
+        } else if (d->sampled && scratch && gemm_tc_supported(x, ldx, w_qkv, dm.D, 2 * dm.D, 2, kvq, dm.D) &&
+                   gemm_tc_supported(scratch, dm.D, wb + 2 * wsz, dm.D, dm.D, 1, &kvq[2], dm.D)) {
+            if ((rc = launch_gemm_tc(x, ldx, w_qkv, nullptr, dm.B * dm.T, 2 * dm.D, dm.D, 2, kvq, dm.D, 0, st))) return rc;
+            if ((rc = launch_gather_rows(d->dtype, x, ldx, cand, scratch, dm.B, dm.T, dm.S, dm.D, st))) return rc;
+            if ((rc = launch_gemm_tc(scratch, dm.D, wb + 2 * wsz, nullptr, dm.B * dm.S, dm.D, dm.D, 1, &kvq[2], dm.D, 0, st)))
+                return rc;
+            done = true;
+        }
+        if (done) {
+            if ((rc = launch_head_fill_and_stats(d, dm, q, dm.S, stats ? qstat : nullptr, st))) return rc;
+            return launch_head_fill_and_stats(d, dm, k, dm.T, stats ? kstat : nullptr, st);
+        }
+    }
     GemmParams p{};
     p.a = x; p.lda = ldx; p.bias = nullptr; p.N = dm.D; p.Kd = dm.D;
     p.a_mode = A_TOKENS; p.c_mode = C_HEADS; p.T = dm.T; p.H = dm.H; p.dk = dm.dk; p.Cp = dm.Cp; p.gelu = 0;
@@ -185,7 +223,6 @@ int convnn_b200_qkv_proj(const convnn_desc* d, const void* x, int64_t ldx, const
     p.cand = d->sampled ? cand : nullptr; p.rows_per_batch = dm.S; p.M = dm.B * dm.S;
     p.w = static_cast<const char*>(w_qkv) + 2 * wsz; p.c = q;
     if ((rc = launch_gemm_simt(d->dtype, p, st))) return rc;
-    const bool stats = d->metric != CONVNN_MATMUL;
     if ((rc = launch_head_fill_and_stats(d, dm, q, dm.S, stats ? qstat : nullptr, st))) return rc;
     if ((rc = launch_head_fill_and_stats(d, dm, k, dm.T, stats ? kstat : nullptr, st))) return rc;
     if ((rc = launch_head_fill_and_stats(d, dm, v, dm.T, nullptr, st))) return rc;
@@ -220,13 +257,23 @@ int convnn_b200_gather_conv(const convnn_desc* d, const void* v, const int32_t* 
 }
 
 int convnn_b200_out_proj(const convnn_desc* d, const void* o, const void* w_o, void* out, int64_t ldo,
-                         void* stream) {
+                         void* scratch, void* stream) {
     Dims dm;
     int rc = validate(d, &dm);
     if (rc) return rc;
     REQUIRE_PTR(o); REQUIRE_PTR(w_o); REQUIRE_PTR(out);
     if (ldo < dm.D) return set_error(CONVNN_E_INVALID, "ldo=%lld is smaller than D=%d", (long long)ldo, dm.D);
     if ((rc = check_device())) return rc;
+    if (d->dtype == CONVNN_BF16 && !force_simt()) {
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        void* cs[1] = {out};
+        if (dm.H == 1 && gemm_tc_supported(o, dm.D, w_o, dm.D, dm.D, 1, cs, ldo))
+            return launch_gemm_tc(o, dm.D, w_o, nullptr, dm.B * dm.T, dm.D, dm.D, 1, cs, ldo, 0, st);
+        if (dm.H > 1 && scratch && gemm_tc_supported(scratch, dm.D, w_o, dm.D, dm.D, 1, cs, ldo)) {
+            if ((rc = launch_merge_heads(d->dtype, o, scratch, dm.B, dm.T, dm.H, dm.dk, st))) return rc;
+            return launch_gemm_tc(scratch, dm.D, w_o, nullptr, dm.B * dm.T, dm.D, dm.D, 1, cs, ldo, 0, st);
+        }
+    }
     GemmParams p{};
     p.a = o; p.w = w_o; p.bias = nullptr; p.c = out; p.cand = nullptr;
     p.lda = dm.D; p.ldc = ldo; p.M = dm.B * dm.T; p.N = dm.D; p.Kd = dm.D;
@@ -246,10 +293,10 @@ int convnn_b200_forward(const convnn_desc* d, const void* x, int64_t ldx, const 
     Workspace w = carve(dm, workspace);
     if (workspace_bytes < w.total)
         return set_error(CONVNN_E_WORKSPACE, "workspace has %zu bytes, %zu needed", workspace_bytes, w.total);
-    if ((rc = convnn_b200_qkv_proj(d, x, ldx, w_qkv, cand, w.q, w.k, w.v, w.qstat, w.kstat, stream))) return rc;
+    if ((rc = convnn_b200_qkv_proj(d, x, ldx, w_qkv, cand, w.q, w.k, w.v, w.qstat, w.kstat, w.scratch, stream))) return rc;
     if ((rc = convnn_b200_sim_topk(d, w.q, w.k, w.qstat, w.kstat, cand, w.idx, w.val, stream))) return rc;
     if ((rc = convnn_b200_gather_conv(d, w.v, w.idx, w.val, w_conv, w_pw, w.o, stream))) return rc;
-    return convnn_b200_out_proj(d, w.o, w_o, out, ldo, stream);
+    return convnn_b200_out_proj(d, w.o, w_o, out, ldo, w.scratch, stream);
 }
 
 }  // extern "C"

@@ -89,6 +89,15 @@ bool sim_topk_tc_supported(const convnn_desc* d, const Dims& dm, const void* q, 
 int launch_sim_topk_tc(const convnn_desc* d, const Dims& dm, const void* q, const void* k, const float* qstat,
                        const float* kstat, const int32_t* cand, int32_t* idx, float* val, cudaStream_t st);
 int read_sim_topk_status(int* out);
+int read_gemm_tc_status(int* out);
+// bfloat16 tensor-core GEMM C = A W^T (+bias, +GELU); `parts` outputs share M and split N evenly.
+bool gemm_tc_supported(const void* a, long long lda, const void* w, int Kd, int N, int parts, const void* const* c,
+                       long long ldc);
+int launch_gemm_tc(const void* a, long long lda, const void* w, const void* bias, int M, int N, int Kd, int parts,
+                   void* const* c, long long ldc, int gelu, cudaStream_t st);
+int launch_gather_rows(int dtype, const void* x, long long ldx, const int32_t* cand, void* xq, int B, int Tn, int S,
+                       int D, cudaStream_t st);
+int launch_merge_heads(int dtype, const void* o, void* y, int B, int Tn, int H, int dk, cudaStream_t st);
 bool force_simt();   // debugging switch: environment variable CONVNN_B200_FORCE_SIMT=1
 int launch_gather_conv_simt(const convnn_desc* d, const Dims& dm, const void* v, const int32_t* idx,
                             const float* val, const void* w_conv, const void* w_pw, void* o,

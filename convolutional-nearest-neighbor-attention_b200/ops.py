@@ -117,8 +117,10 @@ def qkv_proj(spec: LayerSpec, x: torch.Tensor, w_qkv: torch.Tensor, cand: Option
     v = torch.empty(B, T, H, Cp, dtype=x.dtype, device=x.device)
     qstat = torch.empty(B, H, S, dtype=torch.float32, device=x.device)
     kstat = torch.empty(B, H, T, dtype=torch.float32, device=x.device)
+    scratch = torch.empty(L.convnn_b200_stage_scratch_bytes(d), dtype=torch.uint8, device=x.device)
     _capi.check(L.convnn_b200_qkv_proj(d, x.data_ptr(), ldx, w_qkv.data_ptr(), _capi.ptr(cand), q.data_ptr(),
-                                       k.data_ptr(), v.data_ptr(), qstat.data_ptr(), kstat.data_ptr(), _stream(x)))
+                                       k.data_ptr(), v.data_ptr(), qstat.data_ptr(), kstat.data_ptr(),
+                                       scratch.data_ptr(), _stream(x)))
     return q, k, v, qstat, kstat
 
 
@@ -159,7 +161,9 @@ def out_proj(spec: LayerSpec, o, w_o, out: Optional[torch.Tensor] = None, S: Opt
     view, ldo = _rows_view(out)
     if view is not out:
         raise ValueError("out must have unit channel stride and evenly strided rows")
-    _capi.check(L.convnn_b200_out_proj(d, o.data_ptr(), w_o.data_ptr(), out.data_ptr(), ldo, _stream(o)))
+    scratch = torch.empty(L.convnn_b200_stage_scratch_bytes(d), dtype=torch.uint8, device=o.device)
+    _capi.check(L.convnn_b200_out_proj(d, o.data_ptr(), w_o.data_ptr(), out.data_ptr(), ldo, scratch.data_ptr(),
+                                       _stream(o)))
     return out
 
 

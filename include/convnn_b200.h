@@ -95,7 +95,7 @@ uint64_t convnn_b200_launch_count(void);
 
 /* No reference counterpart: reads the device-side error latch (synchronises the device).
  * 0 = no kernel gave up; otherwise the code of the first bounded wait that expired inside
- * a tensor-core kernel (1 producer, 2/3 MMA issuer, 4 epilogue).  Results of a call that
+ * a tensor-core kernel (similarity: 1 producer, 2/3 MMA issuer, 4 epilogue; GEMM: 11-14).  Results of a call that
  * latched a code are undefined. */
 int convnn_b200_device_status(int* code);
 
@@ -103,16 +103,22 @@ int convnn_b200_device_status(int* code);
 int convnn_b200_head_channels(const convnn_desc* d);
 
 /* Bytes of scratch convnn_b200_forward() needs for this descriptor (q, k, v, qstat,
- * kstat, idx, val, o).  Replaces the temporaries the reference allocates implicitly
+ * kstat, idx, val, o, stage scratch).  Replaces the temporaries the reference allocates implicitly
  * along layers.py:264-313. 0 on a bad descriptor. */
 size_t convnn_b200_workspace_bytes(const convnn_desc* d);
+
+/* Bytes of the optional `scratch` argument of the two projection stages: room for the
+ * gathered candidate rows (B, S, D) / the head-merged activations (B, T, D).  With
+ * scratch == NULL those stages still work but leave the tensor cores for the cases that
+ * need it (sampled queries; H > 1 output projection).  No reference counterpart. */
+size_t convnn_b200_stage_scratch_bytes(const convnn_desc* d);
 
 /* K/V/Q projections, head split and (optional) coordinate channel, plus the per-row
  * statistics the similarity needs.  Replaces layers.py:264-265, 269-270, 274-276,
  * 285-287, 298-300 and the norm terms of layers.py:328-329, 337-338. */
 int convnn_b200_qkv_proj(const convnn_desc* d, const void* x, int64_t ldx, const void* w_qkv,
                          const int32_t* cand, void* q, void* k, void* v,
-                         float* qstat, float* kstat, void* stream);
+                         float* qstat, float* kstat, void* scratch, void* stream);
 
 /* Similarity (cosine / matmul / euclidean), sampled-mode self mask and sorted top-K
  * without materialising the T x S matrix.  Replaces layers.py:278/289/302 (323-340),
@@ -132,7 +138,7 @@ int convnn_b200_gather_conv(const convnn_desc* d, const void* v, const int32_t* 
 /* Head merge (including the reference's flat reinterpretation for H > 1) and the W_o
  * projection.  Replaces layers.py:317, 320 (247-259). */
 int convnn_b200_out_proj(const convnn_desc* d, const void* o, const void* w_o,
-                         void* out, int64_t ldo, void* stream);
+                         void* out, int64_t ldo, void* scratch, void* stream);
 
 /* The whole layer forward: the four calls above chained on `stream` with their
  * intermediates placed in `workspace`.  Replaces MultiHeadConvNNAttention.forward

@@ -75,9 +75,34 @@ def test_fp32_module_forward_equals_staged_calls(name):
     assert torch.equal(y1, out)
 
 
-@pytest.mark.parametrize("name", LAYER_NAMES)
+BASELINE_SHAPES = {
+    # the layer shapes of the baseline configs at a reduced batch
+    "cfg2_tiny": (2, 197, dict(d_hidden=192, num_heads=1, K=9, magnitude_type="cosine")),
+    "cfg3_small": (2, 197, dict(d_hidden=384, num_heads=1, K=9, magnitude_type="euclidean", sampling_type="random",
+                                num_samples=64, convolution_type="depthwise-separable")),
+    "cfg4_branch_half": (2, 197, dict(d_hidden=384, num_heads=12, K=9, magnitude_type="cosine",
+                                      convolution_type="standard")),
+    "cfg5_long_all": (1, 1024, dict(d_hidden=768, num_heads=1, K=25, magnitude_type="cosine")),
+    "cfg5_long_spatial": (1, 1024, dict(d_hidden=768, num_heads=1, K=9, magnitude_type="cosine",
+                                        sampling_type="spatial", num_samples=256)),
+    "h3_matmul": (2, 197, dict(d_hidden=192, num_heads=3, K=9, magnitude_type="matmul")),
+}
+
+
+def _named_case(name):
+    if name in BASELINE_SHAPES:
+        B, T, kw = BASELINE_SHAPES[name]
+        cfg = ConvNNConfig(**kw)
+        cand = None
+        if cfg.sampling_type == "random":
+            cand = torch.randperm(T, generator=torch.Generator().manual_seed(17))[: cfg.num_samples]
+        return cfg, make_layer_weights(cfg, seed=7), make_input(B, T, cfg.d_hidden, seed=11), None, cand
+    return layer_case(name)
+
+
+@pytest.mark.parametrize("name", LAYER_NAMES + sorted(BASELINE_SHAPES))
 def test_bf16_stages_against_oracle(name):
-    cfg, w, x, _, cand = layer_case(name)
+    cfg, w, x, _, cand = _named_case(name)
     x = bf16_round(x)
     w = {n: bf16_round(t) for n, t in w.items()}
     tr = convnn_attention(x, w, cfg, cand=cand, policy="bf16")
