@@ -166,6 +166,51 @@ class StageTimer:
         return tot, cnt
 
 
+def stage_profile(model, B, cfg, dev, sets=4, reps=5):
+    """Device time per launch of each stage of one ConvNN layer at the bench shape.
+
+    Each stage is captured in a CUDA graph that runs it once on each of ``sets`` distinct
+    buffer sets (together larger than L2, so no launch finds its inputs cached by the
+    previous one) and the graph is timed with CUDA events on the launching stream."""
+    import convnn_b200
+    from convnn_b200 import ops
+    layer = next(m for m in model.modules() if isinstance(m, convnn_b200.MultiHeadConvNNAttention))
+    spec = layer._spec()
+    w_qkv, w_conv, w_pw, w_o = layer.packed_weights(torch.bfloat16, dev)
+    T, D = cfg.seq_len, cfg.d_hidden
+    g = torch.Generator(device="cpu").manual_seed(7)
+    data = []
+    for _ in range(sets):
+        x = torch.randn(B, T, D, generator=g).to(dev, torch.bfloat16)
+        q, k, v, qs, ks = ops.qkv_proj(spec, x, w_qkv)
+        idx, val = ops.sim_topk(spec, q, k, qs, ks)
+        o = ops.gather_conv(spec, v, idx, val, w_conv, w_pw)
+        data.append(dict(x=x, q=q, k=k, v=v, qs=qs, ks=ks, idx=idx, val=val, o=o))
+    fns = {
+        "qkv_proj": lambda d: ops.qkv_proj(spec, d["x"], w_qkv),
+        "sim_topk": lambda d: ops.sim_topk(spec, d["q"], d["k"], d["qs"], d["ks"]),
+        "gather_conv": lambda d: ops.gather_conv(spec, d["v"], d["idx"], d["val"], w_conv, w_pw),
+        "out_proj": lambda d: ops.out_proj(spec, d["o"], w_o),
+    }
+    out = {}
+    torch.cuda.synchronize()
+    for name, fn in fns.items():
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            keep = [fn(d) for d in data]
+        for _ in range(2):
+            graph.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        out[name] = e0.elapsed_time(e1) / (reps * sets)
+        del keep, graph
+    return out
+
+
 def algorithmic_work(B, T, S, D, H, K, elt=2):
     """Compulsory bytes / flops per launch of each stage (one layer call)."""
     idxval = 8 * B * H * T * K
@@ -294,22 +339,8 @@ def run_ours(args) -> int:
         barrier()
         ms_e2e = f0.elapsed_time(f1)
 
-        # ---- per-stage events for the roofline (same kernels through the stage entry points) -----
-        timer = StageTimer()
-        convs = [m for m in model.modules() if isinstance(m, convnn_b200.MultiHeadConvNNAttention)]
-        for m in convs:
-            m.stage_timer = timer
-        for i in range(2):
-            model(resident[i % NBUF])
-        torch.cuda.synchronize()
-        timer.marks.clear()
-        nprof = max(3, min(args.steps, 10))
-        for i in range(nprof):
-            model(resident[i % NBUF])
-        torch.cuda.synchronize()
-        stage_ms, stage_n = timer.totals()
-        for m in convs:
-            m.stage_timer = None
+        # ---- per-stage device time for the roofline ----------------------------------------
+        stage_ms = stage_profile(model, B, cfg, dev)
 
     t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
     if world > 1:
@@ -321,16 +352,15 @@ def run_ours(args) -> int:
         T = cfg.seq_len
         work = algorithmic_work(B, T, T, cfg.d_hidden, cfg.num_heads, cfg.K)
         dom = max(stage_ms, key=stage_ms.get)
-        per_launch_ms = stage_ms[dom] / stage_n[dom]
+        per_launch_ms = stage_ms[dom]
         ridge = pk["tf_sustained"] * 1e3 / pk["hbm"]
         ai = work[dom]["flops"] / work[dom]["bytes"]
         if ai > ridge:
             bound, ach, peak, unit = "tensor", work[dom]["flops"] / per_launch_ms / 1e9, pk["tf_sustained"], "TFLOP/s"
         else:
             bound, ach, peak, unit = "hbm", work[dom]["bytes"] / per_launch_ms / 1e6, pk["hbm"], "GB/s"
-        stages = {k: {"ms_per_launch": stage_ms[k] / stage_n[k],
-                      "GBps": work[k]["bytes"] / (stage_ms[k] / stage_n[k]) / 1e6,
-                      "TFLOPs": work[k]["flops"] / (stage_ms[k] / stage_n[k]) / 1e9} for k in stage_ms}
+        stages = {k: {"ms_per_launch": stage_ms[k], "GBps": work[k]["bytes"] / stage_ms[k] / 1e6,
+                      "TFLOPs": work[k]["flops"] / stage_ms[k] / 1e9} for k in stage_ms}
         cpu_v, cpu_per, cores, cpu_done = (None, None, None, 0)
         cpu = None
         if world == 1 and not args.no_cpu:

@@ -234,11 +234,16 @@ int launch_mat(const convnn_desc* d, const Dims& dm, const void* v, const int32_
 
 }  // namespace
 
+int try_launch_gather_conv_dw_smem(const convnn_desc* d, const Dims& dm, const void* v, const int32_t* idx,
+                                   const float* val, const void* w_conv, void* o, cudaStream_t st);
+
 int launch_gather_conv_simt(const convnn_desc* d, const Dims& dm, const void* v, const int32_t* idx,
                             const float* val, const void* w_conv, const void* w_pw, void* o,
                             cudaStream_t st) {
     const bool f32 = d->dtype == CONVNN_F32;
     if (d->conv_type == CONVNN_DEPTHWISE) {
+        const int rc = try_launch_gather_conv_dw_smem(d, dm, v, idx, val, w_conv, o, st);
+        if (rc != CONVNN_E_UNSUPPORTED) return rc;
         const int vec = f32 ? 4 : 8;
         const bool vec_ok = dm.dk % vec == 0 && dm.Cp % vec == 0 && aligned16(v) && aligned16(o) && aligned16(w_conv);
         if (f32) return vec_ok ? launch_dw<float, 4>(d, dm, v, idx, val, w_conv, o, st)
@@ -248,6 +253,126 @@ int launch_gather_conv_simt(const convnn_desc* d, const Dims& dm, const void* v,
     }
     return f32 ? launch_mat<float>(d, dm, v, idx, val, w_conv, w_pw, o, st)
                : launch_mat<__nv_bfloat16>(d, dm, v, idx, val, w_conv, w_pw, o, st);
+}
+
+}  // namespace convnn
+
+// ---- depthwise with the value rows resident in shared memory --------------------------
+// When one (batch, head) slice of V (T x d_k) fits in shared memory, a CTA copies it in
+// once with coalesced 16-byte loads and serves all K-fold neighbour reads from there, so
+// HBM and L2 see V once and o once (the compulsory traffic) instead of K gathers per token.
+// Thread layout: `groups` = d_k / VEC consecutive threads cover one token's channels, so a
+// thread's channel group is fixed and its K x VEC tap weights stay in registers (KT > 0);
+// KT == 0 is the run-time-K variant with the taps in shared memory.
+namespace convnn {
+namespace {
+
+template <typename T, int VEC, int KT>
+__global__ void __launch_bounds__(256) gather_conv_dw_smem_kernel(
+    const T* __restrict__ v, const int32_t* __restrict__ idx, const float* __restrict__ val,
+    const T* __restrict__ wconv, T* __restrict__ o, int T_, int H, int dk, int Cp, int K, int maximum,
+    int softmax, int groups, int tpp) {
+    extern __shared__ __align__(16) unsigned char dsm[];
+    T* vs = reinterpret_cast<T*>(dsm);                                   // [T][dk]
+    float* ps = reinterpret_cast<float*>(dsm + (((size_t)T_ * dk * sizeof(T) + 15) & ~(size_t)15));   // [T][K]
+    int* ns = reinterpret_cast<int*>(ps + (size_t)T_ * K);               // [T][K]
+    float* ws = reinterpret_cast<float*>(ns + (size_t)T_ * K);           // [K][dk] (KT == 0 only)
+
+    const int bh = blockIdx.x;
+    const int b = bh / H, h = bh - b * H;
+    const T* vb = v + ((long long)b * T_ * H + h) * Cp;
+    const long long tstride = (long long)H * Cp;
+    const int row_vecs = dk / VEC;
+
+    // 1. V slice -> shared memory (row-major, rows packed)
+    for (int e = threadIdx.x; e < T_ * row_vecs; e += blockDim.x) {
+        const int t = e / row_vecs, cvec = e - t * row_vecs;
+        float tmp[VEC];
+        VecLoad<T, VEC>::load(vb + t * tstride + cvec * VEC, tmp);
+        VecLoad<T, VEC>::store(vs + (size_t)t * dk + cvec * VEC, tmp);
+    }
+    // 2. neighbour lists and their weights
+    const long long nbase = (long long)bh * T_ * K;
+    for (int e = threadIdx.x; e < T_ * K; e += blockDim.x) ns[e] = idx[nbase + e];
+    for (int t = threadIdx.x; t < T_; t += blockDim.x) token_weights(val + nbase + (long long)t * K, ps + t * K, K, maximum, softmax);
+    if (KT == 0)
+        for (int e = threadIdx.x; e < K * dk; e += blockDim.x) ws[e] = to_f32<T>(wconv[e]);
+    __syncthreads();
+
+    // 3. taps
+    const int cg = threadIdx.x % groups, tl = threadIdx.x / groups;
+    if (tl >= tpp) return;
+    const int c = cg * VEC;
+    float wreg[KT > 0 ? KT : 1][VEC];
+    if (KT > 0) {
+#pragma unroll
+        for (int j = 0; j < (KT > 0 ? KT : 1); ++j) VecLoad<T, VEC>::load(wconv + j * dk + c, wreg[j]);
+    }
+    T* ob = o + (long long)bh * T_ * dk + c;
+    for (int t = tl; t < T_; t += tpp) {
+        float acc[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
+        if (KT > 0) {
+#pragma unroll
+            for (int j = 0; j < (KT > 0 ? KT : 1); ++j) {
+                float x[VEC];
+                VecLoad<T, VEC>::load(vs + (size_t)ns[t * KT + j] * dk + c, x);
+                const float pj = ps[t * KT + j];
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) acc[e] = fmaf(wreg[j][e], pj * x[e], acc[e]);
+            }
+        } else {
+            for (int j = 0; j < K; ++j) {
+                float x[VEC];
+                VecLoad<T, VEC>::load(vs + (size_t)ns[t * K + j] * dk + c, x);
+                const float pj = ps[t * K + j];
+                const float* wj = ws + j * dk + c;
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) acc[e] = fmaf(wj[e], pj * x[e], acc[e]);
+            }
+        }
+        VecLoad<T, VEC>::store(ob + (long long)t * dk, acc);
+    }
+}
+
+template <typename T, int VEC>
+int launch_dw_smem(const convnn_desc* d, const Dims& dm, const void* v, const int32_t* idx, const float* val,
+                   const void* w_conv, void* o, size_t smem, cudaStream_t st) {
+    const int groups = dm.dk / VEC;
+    const int tpp = 256 / groups;
+    const int maximum = d->metric != CONVNN_EUCLIDEAN;
+#define CONVNN_DW_LAUNCH(KT)                                                                                 \
+    do {                                                                                                     \
+        auto kern = gather_conv_dw_smem_kernel<T, VEC, KT>;                                                  \
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+        if (e != cudaSuccess) return set_error(CONVNN_E_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e)); \
+        kern<<<dm.B * dm.H, 256, smem, st>>>(static_cast<const T*>(v), idx, val, static_cast<const T*>(w_conv), \
+                                             static_cast<T*>(o), dm.T, dm.H, dm.dk, dm.Cp, dm.K, maximum,    \
+                                             d->softmax, groups, tpp);                                       \
+    } while (0)
+    if (dm.K == 9) CONVNN_DW_LAUNCH(9);
+    else CONVNN_DW_LAUNCH(0);
+#undef CONVNN_DW_LAUNCH
+    CONVNN_CHECK_LAUNCH("gather_conv_dw_smem");
+    return CONVNN_OK;
+}
+
+}  // namespace
+
+// Shared-memory-resident depthwise variant; returns CONVNN_E_UNSUPPORTED (without touching
+// last_error) when the slice does not fit or the layout is not vectorisable.
+int try_launch_gather_conv_dw_smem(const convnn_desc* d, const Dims& dm, const void* v, const int32_t* idx,
+                                   const float* val, const void* w_conv, void* o, cudaStream_t st) {
+    const bool f32 = d->dtype == CONVNN_F32;
+    const int vec = f32 ? 4 : 8;
+    if (dm.dk % vec != 0 || dm.Cp % vec != 0 || dm.dk / vec > 256 || !aligned16(v) || !aligned16(o) || !aligned16(w_conv))
+        return CONVNN_E_UNSUPPORTED;
+    size_t smem = (((size_t)dm.T * dm.dk * dm.elt + 15) & ~(size_t)15) + (size_t)dm.T * dm.K * 8;
+    if (dm.K != 9) smem += (size_t)dm.K * dm.dk * 4;
+    if (smem > 200 * 1024) return CONVNN_E_UNSUPPORTED;
+    return f32 ? launch_dw_smem<float, 4>(d, dm, v, idx, val, w_conv, o, smem, st)
+               : launch_dw_smem<__nv_bfloat16, 8>(d, dm, v, idx, val, w_conv, o, smem, st);
 }
 
 }  // namespace convnn

@@ -164,7 +164,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const int n0 = nt * p.BN;
             const int part = n0 / p.part_cols;
             const int pc0 = n0 - part * p.part_cols;          // first column inside the part
-            __nv_bfloat16* crow = p.c[part] + (long long)row * p.ldc + pc0;
+            __nv_bfloat16* cbase = part == 0 ? p.c[0] : (part == 1 ? p.c[1] : p.c[2]);
+            __nv_bfloat16* crow = cbase + (long long)row * p.ldc + pc0;
             const __nv_bfloat16* brow = p.bias ? p.bias + n0 : nullptr;
             const int ncol = min(p.BN, p.N - n0);             // valid columns of this tile
             ok = mbar_wait(&tfull[buf], u & 1u, abort_flag);

@@ -1,22 +1,25 @@
 // Similarity + streaming top-K on the 5th-generation tensor cores (bfloat16 operands).
 //
-// Work item = 128 consecutive key tokens (rows) of one (batch, head).  A persistent CTA
-// walks its items and, per item, the candidate columns in tiles of BN <= 256:
+// Work unit = 256 consecutive key tokens (two 128-row MMA tiles) of one (batch, head).
+// A persistent CTA walks its units and, per unit, the candidate columns in tiles of
+// BN <= 128:
 //
-//   warp 0   TMA producer: per 64-channel chunk, one box of K rows (128 x 64) and one box
-//            of Q rows (BN x 64) into a 4-stage shared-memory ring (128-byte swizzle),
-//            straight from the (B, tokens, H, C) tensors -- no head-split copies.
-//   warp 1   MMA issuer: tcgen05.mma kind::f16, M = 128, N = BN, fp32 accumulators in one
-//            of two TMEM buffers, so the next tile's MMAs overlap this tile's epilogue;
-//            tcgen05.commit hands the smem stage back and publishes the accumulator.
-//   warps 2-5  epilogue: each thread owns one row (= its TMEM lane), pulls 32 columns at a
-//            time with tcgen05.ld, converts dot products to ranking keys and keeps a
-//            sorted register list of the best candidates.  The T x S matrix never leaves
-//            the SM.
+//   warp 0     TMA producer: per 64-channel chunk two boxes of K rows (128 x 64 each) and
+//              ONE box of Q rows (BN x 64) shared by both row tiles, into a 3-stage ring
+//              (128-byte swizzle), straight from the (B, tokens, H, C) tensors.
+//   warp 1     MMA issuer: tcgen05.mma kind::f16, M = 128, N = BN, two accumulators per
+//              column tile (one per row tile), double-buffered in TMEM across column tiles
+//              (4 x BN columns), so the next tile's MMAs overlap this tile's epilogue.
+//   warps 2-5  epilogue of row tile 0, warps 6-9 epilogue of row tile 1: each thread owns
+//              one row (= its TMEM lane), pulls 32 columns at a time with tcgen05.ld,
+//              turns dot products into ranking keys, filters them against the worst kept
+//              key (branch-free bit mask) and inserts the survivors into a sorted
+//              register list.  The T x S matrix never leaves the SM.
 //
-// bfloat16 products are exact in fp32 and accumulation is fp32, so the selection is as
-// accurate as the SIMT float32 kernel on the same (rounded) q and k.  Every mbarrier wait
-// is bounded; on expiry the CTA records a code in the device status word and drains.
+// Survivors are inserted in ascending column order with strict comparisons, so exact ties
+// keep the lower candidate column.  bfloat16 products are exact in fp32 and accumulation
+// is fp32, so the selection is as accurate as the float32 SIMT kernel on the same q, k.
+// Every mbarrier wait is bounded; on expiry the CTA latches a code and drains.
 #include "common.cuh"
 #include "sm100.cuh"
 #include "toplist.cuh"
@@ -30,8 +33,9 @@ namespace {
 using namespace sm100;
 
 constexpr int BM = 128;
-constexpr int STAGES = 4;
-constexpr int NTHREADS = 192;
+constexpr int STAGES = 3;
+constexpr int NTHREADS = 320;     // TMA warp, MMA warp, 2 x 4 epilogue warps
+constexpr int GROUP = 128;        // threads per epilogue group
 
 struct TcParams {
     const float* qstat;
@@ -42,9 +46,9 @@ struct TcParams {
     int T, S, H, K, nsel, metric, sampled;
     int KCH;          // channels per shared-memory chunk (64, 32 or 16)
     int KC;           // chunks per tile = C / KCH
-    int BN;           // candidate columns per MMA (multiple of 16, <= 256)
-    int BNpad;        // TMEM columns per accumulator buffer (power of two >= BN)
-    int n_row_tiles, n_col_tiles, n_items;
+    int BN;           // candidate columns per MMA (multiple of 16, <= 128)
+    int BNpad;        // TMEM columns per accumulator (power of two >= BN)
+    int n_pairs, n_col_tiles, n_units;
     float sqrt_dk;
 };
 
@@ -53,22 +57,44 @@ __device__ __forceinline__ void fail(volatile int* abort_flag, int code) {
     atomicCAS(&g_sim_topk_status, 0, code);
 }
 
+// One chunk of W accumulator columns of this thread's row: keys, threshold mask, drain.
 template <int NSEL, int W>
-__device__ __forceinline__ void consume(TopList<NSEL>& top, const uint32_t (&r)[W], int col0, float qv, int cv,
-                                        const TcParams& p, int row, bool row_ok, float sentinel) {
+__device__ __forceinline__ void consume(TopList<NSEL>& top, const uint32_t (&acc)[W], int col0, float qv, int cv,
+                                        const TcParams& p, int row, bool row_ok, float sentinel, float* ks) {
+    float key[W];
 #pragma unroll
     for (int j = 0; j < W; ++j) {
-        const float dot = __uint_as_float(r[j]);
-        float key = dot;
+        const float dot = __uint_as_float(acc[j]);
+        float k = dot;
         if (p.metric != CONVNN_MATMUL) {
             const float s = __shfl_sync(0xffffffffu, qv, j);
-            key = (p.metric == CONVNN_COSINE) ? dot * s : fmaf(2.0f, dot, -s);
+            k = (p.metric == CONVNN_COSINE) ? dot * s : fmaf(2.0f, dot, -s);
         }
         if (p.sampled) {
             const int cj = __shfl_sync(0xffffffffu, cv, j);
-            if (cj == row) key = sentinel;
+            if (cj == row) k = sentinel;
         }
-        if (row_ok && (col0 + j) < p.S && key > top.worst()) top.insert(key, col0 + j);
+        key[j] = k;
+    }
+    const float thr = top.worst();
+    uint32_t mask = 0;
+#pragma unroll
+    for (int j = 0; j < W; ++j) mask |= (key[j] > thr) ? (1u << j) : 0u;
+    const int left = p.S - col0;                       // valid columns from col0 on
+    if (left < W) mask &= (left <= 0) ? 0u : ((1u << left) - 1u);
+    if (!row_ok) mask = 0;
+    if (__any_sync(0xffffffffu, mask != 0)) {
+        // keys go through shared memory so the drain loop can pick column j per lane
+#pragma unroll
+        for (int j = 0; j < W; ++j) ks[j * GROUP] = key[j];
+        while (__any_sync(0xffffffffu, mask != 0)) {
+            if (mask) {
+                const int j = __ffs(mask) - 1;
+                mask &= mask - 1;
+                const float k = ks[j * GROUP];
+                if (k > top.worst()) top.insert_sorted(k, col0 + j);
+            }
+        }
     }
 }
 
@@ -80,9 +106,10 @@ sim_topk_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t pitch = p.KCH * 2;
     const uint32_t a_bytes = BM * pitch, b_bytes = p.BN * pitch;
-    uint8_t* sA = smem;
-    uint8_t* sB = smem + STAGES * a_bytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sB + STAGES * b_bytes);
+    const uint32_t stage_bytes = 2 * a_bytes + b_bytes;
+    uint8_t* stages = smem;                                            // [STAGES][A0 | A1 | B]
+    float* keybuf = reinterpret_cast<float*>(smem + STAGES * stage_bytes);   // [2 groups][32][GROUP]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(keybuf + 2 * 32 * GROUP);
     uint64_t* full = bars;
     uint64_t* empty = bars + STAGES;
     uint64_t* tfull = bars + 2 * STAGES;
@@ -91,7 +118,7 @@ sim_topk_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t ncols = 2u * p.BNpad;
+    const uint32_t ncols = 4u * p.BNpad;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -100,7 +127,7 @@ sim_topk_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&tfull[b], 1);
-            mbar_init(&tempty[b], 4);
+            mbar_init(&tempty[b], 8);
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -120,16 +147,20 @@ sim_topk_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
-                const int bh = item / p.n_row_tiles, rt = item - bh * p.n_row_tiles;
+            for (int unit = blockIdx.x; unit < p.n_units && ok; unit += gridDim.x) {
+                const int bh = unit / p.n_pairs, pp = unit - bh * p.n_pairs;
                 const int b = bh / p.H, h = bh - b * p.H;
+                const int row0 = pp * 2 * BM;
+                const bool has1 = row0 + BM < p.T;
                 for (int ct = 0; ct < p.n_col_tiles && ok; ++ct) {
                     for (int kc = 0; kc < p.KC; ++kc, ++it) {
                         const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
                         if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) { fail(abort_flag, 1); ok = false; break; }
-                        mbar_expect_tx(&full[s], a_bytes + b_bytes);
-                        tma_load_4d(sA + s * a_bytes, &tmK, &full[s], kc * p.KCH, h, rt * BM, b);
-                        tma_load_4d(sB + s * b_bytes, &tmQ, &full[s], kc * p.KCH, h, ct * p.BN, b);
+                        uint8_t* st = stages + s * stage_bytes;
+                        mbar_expect_tx(&full[s], (has1 ? 2 : 1) * a_bytes + b_bytes);
+                        tma_load_4d(st, &tmK, &full[s], kc * p.KCH, h, row0, b);
+                        if (has1) tma_load_4d(st + a_bytes, &tmK, &full[s], kc * p.KCH, h, row0 + BM, b);
+                        tma_load_4d(st + 2 * a_bytes, &tmQ, &full[s], kc * p.KCH, h, ct * p.BN, b);
                     }
                 }
             }
@@ -139,34 +170,44 @@ sim_topk_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
             const uint32_t idesc = make_idesc_bf16_f32(BM, p.BN);
             uint32_t it = 0, tile = 0;
             bool ok = true;
-            for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
+            for (int unit = blockIdx.x; unit < p.n_units && ok; unit += gridDim.x) {
+                const int pp = unit % p.n_pairs;
+                const bool has1 = pp * 2 * BM + BM < p.T;
                 for (int ct = 0; ct < p.n_col_tiles && ok; ++ct, ++tile) {
-                    const uint32_t buf = tile & 1u, u = tile >> 1;
-                    if (!mbar_wait(&tempty[buf], (u & 1u) ^ 1u, abort_flag)) { fail(abort_flag, 2); ok = false; break; }
+                    const uint32_t par = tile & 1u, u = tile >> 1;
+                    if (!mbar_wait(&tempty[par], (u & 1u) ^ 1u, abort_flag)) { fail(abort_flag, 2); ok = false; break; }
                     tc_fence_after_sync();
-                    const uint32_t d_tmem = tmem_base + buf * p.BNpad;
+                    const uint32_t d0 = tmem_base + (0 * 2 + par) * p.BNpad;
+                    const uint32_t d1 = tmem_base + (1 * 2 + par) * p.BNpad;
                     for (int kc = 0; kc < p.KC; ++kc, ++it) {
                         const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
                         if (!mbar_wait(&full[s], ph, abort_flag)) { fail(abort_flag, 3); ok = false; break; }
                         tc_fence_after_sync();
-                        const uint64_t adesc = make_kmajor_desc(smem_u32(sA + s * a_bytes), pitch);
-                        const uint64_t bdesc = make_kmajor_desc(smem_u32(sB + s * b_bytes), pitch);
+                        const uint32_t sa = smem_u32(stages + s * stage_bytes);
+                        const uint64_t a0 = make_kmajor_desc(sa, pitch);
+                        const uint64_t a1 = make_kmajor_desc(sa + a_bytes, pitch);
+                        const uint64_t bd = make_kmajor_desc(sa + 2 * a_bytes, pitch);
                         for (int k16 = 0; k16 < p.KCH / 16; ++k16)
-                            mma_bf16_ss(d_tmem, adesc + 2u * k16, bdesc + 2u * k16, idesc, (kc | k16) != 0);
+                            mma_bf16_ss(d0, a0 + 2u * k16, bd + 2u * k16, idesc, (kc | k16) != 0);
+                        if (has1)
+                            for (int k16 = 0; k16 < p.KCH / 16; ++k16)
+                                mma_bf16_ss(d1, a1 + 2u * k16, bd + 2u * k16, idesc, (kc | k16) != 0);
                         mma_commit(&empty[s]);
                     }
-                    if (ok) mma_commit(&tfull[buf]);
+                    if (ok) mma_commit(&tfull[par]);
                 }
             }
         }
     } else {
+        const int grp = (warp - 2) >> 2;         // which row tile of the pair this warp serves
         const int lq = warp & 3;                 // TMEM lane quarter this warp may read
         const int r = lq * 32 + lane;            // row within the tile
+        float* ks = keybuf + grp * 32 * GROUP + r;
         uint32_t tile = 0;
         bool ok = true;
-        for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
-            const int bh = item / p.n_row_tiles, rt = item - bh * p.n_row_tiles;
-            const int row = rt * BM + r;
+        for (int unit = blockIdx.x; unit < p.n_units && ok; unit += gridDim.x) {
+            const int bh = unit / p.n_pairs, pp = unit - bh * p.n_pairs;
+            const int row = pp * 2 * BM + grp * BM + r;
             const bool row_ok = row < p.T;
             const float* qs_row = p.qstat ? p.qstat + (long long)bh * p.S : nullptr;
             float kst = 1.0f;
@@ -180,36 +221,40 @@ sim_topk_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
             TopList<NSEL> top;
             top.init();
             for (int ct = 0; ct < p.n_col_tiles && ok; ++ct, ++tile) {
-                const uint32_t buf = tile & 1u, u = tile >> 1;
-                ok = mbar_wait(&tfull[buf], u & 1u, abort_flag);
+                const uint32_t par = tile & 1u, u = tile >> 1;
+                // column statistics of this tile, fetched before the accumulator is awaited
+                float qv[4];
+                int cv[4];
+#pragma unroll
+                for (int c4 = 0; c4 < 4; ++c4) {
+                    const int cl = min(ct * p.BN + c4 * 32 + lane, p.S - 1);
+                    qv[c4] = (p.metric != CONVNN_MATMUL && c4 * 32 < p.BN) ? qs_row[cl] : 0.f;
+                    cv[c4] = (p.sampled && c4 * 32 < p.BN) ? p.cand[cl] : -1;
+                }
+                ok = mbar_wait(&tfull[par], u & 1u, abort_flag);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) { if (lane == 0) fail(abort_flag, 4); break; }
                 tc_fence_after_sync();
-                const uint32_t taddr = tmem_base + ((uint32_t)(lq * 32) << 16) + buf * p.BNpad;
-                int c = 0;
-                for (; c + 32 <= p.BN; c += 32) {
+                const uint32_t taddr = tmem_base + ((uint32_t)(lq * 32) << 16) + (grp * 2 + par) * p.BNpad;
+#pragma unroll
+                for (int c4 = 0; c4 < 4; ++c4) {
+                    const int c = c4 * 32;
                     const int col0 = ct * p.BN + c;
-                    const int cl = min(col0 + lane, p.S - 1);
-                    const float qv = (p.metric != CONVNN_MATMUL) ? qs_row[cl] : 0.f;
-                    const int cv = p.sampled ? p.cand[cl] : -1;
-                    uint32_t acc[32];
-                    tmem_ld_x32(taddr + c, acc);
-                    tmem_ld_wait();
-                    consume<NSEL, 32>(top, acc, col0, qv, cv, p, row, row_ok, sentinel);
-                }
-                if (c < p.BN) {
-                    const int col0 = ct * p.BN + c;
-                    const int cl = min(col0 + (lane & 15), p.S - 1);
-                    const float qv = (p.metric != CONVNN_MATMUL) ? qs_row[cl] : 0.f;
-                    const int cv = p.sampled ? p.cand[cl] : -1;
-                    uint32_t acc[16];
-                    tmem_ld_x16(taddr + c, acc);
-                    tmem_ld_wait();
-                    consume<NSEL, 16>(top, acc, col0, qv, cv, p, row, row_ok, sentinel);
+                    if (c + 32 <= p.BN) {
+                        uint32_t acc[32];
+                        tmem_ld_x32(taddr + c, acc);
+                        tmem_ld_wait();
+                        consume<NSEL, 32>(top, acc, col0, qv[c4], cv[c4], p, row, row_ok, sentinel, ks);
+                    } else if (c < p.BN) {
+                        uint32_t acc[16];
+                        tmem_ld_x16(taddr + c, acc);
+                        tmem_ld_wait();
+                        consume<NSEL, 16>(top, acc, col0, qv[c4], cv[c4], p, row, row_ok, sentinel, ks);
+                    }
                 }
                 tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&tempty[buf]);
+                if (lane == 0) mbar_arrive(&tempty[par]);
             }
             if (ok && row_ok) {
                 const long long obase = ((long long)bh * p.T + row) * p.K;
@@ -274,12 +319,12 @@ int launch_sim_topk_tc(const convnn_desc* d, const Dims& dm, const void* q, cons
     p.T = dm.T; p.S = dm.S; p.H = dm.H; p.K = dm.K; p.nsel = dm.nsel; p.metric = d->metric; p.sampled = d->sampled;
     p.KCH = dm.Cp % 64 == 0 ? 64 : (dm.Cp % 32 == 0 ? 32 : 16);
     p.KC = dm.Cp / p.KCH;
-    const int ntile = (dm.S + 255) / 256;
+    const int ntile = (dm.S + 127) / 128;
     p.BN = (((dm.S + ntile - 1) / ntile) + 15) / 16 * 16;
     p.BNpad = pow2_at_least(p.BN, 32);
-    p.n_row_tiles = (dm.T + BM - 1) / BM;
+    p.n_pairs = (dm.T + 2 * BM - 1) / (2 * BM);
     p.n_col_tiles = (dm.S + p.BN - 1) / p.BN;
-    p.n_items = dm.B * dm.H * p.n_row_tiles;
+    p.n_units = dm.B * dm.H * p.n_pairs;
     p.sqrt_dk = (float)sqrt((double)dm.dk);
 
     const int pitch = p.KCH * 2;
@@ -293,11 +338,12 @@ int launch_sim_topk_tc(const convnn_desc* d, const Dims& dm, const void* q, cons
     if (!encode_tensor_map_bf16(&tmK, k, 4, dimsK, strK, boxK, pitch)) return CONVNN_E_CUDA;
     if (!encode_tensor_map_bf16(&tmQ, q, 4, dimsQ, strQ, boxQ, pitch)) return CONVNN_E_CUDA;
 
-    const size_t smem = 1024 + (size_t)STAGES * (BM + p.BN) * pitch + (2 * STAGES + 4) * 8 + 16;
+    const size_t smem = 1024 + (size_t)STAGES * (2 * BM + p.BN) * pitch + 2 * 32 * GROUP * sizeof(float) +
+                        (2 * STAGES + 4) * 8 + 16;
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const int grid = p.n_items < sms ? p.n_items : sms;
+    const int grid = p.n_units < sms ? p.n_units : sms;
 
 #define CONVNN_TC_LAUNCH(N)                                                                            \
     do {                                                                                               \

@@ -34,6 +34,22 @@ struct TopList {
             i[s - 1] = hi; i[s] = li;
         }
     }
+
+    // Same result as insert() for any key (no precondition), written so that every slot is
+    // computed from the OLD neighbours with independent compare/select pairs: no serial
+    // dependency chain through the list, which matters when one warp per scheduler runs it.
+    __device__ __forceinline__ void insert_sorted(float key, int col) {
+#pragma unroll
+        for (int s = N - 1; s >= 1; --s) {
+            const bool gt = key > v[s];
+            const bool gtp = key > v[s - 1];
+            v[s] = gt ? (gtp ? v[s - 1] : key) : v[s];
+            i[s] = gt ? (gtp ? i[s - 1] : col) : i[s];
+        }
+        const bool g0 = key > v[0];
+        v[0] = g0 ? key : v[0];
+        i[0] = g0 ? col : i[0];
+    }
 };
 
 }  // namespace convnn
