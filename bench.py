@@ -211,6 +211,41 @@ def stage_profile(model, B, cfg, dev, sets=4, reps=5):
     return out
 
 
+def run_single_stage(args) -> int:
+    """Launch one stage of the layer a few times at the bench shape (for ncu captures and
+    quick timing): python bench.py --stage sim_topk [--stage-batch 64] [--stage-iters 3]."""
+    import convnn_b200
+    from convnn_b200 import ops
+    from oracle.vit_oracle import ViTConfig
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    cfg = ViTConfig(**WORKLOAD)
+    B, T, D = args.stage_batch, cfg.seq_len, cfg.d_hidden
+    layer = convnn_b200.MultiHeadConvNNAttention(D, cfg.num_heads, 0.0, cfg.K, cfg.sampling_type, cfg.num_samples,
+                                                 cfg.sample_padding, cfg.magnitude_type).eval().to(dev, torch.bfloat16)
+    spec = layer._spec()
+    w_qkv, w_conv, w_pw, w_o = layer.packed_weights(torch.bfloat16, dev)
+    x = torch.randn(B, T, D, device=dev).to(torch.bfloat16)
+    q, k, v, qs, ks = ops.qkv_proj(spec, x, w_qkv)
+    idx, val = ops.sim_topk(spec, q, k, qs, ks)
+    o = ops.gather_conv(spec, v, idx, val, w_conv, w_pw)
+    fns = {"qkv_proj": lambda: ops.qkv_proj(spec, x, w_qkv),
+           "sim_topk": lambda: ops.sim_topk(spec, q, k, qs, ks),
+           "gather_conv": lambda: ops.gather_conv(spec, v, idx, val, w_conv, w_pw),
+           "out_proj": lambda: ops.out_proj(spec, o, w_o)}
+    fn = fns[args.stage]
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.stage_iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    print(json.dumps({"stage": args.stage, "batch": B, "iters": args.stage_iters,
+                      "ms_per_call_incl_host": e0.elapsed_time(e1) / args.stage_iters}))
+    return 0
+
+
 def algorithmic_work(B, T, S, D, H, K, elt=2):
     """Compulsory bytes / flops per launch of each stage (one layer call)."""
     idxval = 8 * B * H * T * K
@@ -401,7 +436,13 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--stage", choices=["qkv_proj", "sim_topk", "gather_conv", "out_proj"],
+                    help="run only this stage of one layer (profiling aid)")
+    ap.add_argument("--stage-batch", type=int, default=BATCH_PER_GPU)
+    ap.add_argument("--stage-iters", type=int, default=3)
     args = ap.parse_args()
+    if args.stage:
+        return run_single_stage(args)
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         return run_reference_arm(args)

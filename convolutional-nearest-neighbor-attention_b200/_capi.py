@@ -44,10 +44,17 @@ SIGNATURES = {
                                             c_void, c_void, c_void]),
     "convnn_b200_gather_conv": (ctypes.c_int, [ctypes.POINTER(ConvnnDesc), c_void, c_void, c_void, c_void, c_void,
                                                c_void, c_void]),
-    "convnn_b200_out_proj": (ctypes.c_int, [ctypes.POINTER(ConvnnDesc), c_void, c_void, c_void, c_i64, c_void,
-                                            c_void]),
+    "convnn_b200_out_proj": (ctypes.c_int, [ctypes.POINTER(ConvnnDesc), c_void, c_void, c_void, c_i64, c_void, c_i64,
+                                            c_void, c_void]),
     "convnn_b200_forward": (ctypes.c_int, [ctypes.POINTER(ConvnnDesc), c_void, c_i64, c_void, c_void, c_void, c_void,
-                                           c_void, c_void, c_i64, c_void, c_size, c_void]),
+                                           c_void, c_void, c_i64, c_void, c_i64, c_void, c_size, c_void]),
+    "convnn_b200_layernorm": (ctypes.c_int, [ctypes.c_int, c_void, c_i64, c_void, c_void, ctypes.c_float, c_void,
+                                             c_i64, c_i64, c_i32, c_void]),
+    "convnn_b200_linear": (ctypes.c_int, [ctypes.c_int, c_void, c_i64, c_void, c_void, c_void, c_i64, c_void, c_i64,
+                                          c_i64, c_i32, c_i32, c_i32, c_void]),
+    "convnn_b200_patchify": (ctypes.c_int, [ctypes.c_int, c_void, c_void, c_i32, c_i32, c_i32, c_i32, c_i32, c_void]),
+    "convnn_b200_embed_tokens": (ctypes.c_int, [ctypes.c_int, c_void, c_void, c_void, ctypes.c_float, c_void, c_void,
+                                                c_void, c_i32, c_i32, c_i32, c_void]),
 }
 
 _lock = threading.Lock()

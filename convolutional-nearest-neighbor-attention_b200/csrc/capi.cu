@@ -193,21 +193,30 @@ int convnn_b200_qkv_proj(const convnn_desc* d, const void* x, int64_t ldx, const
     if (d->dtype == CONVNN_BF16 && !d->coord && !force_simt()) {
         const char* wb = static_cast<const char*>(w_qkv);
         void* kvq[3] = {k, v, q};
+        const bool fuse = stats && gemm_tc_can_fuse_stats(dm.D, dm.dk);
+        GemmTcOpts o;
+        o.stat_mode = d->metric; o.dk = dm.dk; o.heads = dm.H;
         bool done = false;
         if (!d->sampled && gemm_tc_supported(x, ldx, w_qkv, dm.D, 3 * dm.D, 3, kvq, dm.D)) {
-            if ((rc = launch_gemm_tc(x, ldx, w_qkv, nullptr, dm.B * dm.T, 3 * dm.D, dm.D, 3, kvq, dm.D, 0, st))) return rc;
+            if (fuse) { o.stat[0] = kstat; o.stat[2] = qstat; o.rows_per_batch = dm.T; }
+            if ((rc = launch_gemm_tc(x, ldx, w_qkv, dm.B * dm.T, 3 * dm.D, dm.D, 3, kvq, dm.D, o, st))) return rc;
             done = true;
         } else if (d->sampled && scratch && gemm_tc_supported(x, ldx, w_qkv, dm.D, 2 * dm.D, 2, kvq, dm.D) &&
                    gemm_tc_supported(scratch, dm.D, wb + 2 * wsz, dm.D, dm.D, 1, &kvq[2], dm.D)) {
-            if ((rc = launch_gemm_tc(x, ldx, w_qkv, nullptr, dm.B * dm.T, 2 * dm.D, dm.D, 2, kvq, dm.D, 0, st))) return rc;
+            if (fuse) { o.stat[0] = kstat; o.rows_per_batch = dm.T; }
+            if ((rc = launch_gemm_tc(x, ldx, w_qkv, dm.B * dm.T, 2 * dm.D, dm.D, 2, kvq, dm.D, o, st))) return rc;
             if ((rc = launch_gather_rows(d->dtype, x, ldx, cand, scratch, dm.B, dm.T, dm.S, dm.D, st))) return rc;
-            if ((rc = launch_gemm_tc(scratch, dm.D, wb + 2 * wsz, nullptr, dm.B * dm.S, dm.D, dm.D, 1, &kvq[2], dm.D, 0, st)))
+            GemmTcOpts oq;
+            oq.stat_mode = d->metric; oq.dk = dm.dk; oq.heads = dm.H;
+            if (fuse) { oq.stat[0] = qstat; oq.rows_per_batch = dm.S; }
+            if ((rc = launch_gemm_tc(scratch, dm.D, wb + 2 * wsz, dm.B * dm.S, dm.D, dm.D, 1, &kvq[2], dm.D, oq, st)))
                 return rc;
             done = true;
         }
         if (done) {
-            if ((rc = launch_head_fill_and_stats(d, dm, q, dm.S, stats ? qstat : nullptr, st))) return rc;
-            return launch_head_fill_and_stats(d, dm, k, dm.T, stats ? kstat : nullptr, st);
+            if (fuse || !stats) return CONVNN_OK;
+            if ((rc = launch_head_fill_and_stats(d, dm, q, dm.S, qstat, st))) return rc;
+            return launch_head_fill_and_stats(d, dm, k, dm.T, kstat, st);
         }
     }
     GemmParams p{};
@@ -256,22 +265,26 @@ int convnn_b200_gather_conv(const convnn_desc* d, const void* v, const int32_t* 
     return launch_gather_conv_simt(d, dm, v, idx, val, w_conv, w_pw, o, static_cast<cudaStream_t>(stream));
 }
 
-int convnn_b200_out_proj(const convnn_desc* d, const void* o, const void* w_o, void* out, int64_t ldo,
-                         void* scratch, void* stream) {
+int convnn_b200_out_proj(const convnn_desc* d, const void* o, const void* w_o, const void* residual, int64_t ldr,
+                         void* out, int64_t ldo, void* scratch, void* stream) {
     Dims dm;
     int rc = validate(d, &dm);
     if (rc) return rc;
     REQUIRE_PTR(o); REQUIRE_PTR(w_o); REQUIRE_PTR(out);
+    if (residual && ldr < dm.D) return set_error(CONVNN_E_INVALID, "ldr=%lld is smaller than D=%d", (long long)ldr, dm.D);
     if (ldo < dm.D) return set_error(CONVNN_E_INVALID, "ldo=%lld is smaller than D=%d", (long long)ldo, dm.D);
     if ((rc = check_device())) return rc;
     if (d->dtype == CONVNN_BF16 && !force_simt()) {
         cudaStream_t st = static_cast<cudaStream_t>(stream);
         void* cs[1] = {out};
-        if (dm.H == 1 && gemm_tc_supported(o, dm.D, w_o, dm.D, dm.D, 1, cs, ldo))
-            return launch_gemm_tc(o, dm.D, w_o, nullptr, dm.B * dm.T, dm.D, dm.D, 1, cs, ldo, 0, st);
-        if (dm.H > 1 && scratch && gemm_tc_supported(scratch, dm.D, w_o, dm.D, dm.D, 1, cs, ldo)) {
+        GemmTcOpts go;
+        go.residual = residual; go.ldr = ldr;
+        const bool res_ok = !residual || (ldr % 8 == 0 && aligned16(residual));
+        if (res_ok && dm.H == 1 && gemm_tc_supported(o, dm.D, w_o, dm.D, dm.D, 1, cs, ldo))
+            return launch_gemm_tc(o, dm.D, w_o, dm.B * dm.T, dm.D, dm.D, 1, cs, ldo, go, st);
+        if (res_ok && dm.H > 1 && scratch && gemm_tc_supported(scratch, dm.D, w_o, dm.D, dm.D, 1, cs, ldo)) {
             if ((rc = launch_merge_heads(d->dtype, o, scratch, dm.B, dm.T, dm.H, dm.dk, st))) return rc;
-            return launch_gemm_tc(scratch, dm.D, w_o, nullptr, dm.B * dm.T, dm.D, dm.D, 1, cs, ldo, 0, st);
+            return launch_gemm_tc(scratch, dm.D, w_o, dm.B * dm.T, dm.D, dm.D, 1, cs, ldo, go, st);
         }
     }
     GemmParams p{};
@@ -279,12 +292,14 @@ int convnn_b200_out_proj(const convnn_desc* d, const void* o, const void* w_o, v
     p.lda = dm.D; p.ldc = ldo; p.M = dm.B * dm.T; p.N = dm.D; p.Kd = dm.D;
     p.a_mode = dm.H == 1 ? A_ROWS : A_HEAD_QUIRK; p.c_mode = C_ROWS;
     p.rows_per_batch = dm.T; p.T = dm.T; p.H = dm.H; p.dk = dm.dk; p.Cp = dm.Cp; p.gelu = 0;
+    p.residual = residual; p.ldr = ldr;
     return launch_gemm_simt(d->dtype, p, static_cast<cudaStream_t>(stream));
 }
 
 int convnn_b200_forward(const convnn_desc* d, const void* x, int64_t ldx, const void* w_qkv,
                         const void* w_conv, const void* w_pw, const void* w_o, const int32_t* cand,
-                        void* out, int64_t ldo, void* workspace, size_t workspace_bytes, void* stream) {
+                        const void* residual, int64_t ldr, void* out, int64_t ldo, void* workspace,
+                        size_t workspace_bytes, void* stream) {
     Dims dm;
     int rc = validate(d, &dm);
     if (rc) return rc;
@@ -296,7 +311,69 @@ int convnn_b200_forward(const convnn_desc* d, const void* x, int64_t ldx, const 
     if ((rc = convnn_b200_qkv_proj(d, x, ldx, w_qkv, cand, w.q, w.k, w.v, w.qstat, w.kstat, w.scratch, stream))) return rc;
     if ((rc = convnn_b200_sim_topk(d, w.q, w.k, w.qstat, w.kstat, cand, w.idx, w.val, stream))) return rc;
     if ((rc = convnn_b200_gather_conv(d, w.v, w.idx, w.val, w_conv, w_pw, w.o, stream))) return rc;
-    return convnn_b200_out_proj(d, w.o, w_o, out, ldo, w.scratch, stream);
+    return convnn_b200_out_proj(d, w.o, w_o, residual, ldr, out, ldo, w.scratch, stream);
+}
+
+int convnn_b200_layernorm(int dtype, const void* x, int64_t ldx, const void* gamma, const void* beta, float eps,
+                          void* y, int64_t ldy, int64_t rows, int32_t D, void* stream) {
+    if (dtype != CONVNN_F32 && dtype != CONVNN_BF16) return set_error(CONVNN_E_INVALID, "unknown dtype %d", dtype);
+    REQUIRE_PTR(x); REQUIRE_PTR(gamma); REQUIRE_PTR(beta); REQUIRE_PTR(y);
+    if (rows < 0 || D < 1 || ldx < D || ldy < D) return set_error(CONVNN_E_INVALID, "layernorm: bad shape");
+    int rc = check_device();
+    if (rc) return rc;
+    if (rows == 0) return CONVNN_OK;
+    return launch_layernorm(dtype, x, ldx, gamma, beta, eps, y, ldy, rows, D, nullptr, nullptr, 0, 0,
+                            static_cast<cudaStream_t>(stream));
+}
+
+int convnn_b200_embed_tokens(int dtype, const void* proj, const void* gamma, const void* beta, float eps,
+                             const void* cls, const void* pe, void* out, int32_t B, int32_t Np, int32_t D,
+                             void* stream) {
+    if (dtype != CONVNN_F32 && dtype != CONVNN_BF16) return set_error(CONVNN_E_INVALID, "unknown dtype %d", dtype);
+    REQUIRE_PTR(proj); REQUIRE_PTR(gamma); REQUIRE_PTR(beta); REQUIRE_PTR(cls); REQUIRE_PTR(pe); REQUIRE_PTR(out);
+    if (B < 1 || Np < 1 || D < 1) return set_error(CONVNN_E_INVALID, "embed_tokens: bad shape");
+    int rc = check_device();
+    if (rc) return rc;
+    return launch_layernorm(dtype, proj, D, gamma, beta, eps, out, D, (long long)B * Np, D, pe, cls, Np, B,
+                            static_cast<cudaStream_t>(stream));
+}
+
+int convnn_b200_patchify(int dtype, const void* img, void* out, int32_t B, int32_t C, int32_t Hh, int32_t Ww,
+                         int32_t P, void* stream) {
+    if (dtype != CONVNN_F32 && dtype != CONVNN_BF16) return set_error(CONVNN_E_INVALID, "unknown dtype %d", dtype);
+    REQUIRE_PTR(img); REQUIRE_PTR(out);
+    if (B < 1 || C < 1 || Hh < 1 || Ww < 1 || P < 1) return set_error(CONVNN_E_INVALID, "patchify: bad shape");
+    int rc = check_device();
+    if (rc) return rc;
+    return launch_patchify(dtype, img, out, B, C, Hh, Ww, P, static_cast<cudaStream_t>(stream));
+}
+
+int convnn_b200_linear(int dtype, const void* a, int64_t lda, const void* w, const void* bias, const void* residual,
+                       int64_t ldr, void* out, int64_t ldo, int64_t M, int32_t N, int32_t K, int32_t gelu,
+                       void* stream) {
+    if (dtype != CONVNN_F32 && dtype != CONVNN_BF16) return set_error(CONVNN_E_INVALID, "unknown dtype %d", dtype);
+    REQUIRE_PTR(a); REQUIRE_PTR(w); REQUIRE_PTR(out);
+    if (M < 0 || N < 1 || K < 1 || lda < K || ldo < N || (residual && ldr < N) || M >= (1ll << 31))
+        return set_error(CONVNN_E_INVALID, "linear: bad shape (M=%lld N=%d K=%d)", (long long)M, N, K);
+    int rc = check_device();
+    if (rc) return rc;
+    if (M == 0) return CONVNN_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == CONVNN_BF16 && !force_simt()) {
+        void* cs[1] = {out};
+        const bool extra_ok = (!bias || aligned16(bias)) && (!residual || (aligned16(residual) && ldr % 8 == 0));
+        if (extra_ok && gemm_tc_supported(a, lda, w, K, N, 1, cs, ldo)) {
+            GemmTcOpts o;
+            o.bias = bias; o.residual = residual; o.ldr = ldr; o.gelu = gelu;
+            return launch_gemm_tc(a, lda, w, (int)M, N, K, 1, cs, ldo, o, st);
+        }
+    }
+    GemmParams p{};
+    p.a = a; p.w = w; p.bias = bias; p.c = out; p.cand = nullptr;
+    p.lda = lda; p.ldc = ldo; p.M = (int)M; p.N = N; p.Kd = K;
+    p.a_mode = A_ROWS; p.c_mode = C_ROWS; p.rows_per_batch = 1; p.T = 1; p.H = 1; p.dk = N; p.Cp = N;
+    p.gelu = gelu; p.residual = residual; p.ldr = ldr;
+    return launch_gemm_simt(dtype, p, st);
 }
 
 }  // extern "C"

@@ -73,6 +73,8 @@ struct GemmParams {
     int rows_per_batch;   // A_TOKENS: rows per batch item (T or S); A_HEAD_QUIRK: T
     int T, H, dk, Cp;     // geometry for A_TOKENS / A_HEAD_QUIRK / C_HEADS
     int gelu;             // apply exact GELU after bias
+    const void* residual; // (M, N) with row stride ldr, added after rounding to dtype; or nullptr
+    long long ldr;
 };
 
 int launch_gemm_simt(int dtype, const GemmParams& p, cudaStream_t st);
@@ -93,8 +95,21 @@ int read_gemm_tc_status(int* out);
 // bfloat16 tensor-core GEMM C = A W^T (+bias, +GELU); `parts` outputs share M and split N evenly.
 bool gemm_tc_supported(const void* a, long long lda, const void* w, int Kd, int N, int parts, const void* const* c,
                        long long ldc);
-int launch_gemm_tc(const void* a, long long lda, const void* w, const void* bias, int M, int N, int Kd, int parts,
-                   void* const* c, long long ldc, int gelu, cudaStream_t st);
+struct GemmTcOpts {
+    const void* bias = nullptr;       // (N) bf16
+    const void* residual = nullptr;   // (M, N) bf16 with row stride ldr, added after rounding
+    long long ldr = 0;
+    int gelu = 0;
+    float* stat[3] = {nullptr, nullptr, nullptr};   // per part: fused per-(row, head) statistic
+    int stat_mode = 0, dk = 0, heads = 1, rows_per_batch = 1;
+};
+bool gemm_tc_can_fuse_stats(int part_cols, int dk);
+int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, int Kd, int parts, void* const* c,
+                   long long ldc, const GemmTcOpts& o, cudaStream_t st);
+int launch_layernorm(int dtype, const void* x, long long ldx, const void* gamma, const void* beta, float eps, void* y,
+                     long long ldy, long long rows, int D, const void* pe, const void* cls, int Np,
+                     long long cls_rows, cudaStream_t st);
+int launch_patchify(int dtype, const void* img, void* out, int B, int C, int Hh, int Ww, int P, cudaStream_t st);
 int launch_gather_rows(int dtype, const void* x, long long ldx, const int32_t* cand, void* xq, int B, int Tn, int S,
                        int D, cudaStream_t st);
 int launch_merge_heads(int dtype, const void* o, void* y, int B, int Tn, int H, int dk, cudaStream_t st);

@@ -1,0 +1,196 @@
+// Memory-bound pieces of the ViT encoder around the ConvNN block (callers of the hot
+// path): LayerNorm, patch unfolding and the token-embedding tail.  One warp per row,
+// 16-byte loads and stores, statistics in fp32, one rounding to the storage type at each
+// point where the reference's eager ops would round (reference vit.py:100-135, 247-270).
+#include "common.cuh"
+
+namespace convnn {
+namespace {
+
+template <typename T> struct Vec16 { static constexpr int N = 16 / sizeof(T); };
+
+template <typename T>
+__device__ __forceinline__ void load_vec(const T* p, float* out) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int j = 0; j < Vec16<T>::N; ++j) out[j] = to_f32<T>(e[j]);
+}
+template <typename T>
+__device__ __forceinline__ void store_vec(T* p, const float* in) {
+    uint4 raw;
+    T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+    for (int j = 0; j < Vec16<T>::N; ++j) e[j] = from_f32<T>(in[j]);
+    *reinterpret_cast<uint4*>(p) = raw;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// LayerNorm of `rows` rows of length D.  NV = 16-byte vectors held per lane (row cached in
+// registers).  Output row r goes to y + out_row(r) * ldy; with `pe` != nullptr the kernel
+// is the embedding tail: row r = (b, n) of the patch projection lands at token 1 + n of
+// image b with pe[1 + n] added after rounding, and `cls_rows` extra rows write cls + pe[0].
+template <typename T, int NV>
+__global__ void __launch_bounds__(256) layernorm_kernel(const T* __restrict__ x, long long ldx,
+                                                        const T* __restrict__ gamma, const T* __restrict__ beta,
+                                                        float eps, T* __restrict__ y, long long ldy, long long rows,
+                                                        int D, const T* __restrict__ pe, const T* __restrict__ cls,
+                                                        int Np, long long cls_rows) {
+    constexpr int V = Vec16<T>::N;
+    const int lane = threadIdx.x & 31;
+    const long long wpb = blockDim.x >> 5;
+    const int nvec = D / V;
+    for (long long r = blockIdx.x * wpb + (threadIdx.x >> 5); r < rows + cls_rows; r += (long long)gridDim.x * wpb) {
+        if (r >= rows) {                       // class-token row of image b: cls + pe[0]
+            const long long b = r - rows;
+            T* out = y + b * (Np + 1) * ldy;
+            for (int i = lane; i < nvec; i += 32) {
+                float c[V], p0[V];
+                load_vec<T>(cls + i * V, c);
+                load_vec<T>(pe + i * V, p0);
+#pragma unroll
+                for (int j = 0; j < V; ++j) c[j] += p0[j];
+                store_vec<T>(out + i * V, c);
+            }
+            continue;
+        }
+        const T* in = x + r * ldx;
+        float v[NV][V];
+        float s = 0.f;
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+            const int i = lane + 32 * k;
+            if (i < nvec) {
+                load_vec<T>(in + i * V, v[k]);
+#pragma unroll
+                for (int j = 0; j < V; ++j) s += v[k][j];
+            }
+        }
+        const float mean = warp_sum(s) / (float)D;
+        float q = 0.f;
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+            const int i = lane + 32 * k;
+            if (i < nvec) {
+#pragma unroll
+                for (int j = 0; j < V; ++j) {
+                    const float d = v[k][j] - mean;
+                    q = fmaf(d, d, q);
+                }
+            }
+        }
+        const float rstd = rsqrtf(warp_sum(q) / (float)D + eps);
+        long long orow = r;
+        const T* perow = nullptr;
+        if (pe) {
+            const long long b = r / Np, n = r - b * Np;
+            orow = b * (Np + 1) + 1 + n;
+            perow = pe + (1 + n) * (long long)D;
+        }
+        T* out = y + orow * ldy;
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+            const int i = lane + 32 * k;
+            if (i < nvec) {
+                float g[V], bt[V], o[V];
+                load_vec<T>(gamma + i * V, g);
+                load_vec<T>(beta + i * V, bt);
+#pragma unroll
+                for (int j = 0; j < V; ++j) o[j] = (v[k][j] - mean) * rstd * g[j] + bt[j];
+                if (perow) {
+                    float pv[V];
+                    load_vec<T>(perow + i * V, pv);
+#pragma unroll
+                    for (int j = 0; j < V; ++j) o[j] = to_f32<T>(from_f32<T>(o[j])) + pv[j];
+                }
+                store_vec<T>(out + i * V, o);
+            }
+        }
+    }
+}
+
+// rows (b, py, px) x columns (c, i, j) <- img[b, c, py*P + i, px*P + j]: the unfold that
+// turns Conv2d(kernel = stride = P) into a GEMM with the (D, C*P*P) weight view.
+template <typename T>
+__global__ void patchify_kernel(const T* __restrict__ img, T* __restrict__ out, int B, int C, int Hh, int Ww, int P,
+                                long long total_vec) {
+    constexpr int V = Vec16<T>::N;
+    const int vec_per_prow = P / V;                  // vectors per patch row
+    const int Wp = Ww / P, Hp = Hh / P;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total_vec;
+         e += (long long)gridDim.x * blockDim.x) {
+        long long t = e;
+        const int jv = (int)(t % vec_per_prow); t /= vec_per_prow;
+        const int i = (int)(t % P); t /= P;
+        const int c = (int)(t % C); t /= C;
+        const int px = (int)(t % Wp); t /= Wp;
+        const int py = (int)(t % Hp); t /= Hp;
+        const long long b = t;
+        const T* src = img + (((b * C + c) * Hh + (py * P + i)) * (long long)Ww + px * P + jv * V);
+        T* dst = out + ((b * Hp + py) * Wp + px) * (long long)(C * P * P) + (c * P + i) * P + jv * V;
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+    }
+}
+
+template <typename T>
+int ln_dispatch(const void* x, long long ldx, const void* gamma, const void* beta, float eps, void* y, long long ldy,
+                long long rows, int D, const void* pe, const void* cls, int Np, long long cls_rows, cudaStream_t st) {
+    constexpr int V = Vec16<T>::N;
+    const int nvec = D / V;
+    const int nv = (nvec + 31) / 32;
+    long long total = rows + cls_rows;
+    int blocks = (int)((total + 7) / 8);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks < 1) blocks = 1;
+#define CONVNN_LN(NVV)                                                                                          \
+    layernorm_kernel<T, NVV><<<blocks, 256, 0, st>>>(static_cast<const T*>(x), ldx, static_cast<const T*>(gamma), \
+        static_cast<const T*>(beta), eps, static_cast<T*>(y), ldy, rows, D, static_cast<const T*>(pe),          \
+        static_cast<const T*>(cls), Np, cls_rows)
+    if (nv <= 1) CONVNN_LN(1);
+    else if (nv <= 2) CONVNN_LN(2);
+    else if (nv <= 4) CONVNN_LN(4);
+    else if (nv <= 8) CONVNN_LN(8);
+    else return set_error(CONVNN_E_UNSUPPORTED, "layernorm: D=%d is larger than this build supports", D);
+#undef CONVNN_LN
+    CONVNN_CHECK_LAUNCH("layernorm");
+    return CONVNN_OK;
+}
+
+}  // namespace
+
+int launch_layernorm(int dtype, const void* x, long long ldx, const void* gamma, const void* beta, float eps, void* y,
+                     long long ldy, long long rows, int D, const void* pe, const void* cls, int Np,
+                     long long cls_rows, cudaStream_t st) {
+    const int V = dtype == CONVNN_F32 ? 4 : 8;
+    if (D % V != 0 || ldx % V != 0 || ldy % V != 0 || !aligned16(x) || !aligned16(y) || !aligned16(gamma) ||
+        !aligned16(beta) || (pe && (!aligned16(pe) || !aligned16(cls))))
+        return set_error(CONVNN_E_ALIGN, "layernorm: D, strides and pointers must be multiples of 16 bytes");
+    if (dtype == CONVNN_F32)
+        return ln_dispatch<float>(x, ldx, gamma, beta, eps, y, ldy, rows, D, pe, cls, Np, cls_rows, st);
+    return ln_dispatch<__nv_bfloat16>(x, ldx, gamma, beta, eps, y, ldy, rows, D, pe, cls, Np, cls_rows, st);
+}
+
+int launch_patchify(int dtype, const void* img, void* out, int B, int C, int Hh, int Ww, int P, cudaStream_t st) {
+    const int V = dtype == CONVNN_F32 ? 4 : 8;
+    if (P % V != 0 || Ww % V != 0 || !aligned16(img) || !aligned16(out))
+        return set_error(CONVNN_E_ALIGN, "patchify: patch size and image width must be multiples of %d elements", V);
+    if (Hh % P != 0 || Ww % P != 0) return set_error(CONVNN_E_INVALID, "patchify: image not divisible into patches");
+    const long long total = (long long)B * C * Hh * Ww / V;
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (dtype == CONVNN_F32)
+        patchify_kernel<float><<<blocks, 256, 0, st>>>(static_cast<const float*>(img), static_cast<float*>(out), B, C,
+                                                      Hh, Ww, P, total);
+    else
+        patchify_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(img),
+                                                              static_cast<__nv_bfloat16*>(out), B, C, Hh, Ww, P, total);
+    CONVNN_CHECK_LAUNCH("patchify");
+    return CONVNN_OK;
+}
+
+}  // namespace convnn

@@ -97,6 +97,8 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const GemmParams p) {
                 int h = n / p.dk, ch = n - h * p.dk;
                 off = (long long)m * p.H * p.Cp + (long long)h * p.Cp + ch;
             }
+            if (p.residual)
+                r = to_f32<T>(from_f32<T>(r)) + to_f32<T>(static_cast<const T*>(p.residual)[(long long)m * p.ldr + n]);
             c[off] = from_f32<T>(r);
         }
     }

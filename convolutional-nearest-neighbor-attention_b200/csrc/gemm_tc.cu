@@ -31,6 +31,11 @@ struct GemmTcParams {
     __nv_bfloat16* c[3];
     long long ldc;
     const __nv_bfloat16* bias;
+    const __nv_bfloat16* residual;   // added after rounding the GEMM result (torch: y = x + linear(...))
+    long long ldr;
+    float* stat[3];        // per part: per-(row, head) statistic of the stored values, or nullptr
+    int stat_mode;         // CONVNN_COSINE: 1/max(norm, 1e-12); otherwise the squared norm
+    int dk, heads, rows_per_batch;   // head geometry of the statistic: stat[(b*heads + h)*rows_per_batch + r]
     int part_cols;         // output columns per part (N for a single output)
     int M, N, gelu;
     int KCH, KC, BN, BNpad;
@@ -46,29 +51,37 @@ __device__ __forceinline__ float gelu_exact(float x) {
     return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
 }
 
-// Convert W fp32 accumulators (+bias, GELU) to bf16 and store the first `valid` (a multiple
-// of 8) of them at dst (16-byte aligned).
-template <int W>
-__device__ __forceinline__ void store_chunk(__nv_bfloat16* dst, const uint32_t (&acc)[W], const __nv_bfloat16* bias,
-                                            int gelu, int valid) {
+// Epilogue, phase A (thread = one output row): 32 fp32 accumulators (+bias, GELU) -> bf16,
+// written as four 16-byte slots into this warp's 32 x 64-byte staging slab.  Slot s of row
+// l lands in physical slot s ^ ((l >> 1) & 3), which makes both this row-wise write and the
+// 8-rows-per-instruction read-back of phase B free of bank conflicts.  Returns the sum of
+// squares of the ROUNDED values (the statistic is defined on what is stored).
+__device__ __forceinline__ float stage_chunk(uint8_t* slab, int lane, const uint32_t (&acc)[32],
+                                             const __nv_bfloat16* bias, int bias_valid, int gelu) {
+    float ss = 0.f;
 #pragma unroll
-    for (int g = 0; g < W / 8; ++g) {
-        if (g * 8 >= valid) break;
+    for (int g = 0; g < 4; ++g) {
         uint4 packed;
         __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
+        uint4 bv = make_uint4(0, 0, 0, 0);
+        if (bias && g * 8 < bias_valid) bv = *reinterpret_cast<const uint4*>(bias + g * 8);
+        const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&bv);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             float a = __uint_as_float(acc[g * 8 + 2 * e]);
             float b = __uint_as_float(acc[g * 8 + 2 * e + 1]);
-            if (bias) {
-                a += __bfloat162float(bias[g * 8 + 2 * e]);
-                b += __bfloat162float(bias[g * 8 + 2 * e + 1]);
-            }
+            const float2 bb = __bfloat1622float2(bh[e]);
+            a += bb.x;
+            b += bb.y;
             if (gelu) { a = gelu_exact(a); b = gelu_exact(b); }
             h[e] = __floats2bfloat162_rn(a, b);
+            const float2 r = __bfloat1622float2(h[e]);
+            ss = fmaf(r.x, r.x, ss);
+            ss = fmaf(r.y, r.y, ss);
         }
-        *reinterpret_cast<uint4*>(dst + g * 8) = packed;   // N % 8 == 0: no ragged group
+        *reinterpret_cast<uint4*>(slab + lane * 64 + ((g ^ ((lane >> 1) & 3)) << 4)) = packed;
     }
+    return ss;
 }
 
 __global__ void __launch_bounds__(NTHREADS, 1)
@@ -80,7 +93,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const uint32_t a_bytes = BM * pitch, b_bytes = p.BN * pitch;
     uint8_t* sA = smem;
     uint8_t* sB = smem + STAGES * a_bytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sB + STAGES * b_bytes);
+    uint8_t* slabs = sB + STAGES * b_bytes;                    // 4 epilogue warps x 2 KB
+    uint64_t* bars = reinterpret_cast<uint64_t*>(slabs + 4 * 2048);
     uint64_t* full = bars;
     uint64_t* empty = bars + STAGES;
     uint64_t* tfull = bars + 2 * STAGES;
@@ -165,26 +179,70 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const int part = n0 / p.part_cols;
             const int pc0 = n0 - part * p.part_cols;          // first column inside the part
             __nv_bfloat16* cbase = part == 0 ? p.c[0] : (part == 1 ? p.c[1] : p.c[2]);
-            __nv_bfloat16* crow = cbase + (long long)row * p.ldc + pc0;
-            const __nv_bfloat16* brow = p.bias ? p.bias + n0 : nullptr;
+            float* stat = part == 0 ? p.stat[0] : (part == 1 ? p.stat[1] : p.stat[2]);
             const int ncol = min(p.BN, p.N - n0);             // valid columns of this tile
             ok = mbar_wait(&tfull[buf], u & 1u, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) { if (lane == 0) fail(abort_flag, 14); break; }
             tc_fence_after_sync();
             const uint32_t taddr = tmem_base + ((uint32_t)(lq * 32) << 16) + buf * p.BNpad;
-            int c = 0;
-            for (; c + 32 <= p.BN; c += 32) {
+            uint8_t* slab = slabs + (warp - 2) * 2048;
+            const int wrow0 = mt * BM + lq * 32;              // first row of this warp's slab
+            float ss = 0.f;
+            // TMEM reads run one chunk ahead of the conversion / store work of this warp
+            uint32_t nxt[32];
+            auto issue = [&](int c) {
+                if (c + 32 <= p.BN) {
+                    tmem_ld_x32(taddr + c, nxt);
+                } else {                                      // BN % 32 == 16: upper half is padding
+                    uint32_t lo[16];
+                    tmem_ld_x16(taddr + c, lo);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) { nxt[j] = lo[j]; nxt[16 + j] = 0u; }
+                }
+            };
+            issue(0);
+            for (int c = 0; c < p.BN; c += 32) {
                 uint32_t acc[32];
-                tmem_ld_x32(taddr + c, acc);
                 tmem_ld_wait();
-                if (row < p.M && c < ncol) store_chunk<32>(crow + c, acc, brow ? brow + c : nullptr, p.gelu, ncol - c);
-            }
-            if (c < p.BN) {
-                uint32_t acc[16];
-                tmem_ld_x16(taddr + c, acc);
-                tmem_ld_wait();
-                if (row < p.M && c < ncol) store_chunk<16>(crow + c, acc, brow ? brow + c : nullptr, p.gelu, ncol - c);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) acc[j] = nxt[j];
+                if (c + 32 < p.BN) issue(c + 32);
+                const float chunk_ss = stage_chunk(slab, lane, acc, p.bias ? p.bias + n0 + c : nullptr, ncol - c, p.gelu);
+                if (stat) {
+                    ss += chunk_ss;
+                    if ((pc0 + c + 32) % p.dk == 0) {         // chunk ends a head (dk % 32 == 0)
+                        if (row < p.M) {
+                            const int hh = (pc0 + c) / p.dk;
+                            const int bb = row / p.rows_per_batch, rr = row - bb * p.rows_per_batch;
+                            stat[((long long)bb * p.heads + hh) * p.rows_per_batch + rr] =
+                                p.stat_mode == CONVNN_COSINE ? 1.0f / fmaxf(sqrtf(ss), 1e-12f) : ss;
+                        }
+                        ss = 0.f;
+                    }
+                }
+                __syncwarp();
+                // phase B: 8 rows x 64 bytes per instruction, coalesced
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int rl = i * 8 + (lane >> 2), sl = lane & 3;
+                    const int grow = wrow0 + rl, gcol = c + sl * 8;
+                    uint4 v = *reinterpret_cast<const uint4*>(slab + rl * 64 + ((sl ^ ((rl >> 1) & 3)) << 4));
+                    if (grow < p.M && gcol < ncol) {
+                        if (p.residual) {
+                            const uint4 rv = *reinterpret_cast<const uint4*>(p.residual + (long long)grow * p.ldr + n0 + gcol);
+                            __nv_bfloat162* vh = reinterpret_cast<__nv_bfloat162*>(&v);
+                            const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float2 a = __bfloat1622float2(vh[e]), b2 = __bfloat1622float2(rh[e]);
+                                vh[e] = __floats2bfloat162_rn(a.x + b2.x, a.y + b2.y);
+                            }
+                        }
+                        *reinterpret_cast<uint4*>(cbase + (long long)grow * p.ldc + pc0 + gcol) = v;
+                    }
+                }
+                __syncwarp();
             }
             tc_fence_before_sync();
             __syncwarp();
@@ -228,16 +286,28 @@ bool gemm_tc_supported(const void* a, long long lda, const void* w, int Kd, int 
     return N % 8 == 0;
 }
 
-int launch_gemm_tc(const void* a, long long lda, const void* w, const void* bias, int M, int N, int Kd, int parts,
-                   void* const* c, long long ldc, int gelu, cudaStream_t st) {
+// Whether the per-(row, head) statistic can be produced by the GEMM epilogue: a tile must
+// cover whole heads and a 32-column chunk must never straddle two heads.
+bool gemm_tc_can_fuse_stats(int part_cols, int dk) {
+    const int bn = dividing_tile(part_cols);
+    return bn != 0 && dk % 32 == 0 && bn % dk == 0;
+}
+
+int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, int Kd, int parts, void* const* c,
+                   long long ldc, const GemmTcOpts& o, cudaStream_t st) {
     GemmTcParams p{};
-    for (int i = 0; i < 3; ++i) p.c[i] = static_cast<__nv_bfloat16*>(c[i < parts ? i : 0]);
-    p.ldc = ldc; p.bias = static_cast<const __nv_bfloat16*>(bias); p.gelu = gelu;
+    for (int i = 0; i < 3; ++i) {
+        p.c[i] = static_cast<__nv_bfloat16*>(c[i < parts ? i : 0]);
+        p.stat[i] = i < parts ? o.stat[i] : nullptr;
+    }
+    p.ldc = ldc; p.bias = static_cast<const __nv_bfloat16*>(o.bias); p.gelu = o.gelu;
+    p.residual = static_cast<const __nv_bfloat16*>(o.residual); p.ldr = o.ldr;
+    p.stat_mode = o.stat_mode; p.dk = o.dk > 0 ? o.dk : 32; p.heads = o.heads; p.rows_per_batch = o.rows_per_batch > 0 ? o.rows_per_batch : 1;
     p.M = M; p.N = N;
     p.part_cols = N / parts;
     p.KCH = Kd % 64 == 0 ? 64 : (Kd % 32 == 0 ? 32 : 16);
     p.KC = Kd / p.KCH;
-    if (parts > 1) {
+    if (parts > 1 || o.stat[0]) {
         p.BN = dividing_tile(p.part_cols);
     } else {
         const int nt = (N + 255) / 256;
@@ -256,7 +326,7 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, const void* bias
     if (!encode_tensor_map_bf16(&tmA, a, 2, dimsA, strA, boxA, pitch)) return CONVNN_E_CUDA;
     if (!encode_tensor_map_bf16(&tmW, w, 2, dimsW, strW, boxW, pitch)) return CONVNN_E_CUDA;
 
-    const size_t smem = 1024 + (size_t)STAGES * (BM + p.BN) * pitch + (2 * STAGES + 4) * 8 + 16;
+    const size_t smem = 1024 + (size_t)STAGES * (BM + p.BN) * pitch + 4 * 2048 + (2 * STAGES + 4) * 8 + 16;
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return set_error(CONVNN_E_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     int dev = 0, sms = 148;

@@ -37,9 +37,22 @@ __global__ void head_stats_kernel(T* t, float* stat, int B, int rows, int H, int
         }
         if (stat) {
             float ss = 0.f;
-            for (int c = lane; c < C; c += 32) {
-                float v = to_f32<T>(p[c]);
-                ss = fmaf(v, v, ss);
+            constexpr int VEC = 16 / sizeof(T);
+            if (C % VEC == 0 && (reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
+                for (int c = lane * VEC; c < C; c += 32 * VEC) {     // 16-byte loads
+                    const uint4 raw = *reinterpret_cast<const uint4*>(p + c);
+                    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+                    for (int j = 0; j < VEC; ++j) {
+                        const float v = to_f32<T>(e[j]);
+                        ss = fmaf(v, v, ss);
+                    }
+                }
+            } else {
+                for (int c = lane; c < C; c += 32) {
+                    float v = to_f32<T>(p[c]);
+                    ss = fmaf(v, v, ss);
+                }
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);

@@ -2,16 +2,16 @@
 //
 // Work unit = 256 consecutive key tokens (two 128-row MMA tiles) of one (batch, head).
 // A persistent CTA walks its units and, per unit, the candidate columns in tiles of
-// BN <= 128:
+// BN <= 128 (<= 64 in the small launch shape, see below):
 //
 //   warp 0     TMA producer: per 64-channel chunk two boxes of K rows (128 x 64 each) and
-//              ONE box of Q rows (BN x 64) shared by both row tiles, into a 3-stage ring
+//              ONE box of Q rows (BN x 64) shared by both row tiles, into a 2/3-stage ring
 //              (128-byte swizzle), straight from the (B, tokens, H, C) tensors.
 //   warp 1     MMA issuer: tcgen05.mma kind::f16, M = 128, N = BN, two accumulators per
 //              column tile (one per row tile), double-buffered in TMEM across column tiles
 //              (4 x BN columns), so the next tile's MMAs overlap this tile's epilogue.
 //   warps 2-5  epilogue of row tile 0, warps 6-9 epilogue of row tile 1: each thread owns
-//              one row (= its TMEM lane), pulls 32 columns at a time with tcgen05.ld,
+//              one row (= its TMEM lane), pulls 16/32 columns at a time with tcgen05.ld,
 //              turns dot products into ranking keys, filters them against the worst kept
 //              key (branch-free bit mask) and inserts the survivors into a sorted
 //              register list.  The T x S matrix never leaves the SM.
@@ -33,9 +33,13 @@ namespace {
 using namespace sm100;
 
 constexpr int BM = 128;
-constexpr int STAGES = 3;
+constexpr int MAX_STAGES = 3;
 constexpr int NTHREADS = 320;     // TMA warp, MMA warp, 2 x 4 epilogue warps
 constexpr int GROUP = 128;        // threads per epilogue group
+// Two launch shapes.  SMALL (short candidate lists, d_k <= 256): BN <= 64, 2 stages, 16-column
+// epilogue chunks and two CTAs per SM, so four epilogue warps per scheduler hide each other's
+// latency -- this regime is bound by the selection, not by the MMAs.  LARGE: BN <= 128, 3 stages,
+// one CTA per SM, for long sequences where the tensor pipe is the limiter.
 
 struct TcParams {
     const float* qstat;
@@ -48,6 +52,7 @@ struct TcParams {
     int KC;           // chunks per tile = C / KCH
     int BN;           // candidate columns per MMA (multiple of 16, <= 128)
     int BNpad;        // TMEM columns per accumulator (power of two >= BN)
+    int stages;       // shared-memory ring depth (<= MAX_STAGES)
     int n_pairs, n_col_tiles, n_units;
     float sqrt_dk;
 };
@@ -57,30 +62,40 @@ __device__ __forceinline__ void fail(volatile int* abort_flag, int code) {
     atomicCAS(&g_sim_topk_status, 0, code);
 }
 
-// One chunk of W accumulator columns of this thread's row: keys, threshold mask, drain.
+// One chunk of W accumulator columns of this thread's row: keys, then either plain inserts
+// (the first 32 columns of a row, where most values enter the list anyway) or a threshold
+// mask followed by a drain loop that only visits the survivors.
+// qv / cv hold the column statistic / candidate token of column (32-aligned base + lane).
 template <int NSEL, int W>
-__device__ __forceinline__ void consume(TopList<NSEL>& top, const uint32_t (&acc)[W], int col0, float qv, int cv,
-                                        const TcParams& p, int row, bool row_ok, float sentinel, float* ks) {
+__device__ __forceinline__ void consume(TopList<NSEL>& top, const uint32_t (&acc)[W], int col0, int lane_off,
+                                        float qv, int cv, const TcParams& p, int row, bool row_ok, float sentinel,
+                                        float* ks) {
     float key[W];
 #pragma unroll
     for (int j = 0; j < W; ++j) {
         const float dot = __uint_as_float(acc[j]);
         float k = dot;
         if (p.metric != CONVNN_MATMUL) {
-            const float s = __shfl_sync(0xffffffffu, qv, j);
+            const float s = __shfl_sync(0xffffffffu, qv, lane_off + j);
             k = (p.metric == CONVNN_COSINE) ? dot * s : fmaf(2.0f, dot, -s);
         }
         if (p.sampled) {
-            const int cj = __shfl_sync(0xffffffffu, cv, j);
+            const int cj = __shfl_sync(0xffffffffu, cv, lane_off + j);
             if (cj == row) k = sentinel;
         }
         key[j] = k;
+    }
+    const int left = p.S - col0;                       // valid columns from col0 on
+    if (col0 < 32) {
+#pragma unroll
+        for (int j = 0; j < W; ++j)
+            if (row_ok && j < left) top.insert_sorted(key[j], col0 + j);
+        return;
     }
     const float thr = top.worst();
     uint32_t mask = 0;
 #pragma unroll
     for (int j = 0; j < W; ++j) mask |= (key[j] > thr) ? (1u << j) : 0u;
-    const int left = p.S - col0;                       // valid columns from col0 on
     if (left < W) mask &= (left <= 0) ? 0u : ((1u << left) - 1u);
     if (!row_ok) mask = 0;
     if (__any_sync(0xffffffffu, mask != 0)) {
@@ -98,8 +113,8 @@ __device__ __forceinline__ void consume(TopList<NSEL>& top, const uint32_t (&acc
     }
 }
 
-template <int NSEL>
-__global__ void __launch_bounds__(NTHREADS, 1)
+template <int NSEL, int MINB, int CW>
+__global__ void __launch_bounds__(NTHREADS, MINB)
 sim_topk_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmQ,
                    const TcParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -107,12 +122,13 @@ sim_topk_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     const uint32_t pitch = p.KCH * 2;
     const uint32_t a_bytes = BM * pitch, b_bytes = p.BN * pitch;
     const uint32_t stage_bytes = 2 * a_bytes + b_bytes;
+    const uint32_t STAGES = p.stages;
     uint8_t* stages = smem;                                            // [STAGES][A0 | A1 | B]
-    float* keybuf = reinterpret_cast<float*>(smem + STAGES * stage_bytes);   // [2 groups][32][GROUP]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(keybuf + 2 * 32 * GROUP);
+    float* keybuf = reinterpret_cast<float*>(smem + STAGES * stage_bytes);   // [2 groups][CW][GROUP]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(keybuf + 2 * CW * GROUP);
     uint64_t* full = bars;
-    uint64_t* empty = bars + STAGES;
-    uint64_t* tfull = bars + 2 * STAGES;
+    uint64_t* empty = bars + MAX_STAGES;
+    uint64_t* tfull = bars + 2 * MAX_STAGES;
     uint64_t* tempty = tfull + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -121,7 +137,7 @@ sim_topk_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     const uint32_t ncols = 4u * p.BNpad;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < MAX_STAGES; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
@@ -202,7 +218,7 @@ sim_topk_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         const int grp = (warp - 2) >> 2;         // which row tile of the pair this warp serves
         const int lq = warp & 3;                 // TMEM lane quarter this warp may read
         const int r = lq * 32 + lane;            // row within the tile
-        float* ks = keybuf + grp * 32 * GROUP + r;
+        float* ks = keybuf + grp * CW * GROUP + r;
         uint32_t tile = 0;
         bool ok = true;
         for (int unit = blockIdx.x; unit < p.n_units && ok; unit += gridDim.x) {
@@ -220,41 +236,49 @@ sim_topk_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
             }
             TopList<NSEL> top;
             top.init();
-            for (int ct = 0; ct < p.n_col_tiles && ok; ++ct, ++tile) {
-                const uint32_t par = tile & 1u, u = tile >> 1;
-                // column statistics of this tile, fetched before the accumulator is awaited
-                float qv[4];
-                int cv[4];
+            // column statistics (4 x 32 columns cover BN <= 128), fetched one tile ahead
+            float qv[4], qn[4];
+            int cv[4], cn[4];
+            auto fetch = [&](int ct, float (&fq)[4], int (&fc)[4]) {
 #pragma unroll
                 for (int c4 = 0; c4 < 4; ++c4) {
                     const int cl = min(ct * p.BN + c4 * 32 + lane, p.S - 1);
-                    qv[c4] = (p.metric != CONVNN_MATMUL && c4 * 32 < p.BN) ? qs_row[cl] : 0.f;
-                    cv[c4] = (p.sampled && c4 * 32 < p.BN) ? p.cand[cl] : -1;
+                    fq[c4] = (p.metric != CONVNN_MATMUL && c4 * 32 < p.BN) ? qs_row[cl] : 0.f;
+                    fc[c4] = (p.sampled && c4 * 32 < p.BN) ? p.cand[cl] : -1;
                 }
+            };
+            fetch(0, qv, cv);
+            for (int ct = 0; ct < p.n_col_tiles && ok; ++ct, ++tile) {
+                const uint32_t par = tile & 1u, u = tile >> 1;
+                if (ct + 1 < p.n_col_tiles) fetch(ct + 1, qn, cn);
                 ok = mbar_wait(&tfull[par], u & 1u, abort_flag);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) { if (lane == 0) fail(abort_flag, 4); break; }
                 tc_fence_after_sync();
                 const uint32_t taddr = tmem_base + ((uint32_t)(lq * 32) << 16) + (grp * 2 + par) * p.BNpad;
-#pragma unroll
-                for (int c4 = 0; c4 < 4; ++c4) {
-                    const int c = c4 * 32;
+#pragma unroll 1
+                for (int c = 0; c < p.BN; c += CW) {
                     const int col0 = ct * p.BN + c;
-                    if (c + 32 <= p.BN) {
+                    const int c4 = c >> 5;
+                    const float q1 = c4 == 0 ? qv[0] : (c4 == 1 ? qv[1] : (c4 == 2 ? qv[2] : qv[3]));
+                    const int c1 = c4 == 0 ? cv[0] : (c4 == 1 ? cv[1] : (c4 == 2 ? cv[2] : cv[3]));
+                    if (CW == 32 && c + 32 <= p.BN) {
                         uint32_t acc[32];
                         tmem_ld_x32(taddr + c, acc);
                         tmem_ld_wait();
-                        consume<NSEL, 32>(top, acc, col0, qv[c4], cv[c4], p, row, row_ok, sentinel, ks);
-                    } else if (c < p.BN) {
+                        consume<NSEL, 32>(top, acc, col0, 0, q1, c1, p, row, row_ok, sentinel, ks);
+                    } else {
                         uint32_t acc[16];
                         tmem_ld_x16(taddr + c, acc);
                         tmem_ld_wait();
-                        consume<NSEL, 16>(top, acc, col0, qv[c4], cv[c4], p, row, row_ok, sentinel, ks);
+                        consume<NSEL, 16>(top, acc, col0, c & 31, q1, c1, p, row, row_ok, sentinel, ks);
                     }
                 }
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&tempty[par]);
+#pragma unroll
+                for (int c4 = 0; c4 < 4; ++c4) { qv[c4] = qn[c4]; cv[c4] = cn[c4]; }
             }
             if (ok && row_ok) {
                 const long long obase = ((long long)bh * p.T + row) * p.K;
@@ -319,7 +343,10 @@ int launch_sim_topk_tc(const convnn_desc* d, const Dims& dm, const void* q, cons
     p.T = dm.T; p.S = dm.S; p.H = dm.H; p.K = dm.K; p.nsel = dm.nsel; p.metric = d->metric; p.sampled = d->sampled;
     p.KCH = dm.Cp % 64 == 0 ? 64 : (dm.Cp % 32 == 0 ? 32 : 16);
     p.KC = dm.Cp / p.KCH;
-    const int ntile = (dm.S + 127) / 128;
+    const bool small_cfg = dm.Cp <= 256 && dm.nsel <= 12;
+    const int bn_cap = small_cfg ? 64 : 128;
+    p.stages = small_cfg ? 2 : 3;
+    const int ntile = (dm.S + bn_cap - 1) / bn_cap;
     p.BN = (((dm.S + ntile - 1) / ntile) + 15) / 16 * 16;
     p.BNpad = pow2_at_least(p.BN, 32);
     p.n_pairs = (dm.T + 2 * BM - 1) / (2 * BM);
@@ -338,30 +365,38 @@ int launch_sim_topk_tc(const convnn_desc* d, const Dims& dm, const void* q, cons
     if (!encode_tensor_map_bf16(&tmK, k, 4, dimsK, strK, boxK, pitch)) return CONVNN_E_CUDA;
     if (!encode_tensor_map_bf16(&tmQ, q, 4, dimsQ, strQ, boxQ, pitch)) return CONVNN_E_CUDA;
 
-    const size_t smem = 1024 + (size_t)STAGES * (2 * BM + p.BN) * pitch + 2 * 32 * GROUP * sizeof(float) +
-                        (2 * STAGES + 4) * 8 + 16;
+    const int cw = small_cfg ? 16 : 32;
+    const size_t smem = 1024 + (size_t)p.stages * (2 * BM + p.BN) * pitch + 2 * cw * GROUP * sizeof(float) +
+                        (2 * MAX_STAGES + 4) * 8 + 16;
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const int grid = p.n_units < sms ? p.n_units : sms;
+    const int ctas = sms * (small_cfg ? 2 : 1);
+    const int grid = p.n_units < ctas ? p.n_units : ctas;
 
-#define CONVNN_TC_LAUNCH(N)                                                                            \
+#define CONVNN_TC_LAUNCH2(N, MINB, CWV)                                                                \
     do {                                                                                               \
-        auto kern = sim_topk_tc_kernel<N>;                                                             \
+        auto kern = sim_topk_tc_kernel<N, MINB, CWV>;                                                  \
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         if (e != cudaSuccess) return set_error(CONVNN_E_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e)); \
         kern<<<grid, NTHREADS, smem, st>>>(tmK, tmQ, p);                                               \
+    } while (0)
+#define CONVNN_TC_LAUNCH(N)                            \
+    do {                                               \
+        if (small_cfg) CONVNN_TC_LAUNCH2(N, 2, 16);    \
+        else CONVNN_TC_LAUNCH2(N, 1, 32);              \
     } while (0)
     const int n = dm.nsel;
     if (n <= 4) CONVNN_TC_LAUNCH(4);
     else if (n <= 8) CONVNN_TC_LAUNCH(8);
     else if (n == 9) CONVNN_TC_LAUNCH(9);
     else if (n <= 12) CONVNN_TC_LAUNCH(12);
-    else if (n <= 16) CONVNN_TC_LAUNCH(16);
-    else if (n <= 24) CONVNN_TC_LAUNCH(24);
-    else if (n == 25) CONVNN_TC_LAUNCH(25);
-    else CONVNN_TC_LAUNCH(32);
+    else if (n <= 16) CONVNN_TC_LAUNCH2(16, 1, 32);
+    else if (n <= 24) CONVNN_TC_LAUNCH2(24, 1, 32);
+    else if (n == 25) CONVNN_TC_LAUNCH2(25, 1, 32);
+    else CONVNN_TC_LAUNCH2(32, 1, 32);
 #undef CONVNN_TC_LAUNCH
+#undef CONVNN_TC_LAUNCH2
     CONVNN_CHECK_LAUNCH("sim_topk_tc");
     return CONVNN_OK;
 }

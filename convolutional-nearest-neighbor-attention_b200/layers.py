@@ -122,16 +122,18 @@ class MultiHeadConvNNAttention(nn.Module):
         if self.magnitude_type not in ('cosine', 'matmul', 'euclidean'):
             raise ValueError(f"unknown magnitude_type {self.magnitude_type!r}")
 
-    def forward(self, x, out: Optional[torch.Tensor] = None):
+    def forward(self, x, out: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None):
+        """``layer(x)``; with ``residual`` the caller's skip connection is folded into the last
+        store (``residual + layer(x)``), with ``out`` the result is written in place."""
         self._check_mode(x)
         B, T, D = x.shape
         cand = self.candidates(T, x.device)
         packed = self.packed_weights(x.dtype, x.device)
         if self.stage_timer is not None:
-            return self._forward_staged(x, packed, cand, out)
-        return ops.forward(self._spec(), x, packed, cand, out=out)
+            return self._forward_staged(x, packed, cand, out, residual)
+        return ops.forward(self._spec(), x, packed, cand, out=out, residual=residual)
 
-    def _forward_staged(self, x, packed, cand, out):
+    def _forward_staged(self, x, packed, cand, out, residual=None):
         """The same kernels in the same order as ``convnn_b200_forward``, issued through the
         four stage entry points so a profiler hook can bracket each with CUDA events."""
         spec, mark = self._spec(), self.stage_timer
@@ -143,7 +145,7 @@ class MultiHeadConvNNAttention(nn.Module):
         mark("sim_topk")
         o = ops.gather_conv(spec, v, idx, val, w_conv, w_pw, S=q.shape[1])
         mark("gather_conv")
-        y = ops.out_proj(spec, o, w_o, out=out, S=q.shape[1])
+        y = ops.out_proj(spec, o, w_o, out=out, S=q.shape[1], residual=residual)
         mark("out_proj")
         return y
 

@@ -150,8 +150,18 @@ def gather_conv(spec: LayerSpec, v, idx, val, w_conv, w_pw=None, S: Optional[int
     return o
 
 
-def out_proj(spec: LayerSpec, o, w_o, out: Optional[torch.Tensor] = None, S: Optional[int] = None):
-    """-> out (B,T,D); ``out`` may be a channel slice of a wider tensor."""
+def _residual_arg(residual, like):
+    if residual is None:
+        return None, 0
+    r, ldr = _rows_view(residual)
+    if r.dtype != like.dtype or not r.is_cuda:
+        raise TypeError("residual must be a CUDA tensor of the activation dtype")
+    return r, ldr
+
+
+def out_proj(spec: LayerSpec, o, w_o, out: Optional[torch.Tensor] = None, S: Optional[int] = None,
+             residual: Optional[torch.Tensor] = None):
+    """-> out (B,T,D) [= residual + proj]; ``out`` may be a channel slice of a wider tensor."""
     _require_cuda(o, w_o)
     L = _capi.lib()
     B, H, T, dk = o.shape
@@ -162,8 +172,9 @@ def out_proj(spec: LayerSpec, o, w_o, out: Optional[torch.Tensor] = None, S: Opt
     if view is not out:
         raise ValueError("out must have unit channel stride and evenly strided rows")
     scratch = torch.empty(L.convnn_b200_stage_scratch_bytes(d), dtype=torch.uint8, device=o.device)
-    _capi.check(L.convnn_b200_out_proj(d, o.data_ptr(), w_o.data_ptr(), out.data_ptr(), ldo, scratch.data_ptr(),
-                                       _stream(o)))
+    res, ldr = _residual_arg(residual, o)
+    _capi.check(L.convnn_b200_out_proj(d, o.data_ptr(), w_o.data_ptr(), _capi.ptr(res), ldr, out.data_ptr(), ldo,
+                                       scratch.data_ptr(), _stream(o)))
     return out
 
 
@@ -177,8 +188,9 @@ def workspace_bytes(spec: LayerSpec, B: int, T: int, S: int, dtype: torch.dtype)
 
 
 def forward(spec: LayerSpec, x: torch.Tensor, packed, cand: Optional[torch.Tensor] = None,
-            out: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Whole-layer forward through ``convnn_b200_forward``."""
+            out: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None,
+            residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Whole-layer forward through ``convnn_b200_forward`` (out = [residual +] layer(x))."""
     w_qkv, w_conv, w_pw, w_o = packed
     _require_cuda(x, w_qkv)
     L = _capi.lib()
@@ -196,7 +208,72 @@ def forward(spec: LayerSpec, x: torch.Tensor, packed, cand: Optional[torch.Tenso
     oview, ldo = _rows_view(out)
     if oview is not out:
         raise ValueError("out must have unit channel stride and evenly strided rows")
+    res, ldr = _residual_arg(residual, x)
     _capi.check(L.convnn_b200_forward(d, x.data_ptr(), ldx, w_qkv.data_ptr(), w_conv.data_ptr(), _capi.ptr(w_pw),
-                                      w_o.data_ptr(), _capi.ptr(cand), out.data_ptr(), ldo,
+                                      w_o.data_ptr(), _capi.ptr(cand), _capi.ptr(res), ldr, out.data_ptr(), ldo,
                                       workspace.data_ptr(), workspace.numel(), _stream(x)))
+    return out
+
+
+# ---- the encoder ops around the layer ---------------------------------------------------
+
+def _flat_rows(t: torch.Tensor) -> Tuple[torch.Tensor, int, int]:
+    """(..., D) tensor -> (tensor, rows, ld) with contiguous rows of a common stride."""
+    D = t.shape[-1]
+    if t.dim() >= 2 and t.stride(-1) == 1 and t.is_contiguous():
+        return t, t.numel() // D, D
+    if t.dim() == 3:
+        v, ld = _rows_view(t)
+        return v, v.shape[0] * v.shape[1], ld
+    t = t.contiguous()
+    return t, t.numel() // D, D
+
+
+def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+    _require_cuda(x, weight, bias)
+    L = _capi.lib()
+    xv, rows, ldx = _flat_rows(x)
+    D = x.shape[-1]
+    y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    _capi.check(L.convnn_b200_layernorm(_dtype_code(x.dtype), xv.data_ptr(), ldx, weight.data_ptr(), bias.data_ptr(),
+                                        float(eps), y.data_ptr(), D, rows, D, _stream(x)))
+    return y
+
+
+def linear(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, gelu: bool = False,
+           residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """[GELU](a @ weight.T + bias) [+ residual] through ``convnn_b200_linear``."""
+    _require_cuda(a, weight, bias, residual)
+    L = _capi.lib()
+    av, M, lda = _flat_rows(a)
+    N, K = weight.shape
+    w = weight if weight.is_contiguous() else weight.contiguous()
+    out = torch.empty(*a.shape[:-1], N, dtype=a.dtype, device=a.device)
+    res, ldr = (None, 0)
+    if residual is not None:
+        res, _, ldr = _flat_rows(residual)
+    _capi.check(L.convnn_b200_linear(_dtype_code(a.dtype), av.data_ptr(), lda, w.data_ptr(), _capi.ptr(bias),
+                                     _capi.ptr(res), ldr, out.data_ptr(), N, M, N, K, int(gelu), _stream(a)))
+    return out
+
+
+def patch_embed(images: torch.Tensor, conv_weight: torch.Tensor, conv_bias: torch.Tensor, norm_weight, norm_bias,
+                cls: torch.Tensor, pe: torch.Tensor, patch: int, eps: float = 1e-5) -> torch.Tensor:
+    """PatchEmbedding + PositionalEncoding (reference vit.py:104-109, 126-135): unfold, GEMM
+    with the (D, C*P*P) weight view, LayerNorm, class token and positional table -> (B, T, D)."""
+    _require_cuda(images, conv_weight)
+    L = _capi.lib()
+    B, C, Hh, Ww = images.shape
+    D = conv_weight.shape[0]
+    Np = (Hh // patch) * (Ww // patch)
+    dt = _dtype_code(images.dtype)
+    images = images.contiguous()
+    cols = torch.empty(B * Np, C * patch * patch, dtype=images.dtype, device=images.device)
+    _capi.check(L.convnn_b200_patchify(dt, images.data_ptr(), cols.data_ptr(), B, C, Hh, Ww, patch, _stream(images)))
+    proj = linear(cols, conv_weight.reshape(D, -1), conv_bias)
+    out = torch.empty(B, Np + 1, D, dtype=images.dtype, device=images.device)
+    pe2 = pe.reshape(-1, D)[: Np + 1].contiguous()
+    _capi.check(L.convnn_b200_embed_tokens(dt, proj.data_ptr(), norm_weight.data_ptr(), norm_bias.data_ptr(), float(eps),
+                                           cls.reshape(-1).contiguous().data_ptr(), pe2.data_ptr(), out.data_ptr(),
+                                           B, Np, D, _stream(images)))
     return out

@@ -14,6 +14,7 @@ from types import SimpleNamespace
 import torch
 import torch.nn as nn
 
+from . import ops
 from .layers import MultiHeadBranchingAttention, MultiHeadBranchingConv, MultiHeadConvNNAttention
 
 _DEFAULTS = dict(layer="ConvNNAttention", patch_size=16, num_layers=12, num_heads=3, d_hidden=192, d_mlp=768,
@@ -38,6 +39,11 @@ class PatchEmbedding(nn.Module):
 
     def forward(self, x):
         return self.norm(self.linear_projection(x).flatten(2).transpose(1, 2))
+
+
+def _library_path(x: torch.Tensor) -> bool:
+    """The fused encoder ops cover CUDA float32 / bfloat16 inference."""
+    return x.is_cuda and x.dtype in (torch.float32, torch.bfloat16) and not torch.is_grad_enabled()
 
 
 class PositionalEncoding(nn.Module):
@@ -83,8 +89,23 @@ class TransformerEncoder(nn.Module):
                                  nn.Linear(d_mlp, d_hidden))
 
     def forward(self, x):
+        if _library_path(x) and not (self.training and (self.dropout1.p > 0 or self.dropout2.p > 0)):
+            return self._forward_library(x)
         x = x + self.dropout1(self.attention(self.norm1(x)))
         return x + self.dropout2(self.mlp(self.norm2(x)))
+
+    def _forward_library(self, x):
+        """The same block with LayerNorm, both Linear layers (GELU and the skip connections
+        folded into their stores) and the attention output projection (+ skip) in libconvnn_b200."""
+        n1, n2, fc1, fc2 = self.norm1, self.norm2, self.mlp[0], self.mlp[3]
+        xn = ops.layernorm(x, n1.weight, n1.bias, n1.eps)
+        if isinstance(self.attention, MultiHeadConvNNAttention):
+            x = self.attention(xn, residual=x)
+        else:
+            x = x + self.attention(xn)
+        xn = ops.layernorm(x, n2.weight, n2.bias, n2.eps)
+        h = ops.linear(xn, fc1.weight, fc1.bias, gelu=True)
+        return ops.linear(h, fc2.weight, fc2.bias, residual=x)
 
 
 class ViT(nn.Module):
@@ -109,6 +130,12 @@ class ViT(nn.Module):
         self.to(self.device)
 
     def forward(self, x):
+        if _library_path(x):
+            pe_mod, pemb = self.positional_encoding, self.patch_embedding
+            x = ops.patch_embed(x, pemb.linear_projection.weight, pemb.linear_projection.bias, pemb.norm.weight,
+                                pemb.norm.bias, pe_mod.cls_tokens, pe_mod.pe, self.args.patch_size, pemb.norm.eps)
+            x = self.transformer_encoder(x)
+            return ops.linear(x[:, 0], self.classifier.weight, self.classifier.bias)
         x = self.positional_encoding(self.patch_embedding(x))
         x = self.transformer_encoder(x)
         return self.classifier(x[:, 0])

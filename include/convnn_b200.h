@@ -136,8 +136,11 @@ int convnn_b200_gather_conv(const convnn_desc* d, const void* v, const int32_t* 
                             void* o, void* stream);
 
 /* Head merge (including the reference's flat reinterpretation for H > 1) and the W_o
- * projection.  Replaces layers.py:317, 320 (247-259). */
+ * projection.  Replaces layers.py:317, 320 (247-259).  With `residual` != NULL (rows of D
+ * elements, stride ldr) the caller's skip connection `x + attention(...)` (vit.py:264) is
+ * folded into the store: out = residual + round(proj). */
 int convnn_b200_out_proj(const convnn_desc* d, const void* o, const void* w_o,
+                         const void* residual, int64_t ldr,
                          void* out, int64_t ldo, void* scratch, void* stream);
 
 /* The whole layer forward: the four calls above chained on `stream` with their
@@ -145,8 +148,37 @@ int convnn_b200_out_proj(const convnn_desc* d, const void* o, const void* w_o,
  * (layers.py:261-321), eval mode. */
 int convnn_b200_forward(const convnn_desc* d, const void* x, int64_t ldx, const void* w_qkv,
                         const void* w_conv, const void* w_pw, const void* w_o,
-                        const int32_t* cand, void* out, int64_t ldo,
+                        const int32_t* cand, const void* residual, int64_t ldr,
+                        void* out, int64_t ldo,
                         void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- callers of the hot path: the rest of the reference's TransformerEncoder / ViT ----
+ * dtype is a convnn_dtype; all pointers are device pointers in that type. */
+
+/* y = LayerNorm(x) over the last dimension, affine (nn.LayerNorm: vit.py:247-248 as used at
+ * vit.py:262, 267).  rows x D, strides ldx / ldy elements, statistics in fp32. */
+int convnn_b200_layernorm(int dtype, const void* x, int64_t ldx, const void* gamma, const void* beta,
+                          float eps, void* y, int64_t ldy, int64_t rows, int32_t D, void* stream);
+
+/* out = [GELU](a * w^T + bias) [+ residual]: nn.Linear with its activation and the skip
+ * connection folded in (vit.py:253-258 with 269; vit.py:71; and, on unfolded patches,
+ * the Conv2d patch projection vit.py:99, 105).  a (M, K) stride lda; w (N, K) as nn.Linear
+ * stores it; bias (N) or NULL; residual (M, N) stride ldr or NULL, added after rounding. */
+int convnn_b200_linear(int dtype, const void* a, int64_t lda, const void* w, const void* bias,
+                       const void* residual, int64_t ldr, void* out, int64_t ldo,
+                       int64_t M, int32_t N, int32_t K, int32_t gelu, void* stream);
+
+/* Unfold non-overlapping P x P patches: img (B, C, Hh, Ww) -> out (B * Hh/P * Ww/P, C*P*P),
+ * the im2col of Conv2d(kernel = stride = P) (vit.py:99, 105-107). */
+int convnn_b200_patchify(int dtype, const void* img, void* out, int32_t B, int32_t C, int32_t Hh,
+                         int32_t Ww, int32_t P, void* stream);
+
+/* Embedding tail: out[b, 0] = cls + pe[0]; out[b, 1 + n] = LayerNorm(proj[b, n]) + pe[1 + n]
+ * (PatchEmbedding.norm, class token and positional table: vit.py:108, 126-135).
+ * proj (B, Np, D), cls (D), pe (Np + 1, D), out (B, Np + 1, D), all contiguous. */
+int convnn_b200_embed_tokens(int dtype, const void* proj, const void* gamma, const void* beta, float eps,
+                             const void* cls, const void* pe, void* out, int32_t B, int32_t Np,
+                             int32_t D, void* stream);
 
 #ifdef __cplusplus
 }

@@ -84,8 +84,11 @@ def test_null_pointer_rejected_before_any_launch():
     L = _capi.lib()
     rc = L.convnn_b200_sim_topk(desc(), None, None, None, None, None, None, None, None)
     assert rc == _capi.E_NULL
-    rc = L.convnn_b200_forward(desc(), None, 48, None, None, None, None, None, None, 48, None, 0, None)
+    rc = L.convnn_b200_forward(desc(), None, 48, None, None, None, None, None, None, 0, None, 48, None, 0, None)
     assert rc == _capi.E_NULL
+    assert L.convnn_b200_layernorm(_capi.F32, None, 8, None, None, 1e-5, None, 8, 4, 8, None) == _capi.E_NULL
+    assert L.convnn_b200_linear(_capi.F32, None, 8, None, None, None, 0, None, 8, 4, 8, 8, 0, None) == _capi.E_NULL
+    assert L.convnn_b200_linear(7, None, 8, None, None, None, 0, None, 8, 4, 8, 8, 0, None) == _capi.E_INVALID
 
 
 def _keys(module):

@@ -75,3 +75,53 @@ def test_full_size_properties_bf16():
         y = m(x)
         yp = m(x[perm])
     assert torch.equal(y[perm], yp)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-6), (torch.bfloat16, 1.2e-2)])
+def test_encoder_ops_match_torch(dtype, tol):
+    """LayerNorm, Linear(+GELU, +residual), patch embedding through the C ABI vs torch fp32."""
+    import torch.nn.functional as F
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(3, 197, 192, generator=g).to(DEV, dtype)
+    w, b = (1 + 0.1 * torch.randn(192, generator=g)).to(DEV, dtype), (0.1 * torch.randn(192, generator=g)).to(DEV, dtype)
+    want = F.layer_norm(x.float(), (192,), w.float(), b.float(), 1e-5)
+    assert rel_err(ops.layernorm(x, w, b, 1e-5), want) < max(tol, 4e-3 if dtype == torch.bfloat16 else tol)
+    W1 = (torch.randn(768, 192, generator=g) / 14).to(DEV, dtype)
+    b1 = (0.1 * torch.randn(768, generator=g)).to(DEV, dtype)
+    h = ops.linear(x, W1, b1, gelu=True)
+    assert rel_err(h, F.gelu(x.float() @ W1.float().t() + b1.float())) < tol
+    W2 = (torch.randn(192, 768, generator=g) / 28).to(DEV, dtype)
+    b2 = (0.1 * torch.randn(192, generator=g)).to(DEV, dtype)
+    y = ops.linear(h, W2, b2, residual=x)
+    assert rel_err(y, x.float() + (h.float() @ W2.float().t() + b2.float())) < tol
+    # ragged N (classifier) and a strided A (class-token rows)
+    Wc = (torch.randn(1000, 192, generator=g) / 14).to(DEV, dtype)
+    bc = (0.1 * torch.randn(1000, generator=g)).to(DEV, dtype)
+    assert rel_err(ops.linear(x[:, 0], Wc, bc), x[:, 0].float() @ Wc.float().t() + bc.float()) < tol
+    # patch embedding: unfold + GEMM + LayerNorm + cls + positional table
+    img = torch.randn(2, 3, 224, 224, generator=g).to(DEV, dtype)
+    cw = (torch.randn(192, 3, 16, 16, generator=g) / 28).to(DEV, dtype)
+    cb = (0.1 * torch.randn(192, generator=g)).to(DEV, dtype)
+    cls = torch.randn(1, 1, 192, generator=g).to(DEV, dtype)
+    pe = torch.randn(1, 197, 192, generator=g).to(DEV, dtype)
+    got = ops.patch_embed(img, cw, cb, w, b, cls, pe, 16)
+    ref = F.conv2d(img.float(), cw.float(), cb.float(), stride=16).flatten(2).transpose(1, 2)
+    ref = F.layer_norm(ref, (192,), w.float(), b.float(), 1e-5)
+    ref = torch.cat([cls.float().expand(2, -1, -1), ref], dim=1) + pe.float()
+    assert rel_err(got, ref) < max(tol, 6e-3 if dtype == torch.bfloat16 else tol)
+
+
+def test_residual_is_folded_into_the_output_projection():
+    cfg = ConvNNConfig(d_hidden=192, num_heads=1, K=9, magnitude_type="cosine")
+    w = {n: bf16_round(t) for n, t in make_layer_weights(cfg, seed=5).items()}
+    m = convnn_b200.MultiHeadConvNNAttention(192, 1, 0.0, 9, "all", -1, 0, "cosine")
+    m.load_state_dict(w)
+    for dtype in (torch.bfloat16, torch.float32):
+        m = m.eval().to(DEV, dtype)
+        x = make_input(3, 197, 192, seed=6).to(DEV, dtype)
+        with torch.no_grad():
+            y = m(x)
+            z = m(x, residual=x)
+        assert torch.equal(z, x + y)
