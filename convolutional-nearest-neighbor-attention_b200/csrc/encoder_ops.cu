@@ -115,11 +115,12 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const T* __restrict__ x,
 }
 
 // rows (b, py, px) x columns (c, i, j) <- img[b, c, py*P + i, px*P + j]: the unfold that
-// turns Conv2d(kernel = stride = P) into a GEMM with the (D, C*P*P) weight view.
-template <typename T>
+// turns Conv2d(kernel = stride = P) into a GEMM with the (D, C*P*P) weight view.  VT is an
+// unsigned integer type carrying VE = sizeof(VT) / sizeof(T) contiguous elements of a patch row.
+template <typename T, typename VT>
 __global__ void patchify_kernel(const T* __restrict__ img, T* __restrict__ out, int B, int C, int Hh, int Ww, int P,
                                 long long total_vec) {
-    constexpr int V = Vec16<T>::N;
+    constexpr int V = sizeof(VT) / sizeof(T);
     const int vec_per_prow = P / V;                  // vectors per patch row
     const int Wp = Ww / P, Hp = Hh / P;
     for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total_vec;
@@ -133,8 +134,17 @@ __global__ void patchify_kernel(const T* __restrict__ img, T* __restrict__ out, 
         const long long b = t;
         const T* src = img + (((b * C + c) * Hh + (py * P + i)) * (long long)Ww + px * P + jv * V);
         T* dst = out + ((b * Hp + py) * Wp + px) * (long long)(C * P * P) + (c * P + i) * P + jv * V;
-        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+        *reinterpret_cast<VT*>(dst) = *reinterpret_cast<const VT*>(src);
     }
+}
+
+template <typename T, typename VT>
+void patchify_launch(const void* img, void* out, int B, int C, int Hh, int Ww, int P, cudaStream_t st) {
+    const long long total = (long long)B * C * Hh * Ww / (long long)(sizeof(VT) / sizeof(T));
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    patchify_kernel<T, VT><<<blocks, 256, 0, st>>>(static_cast<const T*>(img), static_cast<T*>(out), B, C, Hh, Ww, P,
+                                                   total);
 }
 
 template <typename T>
@@ -176,19 +186,21 @@ int launch_layernorm(int dtype, const void* x, long long ldx, const void* gamma,
 }
 
 int launch_patchify(int dtype, const void* img, void* out, int B, int C, int Hh, int Ww, int P, cudaStream_t st) {
-    const int V = dtype == CONVNN_F32 ? 4 : 8;
-    if (P % V != 0 || Ww % V != 0 || !aligned16(img) || !aligned16(out))
-        return set_error(CONVNN_E_ALIGN, "patchify: patch size and image width must be multiples of %d elements", V);
     if (Hh % P != 0 || Ww % P != 0) return set_error(CONVNN_E_INVALID, "patchify: image not divisible into patches");
-    const long long total = (long long)B * C * Hh * Ww / V;
-    int blocks = (int)((total + 255) / 256);
-    if (blocks > 148 * 32) blocks = 148 * 32;
-    if (dtype == CONVNN_F32)
-        patchify_kernel<float><<<blocks, 256, 0, st>>>(static_cast<const float*>(img), static_cast<float*>(out), B, C,
-                                                      Hh, Ww, P, total);
-    else
-        patchify_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(img),
-                                                              static_cast<__nv_bfloat16*>(out), B, C, Hh, Ww, P, total);
+    if (!aligned16(img) || !aligned16(out)) return set_error(CONVNN_E_ALIGN, "patchify: pointers must be 16-byte aligned");
+    const int elt = dtype == CONVNN_F32 ? 4 : 2;
+    int vb = 16;                                      // widest vector (bytes) that divides a patch row
+    while (vb > elt && (P * elt) % vb != 0) vb >>= 1;
+    if (dtype == CONVNN_F32) {
+        if (vb == 16) patchify_launch<float, uint4>(img, out, B, C, Hh, Ww, P, st);
+        else if (vb == 8) patchify_launch<float, uint2>(img, out, B, C, Hh, Ww, P, st);
+        else patchify_launch<float, uint32_t>(img, out, B, C, Hh, Ww, P, st);
+    } else {
+        if (vb == 16) patchify_launch<__nv_bfloat16, uint4>(img, out, B, C, Hh, Ww, P, st);
+        else if (vb == 8) patchify_launch<__nv_bfloat16, uint2>(img, out, B, C, Hh, Ww, P, st);
+        else if (vb == 4) patchify_launch<__nv_bfloat16, uint32_t>(img, out, B, C, Hh, Ww, P, st);
+        else patchify_launch<__nv_bfloat16, uint16_t>(img, out, B, C, Hh, Ww, P, st);
+    }
     CONVNN_CHECK_LAUNCH("patchify");
     return CONVNN_OK;
 }
