@@ -154,6 +154,10 @@ int convnn_b200_device_status(int* code) {
     return CONVNN_OK;
 }
 
+int convnn_b200_debug_gemm_trace(int enable, uint64_t* host_out, int n) {
+    return gemm_tc_trace(enable, reinterpret_cast<unsigned long long*>(host_out), n);
+}
+
 uint64_t convnn_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int convnn_b200_head_channels(const convnn_desc* d) {

@@ -92,6 +92,7 @@ int launch_sim_topk_tc(const convnn_desc* d, const Dims& dm, const void* q, cons
                        const float* kstat, const int32_t* cand, int32_t* idx, float* val, cudaStream_t st);
 int read_sim_topk_status(int* out);
 int read_gemm_tc_status(int* out);
+int gemm_tc_trace(int enable, unsigned long long* host_out, int n);
 // bfloat16 tensor-core GEMM C = A W^T (+bias, +GELU); `parts` outputs share M and split N evenly.
 bool gemm_tc_supported(const void* a, long long lda, const void* w, int Kd, int N, int parts, const void* const* c,
                        long long ldc);

@@ -8,7 +8,9 @@
 // (n fastest, so the CTAs of a wave share a handful of A row blocks and all of W in L2):
 //   warp 0     TMA producer, 4-stage ring of (A chunk, W chunk) pairs
 //   warp 1     MMA issuer, fp32 accumulators double-buffered in TMEM
-//   warps 2-5  epilogue: tcgen05.ld -> (+bias, GELU) -> bf16 -> 16-byte global stores
+//   warps 2-5  epilogue of the even tiles (TMEM buffer 0), warps 6-9 of the odd tiles (buffer
+//              1): tcgen05.ld -> (+bias, GELU) -> bf16 -> swizzled shared-memory slab ->
+//              coalesced 16-byte global stores (+ residual); two tiles drain concurrently
 // The N range may be split into up to three equal parts with their own output tensors,
 // which lets one launch produce k, v and q from the packed [W_k; W_v; W_q].
 // Every mbarrier wait is bounded (see sm100.cuh); an expiry latches the device status.
@@ -19,13 +21,18 @@ namespace convnn {
 
 __device__ int g_gemm_tc_status = 0;   // error latch of this translation unit
 
+// Pipeline trace (diagnostic): when enabled, CTA 0 records SM clock stamps of its producer,
+// MMA and epilogue events; four regions of 512 slots (producer, MMA, epilogue half 0 / 1).
+__device__ int g_gemm_trace_on = 0;
+__device__ unsigned long long g_gemm_trace[4 * 512];
+
 namespace {
 
 using namespace sm100;
 
 constexpr int BM = 128;
 constexpr int STAGES = 4;
-constexpr int NTHREADS = 192;
+constexpr int NTHREADS = 320;    // TMA warp, MMA warp, 2 x 4 epilogue warps
 
 struct GemmTcParams {
     __nv_bfloat16* c[3];
@@ -47,43 +54,57 @@ __device__ __forceinline__ void fail(volatile int* abort_flag, int code) {
     atomicCAS(&g_gemm_tc_status, 0, code);
 }
 
+__device__ __forceinline__ void trace(bool on, int region, int& n) {
+    if (on && n < 512) g_gemm_trace[region * 512 + n++] = clock64();
+}
+
 __device__ __forceinline__ float gelu_exact(float x) {
     return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
 }
 
 // Epilogue, phase A (thread = one output row): 32 fp32 accumulators (+bias, GELU) -> bf16,
 // written as four 16-byte slots into this warp's 32 x 64-byte staging slab.  Slot s of row
-// l lands in physical slot s ^ ((l >> 1) & 3), which makes both this row-wise write and the
-// 8-rows-per-instruction read-back of phase B free of bank conflicts.  Returns the sum of
-// squares of the ROUNDED values (the statistic is defined on what is stored).
-__device__ __forceinline__ float stage_chunk(uint8_t* slab, int lane, const uint32_t (&acc)[32],
-                                             const __nv_bfloat16* bias, int bias_valid, int gelu) {
-    float ss = 0.f;
+// l lands in physical slot s ^ ((l >> 1) & 3) (precomputed in `sts`), which makes both this
+// row-wise write and the 8-rows-per-instruction read-back of phase B free of bank
+// conflicts.  With STAT it returns the sum of squares of the ROUNDED values (the statistic
+// is defined on what is stored), accumulated in four independent partial sums.
+template <bool STAT, bool BIAS, bool GELU>
+__device__ __forceinline__ float stage_chunk(const uint32_t (&sts)[4], const uint32_t (&acc)[32],
+                                             const __nv_bfloat16* bias, int bias_valid) {
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
-        uint4 packed;
-        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
+        uint32_t pk[4];
         uint4 bv = make_uint4(0, 0, 0, 0);
-        if (bias && g * 8 < bias_valid) bv = *reinterpret_cast<const uint4*>(bias + g * 8);
-        const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&bv);
+        if (BIAS) {
+            if (g * 8 < bias_valid) bv = *reinterpret_cast<const uint4*>(bias + g * 8);
+        }
+        const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             float a = __uint_as_float(acc[g * 8 + 2 * e]);
             float b = __uint_as_float(acc[g * 8 + 2 * e + 1]);
-            const float2 bb = __bfloat1622float2(bh[e]);
-            a += bb.x;
-            b += bb.y;
-            if (gelu) { a = gelu_exact(a); b = gelu_exact(b); }
-            h[e] = __floats2bfloat162_rn(a, b);
-            const float2 r = __bfloat1622float2(h[e]);
-            ss = fmaf(r.x, r.x, ss);
-            ss = fmaf(r.y, r.y, ss);
+            if (BIAS) {
+                a += __uint_as_float(bw[e] << 16);
+                b += __uint_as_float(bw[e] & 0xffff0000u);
+            }
+            if (GELU) { a = gelu_exact(a); b = gelu_exact(b); }
+            __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+            pk[e] = *reinterpret_cast<uint32_t*>(&h);
+            if (STAT) {
+                const float rx = __uint_as_float(pk[e] << 16), ry = __uint_as_float(pk[e] & 0xffff0000u);
+                if (e & 1) { s2 = fmaf(rx, rx, s2); s3 = fmaf(ry, ry, s3); }
+                else { s0 = fmaf(rx, rx, s0); s1 = fmaf(ry, ry, s1); }
+            }
         }
-        *reinterpret_cast<uint4*>(slab + lane * 64 + ((g ^ ((lane >> 1) & 3)) << 4)) = packed;
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sts[g]), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]),
+                     "r"(pk[3])
+                     : "memory");
     }
-    return ss;
+    return (s0 + s1) + (s2 + s3);
 }
 
+template <bool STAT, bool BIAS, bool GELU, bool RES>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
                const GemmTcParams p) {
@@ -93,8 +114,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const uint32_t a_bytes = BM * pitch, b_bytes = p.BN * pitch;
     uint8_t* sA = smem;
     uint8_t* sB = smem + STAGES * a_bytes;
-    uint8_t* slabs = sB + STAGES * b_bytes;                    // 4 epilogue warps x 2 KB
-    uint64_t* bars = reinterpret_cast<uint64_t*>(slabs + 4 * 2048);
+    uint8_t* slabs = sB + STAGES * b_bytes;                    // 8 epilogue warps x 2 KB
+    uint64_t* bars = reinterpret_cast<uint64_t*>(slabs + 8 * 2048);
     uint64_t* full = bars;
     uint64_t* empty = bars + STAGES;
     uint64_t* tfull = bars + 2 * STAGES;
@@ -132,11 +153,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
+            const bool tr = g_gemm_trace_on && blockIdx.x == 0;
+            int tn = 0;
+            trace(tr, 0, tn);
             for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
                 const int mt = t / p.n_n_tiles, nt = t - mt * p.n_n_tiles;
                 for (int kc = 0; kc < p.KC; ++kc, ++it) {
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
                     if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) { fail(abort_flag, 11); ok = false; break; }
+                    trace(tr, 0, tn);                       // stage free -> loads issued
                     mbar_expect_tx(&full[s], a_bytes + b_bytes);
                     tma_load_2d(sA + s * a_bytes, &tmA, &full[s], kc * p.KCH, mt * BM);
                     tma_load_2d(sB + s * b_bytes, &tmW, &full[s], kc * p.KCH, nt * p.BN);
@@ -148,14 +173,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const uint32_t idesc = make_idesc_bf16_f32(BM, p.BN);
             uint32_t it = 0, tile = 0;
             bool ok = true;
+            const bool tr = g_gemm_trace_on && blockIdx.x == 0;
+            int tn = 0;
             for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x, ++tile) {
                 const uint32_t buf = tile & 1u, u = tile >> 1;
                 if (!mbar_wait(&tempty[buf], (u & 1u) ^ 1u, abort_flag)) { fail(abort_flag, 12); ok = false; break; }
+                trace(tr, 1, tn);                           // accumulator buffer free
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + buf * p.BNpad;
                 for (int kc = 0; kc < p.KC; ++kc, ++it) {
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
                     if (!mbar_wait(&full[s], ph, abort_flag)) { fail(abort_flag, 13); ok = false; break; }
+                    trace(tr, 1, tn);                       // stage landed
                     tc_fence_after_sync();
                     const uint64_t adesc = make_kmajor_desc(smem_u32(sA + s * a_bytes), pitch);
                     const uint64_t bdesc = make_kmajor_desc(smem_u32(sB + s * b_bytes), pitch);
@@ -167,11 +196,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
         }
     } else {
+        const int half = (warp - 2) >> 2;        // which TMEM buffer / tile parity this warp drains
         const int lq = warp & 3;
         const int r = lq * 32 + lane;
-        uint32_t tile = 0;
+        const uint32_t slab = smem_u32(slabs + (warp - 2) * 2048);
+        // shared-memory addresses of this lane's four 16-byte slots, for the row-wise write
+        // (sts) and for the 8-rows-per-instruction read-back (lds), fixed for the whole kernel
+        uint32_t sts[4], lds[4];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            sts[g] = slab + lane * 64 + ((g ^ ((lane >> 1) & 3)) << 4);
+            const int rl = g * 8 + (lane >> 2), sl = lane & 3;
+            lds[g] = slab + rl * 64 + ((sl ^ ((rl >> 1) & 3)) << 4);
+        }
+        uint32_t tile = half;
         bool ok = true;
-        for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x, ++tile) {
+        const bool tr = g_gemm_trace_on && blockIdx.x == 0 && lq == 0 && lane == 0;
+        int tn = 0;
+        for (int t = blockIdx.x + half * gridDim.x; t < p.n_tiles && ok; t += 2 * gridDim.x, tile += 2) {
             const int mt = t / p.n_n_tiles, nt = t - mt * p.n_n_tiles;
             const uint32_t buf = tile & 1u, u = tile >> 1;
             const int row = mt * BM + r;
@@ -181,56 +223,73 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             __nv_bfloat16* cbase = part == 0 ? p.c[0] : (part == 1 ? p.c[1] : p.c[2]);
             float* stat = part == 0 ? p.stat[0] : (part == 1 ? p.stat[1] : p.stat[2]);
             const int ncol = min(p.BN, p.N - n0);             // valid columns of this tile
+            // phase-B pointers of this lane: row g*8 + lane/4 of the warp's slab, columns (lane%4)*8..
+            __nv_bfloat16* optr[4];
+            const __nv_bfloat16* rptr[4];
+            bool rok[4];
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                const int grow = mt * BM + lq * 32 + g * 8 + (lane >> 2);
+                rok[g] = grow < p.M;
+                optr[g] = cbase + (long long)grow * p.ldc + pc0 + (lane & 3) * 8;
+                rptr[g] = RES ? p.residual + (long long)grow * p.ldr + n0 + (lane & 3) * 8 : nullptr;
+            }
+            // statistic bookkeeping without divisions in the chunk loop
+            int head = 0, head_left = 0;
+            long long stat_base = 0;
+            if (STAT) {
+                head = pc0 / p.dk;
+                head_left = p.dk;
+                const int bb = row / p.rows_per_batch, rr = row - bb * p.rows_per_batch;
+                stat_base = (long long)bb * p.heads * p.rows_per_batch + rr;
+            }
             ok = mbar_wait(&tfull[buf], u & 1u, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) { if (lane == 0) fail(abort_flag, 14); break; }
+            trace(tr, 2 + half, tn);                        // accumulator ready
             tc_fence_after_sync();
             const uint32_t taddr = tmem_base + ((uint32_t)(lq * 32) << 16) + buf * p.BNpad;
-            uint8_t* slab = slabs + (warp - 2) * 2048;
-            const int wrow0 = mt * BM + lq * 32;              // first row of this warp's slab
             float ss = 0.f;
-            // TMEM reads run one chunk ahead of the conversion / store work of this warp
-            uint32_t nxt[32];
-            auto issue = [&](int c) {
+            // TMEM reads run one chunk ahead of the conversion / store work (ping-pong registers)
+            uint32_t ra[32], rb[32];
+            auto issue = [&](int c, uint32_t (&dst)[32]) {
                 if (c + 32 <= p.BN) {
-                    tmem_ld_x32(taddr + c, nxt);
+                    tmem_ld_x32(taddr + c, dst);
                 } else {                                      // BN % 32 == 16: upper half is padding
                     uint32_t lo[16];
                     tmem_ld_x16(taddr + c, lo);
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) { nxt[j] = lo[j]; nxt[16 + j] = 0u; }
+                    for (int j = 0; j < 16; ++j) { dst[j] = lo[j]; dst[16 + j] = 0u; }
                 }
             };
-            issue(0);
-            for (int c = 0; c < p.BN; c += 32) {
-                uint32_t acc[32];
-                tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 32; ++j) acc[j] = nxt[j];
-                if (c + 32 < p.BN) issue(c + 32);
-                const float chunk_ss = stage_chunk(slab, lane, acc, p.bias ? p.bias + n0 + c : nullptr, ncol - c, p.gelu);
-                if (stat) {
-                    ss += chunk_ss;
-                    if ((pc0 + c + 32) % p.dk == 0) {         // chunk ends a head (dk % 32 == 0)
-                        if (row < p.M) {
-                            const int hh = (pc0 + c) / p.dk;
-                            const int bb = row / p.rows_per_batch, rr = row - bb * p.rows_per_batch;
-                            stat[((long long)bb * p.heads + hh) * p.rows_per_batch + rr] =
-                                p.stat_mode == CONVNN_COSINE ? 1.0f / fmaxf(sqrtf(ss), 1e-12f) : ss;
+            auto finish = [&](int c, const uint32_t (&acc)[32]) {
+                const float css = stage_chunk<STAT, BIAS, GELU>(sts, acc, BIAS ? p.bias + n0 + c : nullptr, ncol - c);
+                if (STAT) {
+                    if (stat) {
+                        ss += css;
+                        head_left -= 32;
+                        if (head_left == 0) {                 // chunk ends a head (dk % 32 == 0)
+                            if (row < p.M)
+                                stat[stat_base + (long long)head * p.rows_per_batch] =
+                                    p.stat_mode == CONVNN_COSINE ? 1.0f / fmaxf(sqrtf(ss), 1e-12f) : ss;
+                            ss = 0.f;
+                            head_left = p.dk;
+                            ++head;
                         }
-                        ss = 0.f;
                     }
                 }
                 __syncwarp();
                 // phase B: 8 rows x 64 bytes per instruction, coalesced
+                const bool cok = c + (lane & 3) * 8 < ncol;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int rl = i * 8 + (lane >> 2), sl = lane & 3;
-                    const int grow = wrow0 + rl, gcol = c + sl * 8;
-                    uint4 v = *reinterpret_cast<const uint4*>(slab + rl * 64 + ((sl ^ ((rl >> 1) & 3)) << 4));
-                    if (grow < p.M && gcol < ncol) {
-                        if (p.residual) {
-                            const uint4 rv = *reinterpret_cast<const uint4*>(p.residual + (long long)grow * p.ldr + n0 + gcol);
+                for (int g = 0; g < 4; ++g) {
+                    uint32_t v0, v1, v2, v3;
+                    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3)
+                                 : "r"(lds[g]) : "memory");
+                    if (rok[g] && cok) {
+                        uint4 v = make_uint4(v0, v1, v2, v3);
+                        if (RES) {
+                            const uint4 rv = *reinterpret_cast<const uint4*>(rptr[g] + c);
                             __nv_bfloat162* vh = reinterpret_cast<__nv_bfloat162*>(&v);
                             const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&rv);
 #pragma unroll
@@ -239,14 +298,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                                 vh[e] = __floats2bfloat162_rn(a.x + b2.x, a.y + b2.y);
                             }
                         }
-                        *reinterpret_cast<uint4*>(cbase + (long long)grow * p.ldc + pc0 + gcol) = v;
+                        *reinterpret_cast<uint4*>(optr[g] + c) = v;
                     }
                 }
                 __syncwarp();
+            };
+            issue(0, ra);
+            for (int c = 0; c < p.BN; c += 64) {
+                tmem_ld_wait();
+                if (c + 32 < p.BN) issue(c + 32, rb);
+                finish(c, ra);
+                if (c + 32 < p.BN) {
+                    tmem_ld_wait();
+                    if (c + 64 < p.BN) issue(c + 64, ra);
+                    finish(c + 32, rb);
+                }
             }
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&tempty[buf]);
+            trace(tr, 2 + half, tn);                        // tile drained
         }
     }
 
@@ -326,15 +397,44 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
     if (!encode_tensor_map_bf16(&tmA, a, 2, dimsA, strA, boxA, pitch)) return CONVNN_E_CUDA;
     if (!encode_tensor_map_bf16(&tmW, w, 2, dimsW, strW, boxW, pitch)) return CONVNN_E_CUDA;
 
-    const size_t smem = 1024 + (size_t)STAGES * (BM + p.BN) * pitch + 4 * 2048 + (2 * STAGES + 4) * 8 + 16;
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return set_error(CONVNN_E_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    const size_t smem = 1024 + (size_t)STAGES * (BM + p.BN) * pitch + 8 * 2048 + (2 * STAGES + 4) * 8 + 16;
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int grid = p.n_tiles < sms ? p.n_tiles : sms;
-    gemm_tc_kernel<<<grid, NTHREADS, smem, st>>>(tmA, tmW, p);
+    const bool has_stat = p.stat[0] || p.stat[1] || p.stat[2];
+    if (has_stat && (p.bias || p.residual || p.gelu))
+        return set_error(CONVNN_E_UNSUPPORTED, "gemm_tc: statistics cannot be combined with bias / GELU / residual");
+    if (p.gelu && p.residual) return set_error(CONVNN_E_UNSUPPORTED, "gemm_tc: GELU with a residual is not built");
+#define CONVNN_GEMM_LAUNCH(S, B, G, R)                                                                      \
+    do {                                                                                                    \
+        auto kern = gemm_tc_kernel<S, B, G, R>;                                                             \
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (e != cudaSuccess) return set_error(CONVNN_E_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e)); \
+        kern<<<grid, NTHREADS, smem, st>>>(tmA, tmW, p);                                                    \
+    } while (0)
+    if (has_stat) CONVNN_GEMM_LAUNCH(true, false, false, false);
+    else if (p.gelu) { if (p.bias) CONVNN_GEMM_LAUNCH(false, true, true, false); else CONVNN_GEMM_LAUNCH(false, false, true, false); }
+    else if (p.bias && p.residual) CONVNN_GEMM_LAUNCH(false, true, false, true);
+    else if (p.bias) CONVNN_GEMM_LAUNCH(false, true, false, false);
+    else if (p.residual) CONVNN_GEMM_LAUNCH(false, false, false, true);
+    else CONVNN_GEMM_LAUNCH(false, false, false, false);
+#undef CONVNN_GEMM_LAUNCH
     CONVNN_CHECK_LAUNCH("gemm_tc");
+    return CONVNN_OK;
+}
+
+int gemm_tc_trace(int enable, unsigned long long* host_out, int n) {
+    cudaError_t e = cudaSuccess;
+    if (host_out && n > 0) {
+        if (n > 4 * 512) n = 4 * 512;
+        e = cudaMemcpyFromSymbol(host_out, g_gemm_trace, sizeof(unsigned long long) * n);
+        if (e != cudaSuccess) return set_error(CONVNN_E_CUDA, "cudaMemcpyFromSymbol: %s", cudaGetErrorString(e));
+    }
+    static const unsigned long long zeros[4 * 512] = {0};
+    e = cudaMemcpyToSymbol(g_gemm_trace, zeros, sizeof(zeros));
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_gemm_trace_on, &enable, sizeof(int));
+    if (e != cudaSuccess) return set_error(CONVNN_E_CUDA, "cudaMemcpyToSymbol: %s", cudaGetErrorString(e));
     return CONVNN_OK;
 }
 

@@ -99,6 +99,12 @@ uint64_t convnn_b200_launch_count(void);
  * latched a code are undefined. */
 int convnn_b200_device_status(int* code);
 
+/* No reference counterpart: pipeline trace of the tensor-core GEMM (diagnostic).  Copies up
+ * to 2048 recorded SM clock stamps of CTA 0 to `host_out` (HOST memory; four regions of 512:
+ * producer, MMA issuer, epilogue halves), clears the trace and sets recording on or off.
+ * Synchronises the device. */
+int convnn_b200_debug_gemm_trace(int enable, uint64_t* host_out, int n);
+
 /* Channels per head as stored in q/k/v (Cp above). Negative status on a bad descriptor. */
 int convnn_b200_head_channels(const convnn_desc* d);
 
