@@ -31,7 +31,7 @@ namespace {
 using namespace sm100;
 
 constexpr int BM = 128;
-constexpr int STAGES = 4;
+constexpr int MAX_STAGES = 8;
 constexpr int NTHREADS = 320;    // TMA warp, MMA warp, 2 x 4 epilogue warps
 
 struct GemmTcParams {
@@ -47,6 +47,9 @@ struct GemmTcParams {
     int M, N, gelu;
     int KCH, KC, BN, BNpad;
     int n_m_tiles, n_n_tiles, n_tiles;
+    int stages;            // depth of the shared-memory ring
+    int wstat;             // 1: the whole W tile (BN x Kd) stays in shared memory; the ring holds A only
+    int tiles_per_cta;     // wstat: each CTA owns a contiguous range of the n-major tile list
 };
 
 __device__ __forceinline__ void fail(volatile int* abort_flag, int code) {
@@ -112,22 +115,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t pitch = p.KCH * 2;
     const uint32_t a_bytes = BM * pitch, b_bytes = p.BN * pitch;
-    uint8_t* sA = smem;
-    uint8_t* sB = smem + STAGES * a_bytes;
-    uint8_t* slabs = sB + STAGES * b_bytes;                    // 8 epilogue warps x 2 KB
+    const uint32_t STAGES = p.stages;
+    uint8_t* sA = smem;                                        // [STAGES][128 x KCH]
+    uint8_t* sB = smem + STAGES * a_bytes;                     // ring [STAGES] or resident [KC] chunks of W
+    uint8_t* slabs = sB + (p.wstat ? p.KC : STAGES) * b_bytes; // 8 epilogue warps x 2 KB
     uint64_t* bars = reinterpret_cast<uint64_t*>(slabs + 8 * 2048);
     uint64_t* full = bars;
-    uint64_t* empty = bars + STAGES;
-    uint64_t* tfull = bars + 2 * STAGES;
+    uint64_t* empty = bars + MAX_STAGES;
+    uint64_t* tfull = bars + 2 * MAX_STAGES;
     uint64_t* tempty = tfull + 2;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+    uint64_t* wfull = tempty + 2;                              // resident W tile landed
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(wfull + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t ncols = 2u * p.BNpad;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < MAX_STAGES; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
@@ -135,6 +140,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             mbar_init(&tfull[b], 1);
             mbar_init(&tempty[b], 4);
         }
+        mbar_init(wfull, 1);
         *abort_flag = 0;
         fence_barrier_init();
         prefetch_tensormap(&tmA);
@@ -149,50 +155,93 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
+    // Tile order.  Streaming mode: tile k of this CTA is blockIdx.x + k * gridDim.x in the m-major
+    // list (n fastest).  W-resident mode: a contiguous range of the n-major list (m fastest), so
+    // the W tile changes at most a few times per CTA.
+    const int first = p.wstat ? blockIdx.x * p.tiles_per_cta : blockIdx.x;
+    const int step = p.wstat ? 1 : gridDim.x;
+    const int last = p.wstat ? min(first + p.tiles_per_cta, p.n_tiles) : p.n_tiles;
+    auto tile_mn = [&](int t, int& mt, int& nt) {
+        if (p.wstat) { nt = t / p.n_m_tiles; mt = t - nt * p.n_m_tiles; }
+        else { mt = t / p.n_n_tiles; nt = t - mt * p.n_n_tiles; }
+    };
+
+    const uint32_t full0 = smem_u32(full), empty0 = smem_u32(empty), wfull_a = smem_u32(wfull);
+    const uint32_t sA0 = smem_u32(sA), sB0 = smem_u32(sB);
+
     if (warp == 0) {
         if (lane == 0) {
-            uint32_t it = 0;
+            uint32_t s = 0, ph = 0, wloads = 0;      // ring slot and its phase, advanced incrementally
+            uint32_t last_s = 0, last_ph = 0;
+            bool any = false;
+            int cur_nt = -1;
             bool ok = true;
             const bool tr = g_gemm_trace_on && blockIdx.x == 0;
             int tn = 0;
             trace(tr, 0, tn);
-            for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
-                const int mt = t / p.n_n_tiles, nt = t - mt * p.n_n_tiles;
-                for (int kc = 0; kc < p.KC; ++kc, ++it) {
-                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-                    if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) { fail(abort_flag, 11); ok = false; break; }
-                    trace(tr, 0, tn);                       // stage free -> loads issued
-                    mbar_expect_tx(&full[s], a_bytes + b_bytes);
-                    tma_load_2d(sA + s * a_bytes, &tmA, &full[s], kc * p.KCH, mt * BM);
-                    tma_load_2d(sB + s * b_bytes, &tmW, &full[s], kc * p.KCH, nt * p.BN);
+            const uint32_t tx = a_bytes + (p.wstat ? 0u : b_bytes);
+            for (int t = first; t < last && ok; t += step) {
+                int mt, nt;
+                tile_mn(t, mt, nt);
+                if (p.wstat && nt != cur_nt) {
+                    // every MMA that reads the old W tile has completed once the most recently
+                    // filled ring stage has been released
+                    if (any && !mbar_wait_a(empty0 + 8 * last_s, last_ph, abort_flag)) { fail(abort_flag, 15); ok = false; break; }
+                    mbar_expect_tx_a(wfull_a, p.KC * b_bytes);
+                    for (int kc = 0; kc < p.KC; ++kc)
+                        tma_load_2d_a(sB0 + kc * b_bytes, &tmW, wfull_a, kc * p.KCH, nt * p.BN);
+                    cur_nt = nt;
+                    ++wloads;
+                }
+                trace(tr, 0, tn);
+                const int m0 = mt * BM, n0 = nt * p.BN;
+                for (int kc = 0; kc < p.KC; ++kc) {
+                    if (!mbar_wait_a(empty0 + 8 * s, ph ^ 1u, abort_flag)) { fail(abort_flag, 11); ok = false; break; }
+                    mbar_expect_tx_a(full0 + 8 * s, tx);
+                    tma_load_2d_a(sA0 + s * a_bytes, &tmA, full0 + 8 * s, kc * p.KCH, m0);
+                    if (!p.wstat) tma_load_2d_a(sB0 + s * b_bytes, &tmW, full0 + 8 * s, kc * p.KCH, n0);
+                    last_s = s; last_ph = ph; any = true;
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = make_idesc_bf16_f32(BM, p.BN);
-            uint32_t it = 0, tile = 0;
+            const uint64_t dhi = kmajor_desc_hi(pitch);
+            const int nk16 = p.KCH / 16;
+            const uint32_t tfull0 = smem_u32(tfull), tempty0 = smem_u32(tempty);
+            uint32_t s = 0, ph = 0, tile = 0, wloads = 0;
+            int cur_nt = -1;
             bool ok = true;
             const bool tr = g_gemm_trace_on && blockIdx.x == 0;
             int tn = 0;
-            for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x, ++tile) {
+            for (int t = first; t < last && ok; t += step, ++tile) {
                 const uint32_t buf = tile & 1u, u = tile >> 1;
-                if (!mbar_wait(&tempty[buf], (u & 1u) ^ 1u, abort_flag)) { fail(abort_flag, 12); ok = false; break; }
+                if (!mbar_wait_a(tempty0 + 8 * buf, (u & 1u) ^ 1u, abort_flag)) { fail(abort_flag, 12); ok = false; break; }
                 trace(tr, 1, tn);                           // accumulator buffer free
+                if (p.wstat) {
+                    int mt, nt;
+                    tile_mn(t, mt, nt);
+                    if (nt != cur_nt) {
+                        if (!mbar_wait_a(wfull_a, wloads & 1u, abort_flag)) { fail(abort_flag, 16); ok = false; break; }
+                        cur_nt = nt;
+                        ++wloads;
+                    }
+                }
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + buf * p.BNpad;
-                for (int kc = 0; kc < p.KC; ++kc, ++it) {
-                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-                    if (!mbar_wait(&full[s], ph, abort_flag)) { fail(abort_flag, 13); ok = false; break; }
-                    trace(tr, 1, tn);                       // stage landed
+                for (int kc = 0; kc < p.KC; ++kc) {
+                    if (!mbar_wait_a(full0 + 8 * s, ph, abort_flag)) { fail(abort_flag, 13); ok = false; break; }
                     tc_fence_after_sync();
-                    const uint64_t adesc = make_kmajor_desc(smem_u32(sA + s * a_bytes), pitch);
-                    const uint64_t bdesc = make_kmajor_desc(smem_u32(sB + s * b_bytes), pitch);
-                    for (int k16 = 0; k16 < p.KCH / 16; ++k16)
-                        mma_bf16_ss(d_tmem, adesc + 2u * k16, bdesc + 2u * k16, idesc, (kc | k16) != 0);
-                    mma_commit(&empty[s]);
+                    const uint64_t adesc = dhi | (uint64_t)((sA0 + s * a_bytes) >> 4);
+                    const uint64_t bdesc = dhi | (uint64_t)((sB0 + (p.wstat ? (uint32_t)kc : s) * b_bytes) >> 4);
+                    mma_chunk(d_tmem, adesc, bdesc, idesc, nk16, kc != 0);
+                    mma_commit_a(empty0 + 8 * s);
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
                 }
-                if (ok) mma_commit(&tfull[buf]);
+                if (ok) mma_commit_a(tfull0 + 8 * buf);
+                trace(tr, 1, tn);                           // tile issued
             }
         }
     } else {
@@ -213,8 +262,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         bool ok = true;
         const bool tr = g_gemm_trace_on && blockIdx.x == 0 && lq == 0 && lane == 0;
         int tn = 0;
-        for (int t = blockIdx.x + half * gridDim.x; t < p.n_tiles && ok; t += 2 * gridDim.x, tile += 2) {
-            const int mt = t / p.n_n_tiles, nt = t - mt * p.n_n_tiles;
+        for (int t = first + half * step; t < last && ok; t += 2 * step, tile += 2) {
+            int mt, nt;
+            tile_mn(t, mt, nt);
             const uint32_t buf = tile & 1u, u = tile >> 1;
             const int row = mt * BM + r;
             const int n0 = nt * p.BN;
@@ -397,11 +447,30 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
     if (!encode_tensor_map_bf16(&tmA, a, 2, dimsA, strA, boxA, pitch)) return CONVNN_E_CUDA;
     if (!encode_tensor_map_bf16(&tmW, w, 2, dimsW, strW, boxW, pitch)) return CONVNN_E_CUDA;
 
-    const size_t smem = 1024 + (size_t)STAGES * (BM + p.BN) * pitch + 8 * 2048 + (2 * STAGES + 4) * 8 + 16;
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const int grid = p.n_tiles < sms ? p.n_tiles : sms;
+    // W-resident mode when the whole BN x Kd tile of W fits beside a useful ring of A chunks and
+    // a CTA sees several row tiles per W tile; otherwise both operands stream through the ring.
+    const size_t fixed = 1024 + 8 * 2048 + (2 * MAX_STAGES + 5) * 8 + 16;
+    const size_t budget = 200 * 1024;
+    const size_t a_bytes = (size_t)BM * pitch, b_bytes = (size_t)p.BN * pitch;
+    const size_t w_tile = (size_t)p.KC * b_bytes;
+    p.wstat = (w_tile + 3 * a_bytes + fixed <= budget && p.n_tiles >= 2 * sms) ? 1 : 0;
+    int grid;
+    size_t smem;
+    if (p.wstat) {
+        p.tiles_per_cta = (p.n_tiles + sms - 1) / sms;
+        grid = (p.n_tiles + p.tiles_per_cta - 1) / p.tiles_per_cta;
+        int st_a = (int)((budget - fixed - w_tile) / a_bytes);
+        p.stages = st_a > MAX_STAGES ? MAX_STAGES : st_a;
+        smem = fixed + w_tile + (size_t)p.stages * a_bytes;
+    } else {
+        grid = p.n_tiles < sms ? p.n_tiles : sms;
+        int st_ab = (int)((budget - fixed) / (a_bytes + b_bytes));
+        p.stages = st_ab > 6 ? 6 : (st_ab < 2 ? 2 : st_ab);
+        smem = fixed + (size_t)p.stages * (a_bytes + b_bytes);
+    }
     const bool has_stat = p.stat[0] || p.stat[1] || p.stat[2];
     if (has_stat && (p.bias || p.residual || p.gelu))
         return set_error(CONVNN_E_UNSUPPORTED, "gemm_tc: statistics cannot be combined with bias / GELU / residual");

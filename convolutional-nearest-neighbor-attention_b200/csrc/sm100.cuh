@@ -53,6 +53,46 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     return false;
 }
 
+// Variants on raw shared-memory addresses for the single-thread producer / MMA loops, whose
+// instruction count per pipeline step is what bounds the whole kernel's issue rate.
+__device__ __forceinline__ bool mbar_try_wait_a(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_a(uint32_t bar, uint32_t parity, volatile int* abort) {
+    if (mbar_try_wait_a(bar, parity)) return true;          // common case: already complete
+    for (uint32_t i = 0; i < kWaitLimit; ++i) {
+        if (mbar_try_wait_a(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort) return false;
+    }
+    return false;
+}
+__device__ __forceinline__ void mbar_expect_tx_a(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mma_commit_a(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_a(uint32_t dst, const CUtensorMap* m, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_4d_a(uint32_t dst, const CUtensorMap* m, uint32_t bar, int c0, int c1, int c2,
+                                              int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
 // ---- TMA -----------------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
@@ -142,6 +182,24 @@ __device__ __forceinline__ void mma_bf16_ss(uint32_t tmem_d, uint64_t adesc, uin
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                  : "memory");
+}
+
+// Constant upper part of a K-major descriptor (everything except the start address).
+__device__ __forceinline__ uint64_t kmajor_desc_hi(uint32_t pitch) {
+    const uint64_t layout = pitch == 128 ? 2 : (pitch == 64 ? 4 : 6);
+    return ((uint64_t)1 << 16) | ((uint64_t)((8u * pitch) >> 4) << 32) | ((uint64_t)1 << 46) | (layout << 61);
+}
+// Four (or fewer) K = 16 steps of one shared-memory chunk, straight-line.
+__device__ __forceinline__ void mma_chunk(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, int nk16,
+                                          uint32_t accumulate_first) {
+    mma_bf16_ss(d_tmem, adesc, bdesc, idesc, accumulate_first);
+    if (nk16 == 4) {
+        mma_bf16_ss(d_tmem, adesc + 2, bdesc + 2, idesc, 1);
+        mma_bf16_ss(d_tmem, adesc + 4, bdesc + 4, idesc, 1);
+        mma_bf16_ss(d_tmem, adesc + 6, bdesc + 6, idesc, 1);
+    } else if (nk16 == 2) {
+        mma_bf16_ss(d_tmem, adesc + 2, bdesc + 2, idesc, 1);
+    }
 }
 
 // ---- TMEM -> registers ---------------------------------------------------------------
