@@ -159,24 +159,29 @@ sim_topk_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
+    const uint32_t full0 = smem_u32(full), empty0 = smem_u32(empty);
+    const uint32_t st0 = smem_u32(stages);
+
     if (warp == 0) {
         if (lane == 0) {
-            uint32_t it = 0;
+            uint32_t s = 0, ph = 0;                  // ring slot and phase, advanced incrementally
             bool ok = true;
             for (int unit = blockIdx.x; unit < p.n_units && ok; unit += gridDim.x) {
                 const int bh = unit / p.n_pairs, pp = unit - bh * p.n_pairs;
                 const int b = bh / p.H, h = bh - b * p.H;
                 const int row0 = pp * 2 * BM;
                 const bool has1 = row0 + BM < p.T;
+                const uint32_t tx = (has1 ? 2u : 1u) * a_bytes + b_bytes;
                 for (int ct = 0; ct < p.n_col_tiles && ok; ++ct) {
-                    for (int kc = 0; kc < p.KC; ++kc, ++it) {
-                        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-                        if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) { fail(abort_flag, 1); ok = false; break; }
-                        uint8_t* st = stages + s * stage_bytes;
-                        mbar_expect_tx(&full[s], (has1 ? 2 : 1) * a_bytes + b_bytes);
-                        tma_load_4d(st, &tmK, &full[s], kc * p.KCH, h, row0, b);
-                        if (has1) tma_load_4d(st + a_bytes, &tmK, &full[s], kc * p.KCH, h, row0 + BM, b);
-                        tma_load_4d(st + 2 * a_bytes, &tmQ, &full[s], kc * p.KCH, h, ct * p.BN, b);
+                    const int col0 = ct * p.BN;
+                    for (int kc = 0; kc < p.KC; ++kc) {
+                        if (!mbar_wait_a(empty0 + 8 * s, ph ^ 1u, abort_flag)) { fail(abort_flag, 1); ok = false; break; }
+                        const uint32_t st = st0 + s * stage_bytes, fb = full0 + 8 * s;
+                        mbar_expect_tx_a(fb, tx);
+                        tma_load_4d_a(st, &tmK, fb, kc * p.KCH, h, row0, b);
+                        if (has1) tma_load_4d_a(st + a_bytes, &tmK, fb, kc * p.KCH, h, row0 + BM, b);
+                        tma_load_4d_a(st + 2 * a_bytes, &tmQ, fb, kc * p.KCH, h, col0, b);
+                        if (++s == STAGES) { s = 0; ph ^= 1u; }
                     }
                 }
             }
@@ -184,33 +189,33 @@ sim_topk_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = make_idesc_bf16_f32(BM, p.BN);
-            uint32_t it = 0, tile = 0;
+            const uint64_t dhi = kmajor_desc_hi(pitch);
+            const int nk16 = p.KCH / 16;
+            const uint32_t tfull0 = smem_u32(tfull), tempty0 = smem_u32(tempty);
+            uint32_t s = 0, ph = 0, tile = 0;
             bool ok = true;
             for (int unit = blockIdx.x; unit < p.n_units && ok; unit += gridDim.x) {
                 const int pp = unit % p.n_pairs;
                 const bool has1 = pp * 2 * BM + BM < p.T;
                 for (int ct = 0; ct < p.n_col_tiles && ok; ++ct, ++tile) {
                     const uint32_t par = tile & 1u, u = tile >> 1;
-                    if (!mbar_wait(&tempty[par], (u & 1u) ^ 1u, abort_flag)) { fail(abort_flag, 2); ok = false; break; }
+                    if (!mbar_wait_a(tempty0 + 8 * par, (u & 1u) ^ 1u, abort_flag)) { fail(abort_flag, 2); ok = false; break; }
                     tc_fence_after_sync();
-                    const uint32_t d0 = tmem_base + (0 * 2 + par) * p.BNpad;
-                    const uint32_t d1 = tmem_base + (1 * 2 + par) * p.BNpad;
-                    for (int kc = 0; kc < p.KC; ++kc, ++it) {
-                        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-                        if (!mbar_wait(&full[s], ph, abort_flag)) { fail(abort_flag, 3); ok = false; break; }
+                    const uint32_t d0 = tmem_base + par * p.BNpad;
+                    const uint32_t d1 = tmem_base + (2 + par) * p.BNpad;
+                    for (int kc = 0; kc < p.KC; ++kc) {
+                        if (!mbar_wait_a(full0 + 8 * s, ph, abort_flag)) { fail(abort_flag, 3); ok = false; break; }
                         tc_fence_after_sync();
-                        const uint32_t sa = smem_u32(stages + s * stage_bytes);
-                        const uint64_t a0 = make_kmajor_desc(sa, pitch);
-                        const uint64_t a1 = make_kmajor_desc(sa + a_bytes, pitch);
-                        const uint64_t bd = make_kmajor_desc(sa + 2 * a_bytes, pitch);
-                        for (int k16 = 0; k16 < p.KCH / 16; ++k16)
-                            mma_bf16_ss(d0, a0 + 2u * k16, bd + 2u * k16, idesc, (kc | k16) != 0);
-                        if (has1)
-                            for (int k16 = 0; k16 < p.KCH / 16; ++k16)
-                                mma_bf16_ss(d1, a1 + 2u * k16, bd + 2u * k16, idesc, (kc | k16) != 0);
-                        mma_commit(&empty[s]);
+                        const uint32_t sa = st0 + s * stage_bytes;
+                        const uint64_t a0 = dhi | (uint64_t)(sa >> 4);
+                        const uint64_t a1 = dhi | (uint64_t)((sa + a_bytes) >> 4);
+                        const uint64_t bd = dhi | (uint64_t)((sa + 2 * a_bytes) >> 4);
+                        mma_chunk(d0, a0, bd, idesc, nk16, kc != 0);
+                        if (has1) mma_chunk(d1, a1, bd, idesc, nk16, kc != 0);
+                        mma_commit_a(empty0 + 8 * s);
+                        if (++s == STAGES) { s = 0; ph ^= 1u; }
                     }
-                    if (ok) mma_commit(&tfull[par]);
+                    if (ok) mma_commit_a(tfull0 + 8 * par);
                 }
             }
         }
