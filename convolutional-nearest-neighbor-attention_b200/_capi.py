@@ -49,6 +49,9 @@ SIGNATURES = {
                                             c_void, c_void]),
     "convnn_b200_forward": (ctypes.c_int, [ctypes.POINTER(ConvnnDesc), c_void, c_i64, c_void, c_void, c_void, c_void,
                                            c_void, c_void, c_i64, c_void, c_i64, c_void, c_size, c_void]),
+    "convnn_b200_noalloc_capacity": (c_size, []),
+    "convnn_b200_forward_noalloc": (ctypes.c_int, [ctypes.POINTER(ConvnnDesc), c_void, c_i64, c_void, c_void, c_void,
+                                                   c_void, c_void, c_void, c_i64, c_void, c_i64, c_void]),
     "convnn_b200_layernorm": (ctypes.c_int, [ctypes.c_int, c_void, c_i64, c_void, c_void, ctypes.c_float, c_void,
                                              c_i64, c_i64, c_i32, c_void]),
     "convnn_b200_linear": (ctypes.c_int, [ctypes.c_int, c_void, c_i64, c_void, c_void, c_void, c_i64, c_void, c_i64,

@@ -158,6 +158,27 @@ int convnn_b200_forward(const convnn_desc* d, const void* x, int64_t ldx, const 
                         void* out, int64_t ldo,
                         void* workspace, size_t workspace_bytes, void* stream);
 
+/* No counterpart in the reference (which allocates its temporaries freely through PyTorch).
+ * The same forward as convnn_b200_forward for callers that cannot provide a workspace because
+ * they must not allocate device memory where they call from: inside a stream capture or a
+ * serving loop in which cudaMalloc would stall the device, from a plugin whose host owns the
+ * allocator, or on a GPU whose memory was handed out in full beforehand.  The intermediates
+ * live in a fixed array inside the library's device image: convnn_b200_noalloc_capacity()
+ * bytes (32 MiB), held by every GPU that loads the library until the process exits.  The
+ * call allocates and frees nothing.  A descriptor whose convnn_b200_workspace_bytes()
+ * exceeds the capacity is refused with CONVNN_E_WORKSPACE.
+ *   - The first call on each device looks the array's device address up (with that device
+ *     current); make that first call outside any stream capture.
+ *   - All calls on a device share the one array and it keeps the previous call's contents.
+ *     Every intermediate is written before it is read, so nothing has to be cleared, but two
+ *     calls that overlap on the GPU (different streams, or graph branches) race on it: keep
+ *     calls on one device stream-ordered. */
+size_t convnn_b200_noalloc_capacity(void);
+int convnn_b200_forward_noalloc(const convnn_desc* d, const void* x, int64_t ldx, const void* w_qkv,
+                                const void* w_conv, const void* w_pw, const void* w_o,
+                                const int32_t* cand, const void* residual, int64_t ldr,
+                                void* out, int64_t ldo, void* stream);
+
 /* ---- callers of the hot path: the rest of the reference's TransformerEncoder / ViT ----
  * dtype is a convnn_dtype; all pointers are device pointers in that type. */
 
