@@ -1,9 +1,8 @@
 // convnn_b200_forward_noalloc: the whole-layer forward for callers that cannot hand the
 // library a workspace because they are not allowed to allocate device memory at the point
-// of the call -- code running inside a CUDA stream capture or a latency-critical serving
-// loop where cudaMalloc would synchronise the device, plugins of a host runtime that owns
-// the allocator and exposes no allocation hook, and processes on a GPU whose memory has
-// been fully handed out up front.  Instead of a caller-provided workspace, the layer's
+// of the call -- a latency-critical serving loop where cudaMalloc would synchronise the
+// device, plugins of a host runtime that owns the allocator and exposes no allocation hook,
+// and processes on a GPU whose memory has been fully handed out up front.  Instead of a caller-provided workspace, the layer's
 // intermediates (q, k, v, statistics, neighbour lists, conv output, stage scratch) live in
 // one fixed array that is part of the library's device image.
 #include <mutex>

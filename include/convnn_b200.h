@@ -160,9 +160,9 @@ int convnn_b200_forward(const convnn_desc* d, const void* x, int64_t ldx, const 
 
 /* No counterpart in the reference (which allocates its temporaries freely through PyTorch).
  * The same forward as convnn_b200_forward for callers that cannot provide a workspace because
- * they must not allocate device memory where they call from: inside a stream capture or a
- * serving loop in which cudaMalloc would stall the device, from a plugin whose host owns the
- * allocator, or on a GPU whose memory was handed out in full beforehand.  The intermediates
+ * they must not allocate device memory where they call from: a serving loop in which
+ * cudaMalloc would stall the device, a plugin whose host application owns the allocator, or
+ * a GPU whose memory was handed out in full beforehand.  The intermediates
  * live in a fixed array inside the library's device image: convnn_b200_noalloc_capacity()
  * bytes (32 MiB), held by every GPU that loads the library until the process exits.  The
  * call allocates and frees nothing.  A descriptor whose convnn_b200_workspace_bytes()

@@ -1,8 +1,8 @@
 """The allocation-free forward (convnn_b200_forward_noalloc), collected last on purpose.
 
 Some callers may not allocate device memory at the point where they run the layer (inside a
-stream capture, inside a serving loop where cudaMalloc would stall the GPU, from a plugin
-whose host owns the allocator).  For them the library keeps the layer's intermediates in a
+serving loop where cudaMalloc would stall the GPU, from a plugin whose host owns the
+allocator, on a GPU whose memory is already handed out).  For them the library keeps the layer's intermediates in a
 fixed 32 MiB array of its own.  This test calls that entry point through the C ABI twice in a
 row, with different inputs, and requires the same output as the ordinary entry point that is
 given a workspace; it also checks that a shape too large for the built-in array is refused.
