@@ -78,6 +78,8 @@ def run_reference_arm(args) -> int:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
+    # torchrun pins OMP_NUM_THREADS=1; the CPU arm is meant to use every host core
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
     batch = 32
     steps = max(1, min(args.steps, 10))
     v, per, cores, done = cpu_model_throughput(batch, steps, max(1, min(args.warmup, 2)), budget_s=120.0)
@@ -110,7 +112,7 @@ class ClockSampler:
         self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
         try:
             self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                       "-lms", "100", "-i", str(index)], stdout=self.f, stderr=subprocess.DEVNULL)
+                                       "-lms", "20", "-i", str(index)], stdout=self.f, stderr=subprocess.DEVNULL)
         except OSError:
             self.p = None
 
@@ -243,6 +245,60 @@ def run_single_stage(args) -> int:
     torch.cuda.synchronize()
     print(json.dumps({"stage": args.stage, "batch": B, "iters": args.stage_iters,
                       "ms_per_call_incl_host": e0.elapsed_time(e1) / args.stage_iters}))
+    return 0
+
+
+def run_layer_sweep(args) -> int:
+    """Standalone ConvNN layer on long sequences (cfg-5 of the baseline): x ~ N(0,1) of shape
+    8 x N x 768 bf16, cosine, depthwise, sampling 'all' and 'spatial' (N/4 candidates), K in {9, 25}.
+    Prints one JSON line per case with per-stage device time, tokens/s and roofline fractions."""
+    import convnn_b200
+    from convnn_b200 import ops
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    pk = peaks()
+    B, D = 8, 768
+    for N in args.sweep_n:
+        for K in (9, 25):
+            for sampling in ("all", "spatial"):
+                S = N if sampling == "all" else N // 4
+                layer = convnn_b200.MultiHeadConvNNAttention(D, 1, 0.0, K, sampling, S if sampling != "all" else -1,
+                                                             0, "cosine", seq_length=N).eval().to(dev, torch.bfloat16)
+                spec = layer._spec()
+                w_qkv, w_conv, w_pw, w_o = layer.packed_weights(torch.bfloat16, dev)
+                cand = layer.candidates(N, dev)
+                x = torch.randn(B, N, D, device=dev).to(torch.bfloat16)
+                q, k, v, qs, ks = ops.qkv_proj(spec, x, w_qkv, cand)
+                idx, val = ops.sim_topk(spec, q, k, qs, ks, cand)
+                o = ops.gather_conv(spec, v, idx, val, w_conv, w_pw, S=S)
+                fns = {"qkv_proj": lambda: ops.qkv_proj(spec, x, w_qkv, cand),
+                       "sim_topk": lambda: ops.sim_topk(spec, q, k, qs, ks, cand),
+                       "gather_conv": lambda: ops.gather_conv(spec, v, idx, val, w_conv, w_pw, S=S),
+                       "out_proj": lambda: ops.out_proj(spec, o, w_o, S=S)}
+                times = {}
+                for name, fn in fns.items():
+                    fn()
+                    torch.cuda.synchronize()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    reps = 3
+                    e0.record()
+                    for _ in range(reps):
+                        fn()
+                    e1.record()
+                    torch.cuda.synchronize()
+                    times[name] = e0.elapsed_time(e1) / reps
+                work = algorithmic_work(B, N, S, D, 1, K)
+                total = sum(times.values())
+                sim_tf = work["sim_topk"]["flops"] / times["sim_topk"] / 1e9
+                print(json.dumps({
+                    "case": f"N={N} K={K} {sampling} S={S}", "tokens_per_s": B * N / (total / 1e3),
+                    "ms": {k2: round(v2, 4) for k2, v2 in times.items()},
+                    "sim_topk_TFLOPs": sim_tf, "sim_topk_frac_of_tensor_peak": sim_tf / pk["tf_burst"],
+                    "gather_conv_GBps": work["gather_conv"]["bytes"] / times["gather_conv"] / 1e6,
+                    "gather_conv_frac_of_hbm_peak": work["gather_conv"]["bytes"] / times["gather_conv"] / 1e6 / pk["hbm"],
+                    "peak_source": pk["source"]}))
+                del layer, x, q, k, v, idx, val, o
+                torch.cuda.empty_cache()
     return 0
 
 
@@ -399,6 +455,7 @@ def run_ours(args) -> int:
         cpu_v, cpu_per, cores, cpu_done = (None, None, None, 0)
         cpu = None
         if world == 1 and not args.no_cpu:
+            torch.set_num_threads(max(1, os.cpu_count() or 1))
             cpu_v, cpu_per, cores, cpu_done = cpu_model_throughput(32, 8, 1, budget_s=20.0)
             cpu = {"value": cpu_v, "unit": UNIT, "cores": cores, "kind": "port",
                    "sample": f"{cpu_done} forwards of 32 images (of the 256-image batch), fp32, torch CPU oracle"}
@@ -431,18 +488,23 @@ def run_ours(args) -> int:
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--stage", choices=["qkv_proj", "sim_topk", "gather_conv", "out_proj"],
                     help="run only this stage of one layer (profiling aid)")
+    ap.add_argument("--layer-sweep", action="store_true",
+                    help="standalone layer on long sequences (8 x N x 768), per-stage time and roofline")
+    ap.add_argument("--sweep-n", type=int, nargs="+", default=[1024, 4096, 16384])
     ap.add_argument("--stage-batch", type=int, default=BATCH_PER_GPU)
     ap.add_argument("--stage-iters", type=int, default=3)
     args = ap.parse_args()
     if args.stage:
         return run_single_stage(args)
+    if args.layer_sweep:
+        return run_layer_sweep(args)
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         return run_reference_arm(args)

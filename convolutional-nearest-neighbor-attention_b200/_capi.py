@@ -44,7 +44,7 @@ SIGNATURES = {
     "convnn_b200_sim_topk": (ctypes.c_int, [ctypes.POINTER(ConvnnDesc), c_void, c_void, c_void, c_void, c_void,
                                             c_void, c_void, c_void]),
     "convnn_b200_gather_conv": (ctypes.c_int, [ctypes.POINTER(ConvnnDesc), c_void, c_void, c_void, c_void, c_void,
-                                               c_void, c_void]),
+                                               c_void, c_void, c_void]),
     "convnn_b200_out_proj": (ctypes.c_int, [ctypes.POINTER(ConvnnDesc), c_void, c_void, c_void, c_i64, c_void, c_i64,
                                             c_void, c_void]),
     "convnn_b200_forward": (ctypes.c_int, [ctypes.POINTER(ConvnnDesc), c_void, c_i64, c_void, c_void, c_void, c_void,

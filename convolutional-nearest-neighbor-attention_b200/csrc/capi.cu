@@ -91,11 +91,21 @@ struct Workspace {
 
 size_t up256(size_t n) { return (n + 255) & ~(size_t)255; }
 
-// Gathered candidate rows of x (B, S, D) for the query projection, later reused for the
-// head-merged (B, T, D) operand of the output projection.
-size_t stage_scratch(const Dims& dm) { return (size_t)dm.B * (dm.T > dm.S ? dm.T : dm.S) * dm.D * dm.elt; }
+// Gathered candidate rows of x (B, S, D) for the query projection, later reused for the conv's
+// GEMM operand and for the head-merged (B, T, D) operand of the output projection.
+size_t stage_scratch(const Dims& dm, int conv_type) {
+    size_t n = (size_t)dm.B * (dm.T > dm.S ? dm.T : dm.S) * dm.D;
+    if (conv_type == CONVNN_STANDARD) {          // weighted neighbour block (B, H, T, K*C) of the tensor-core conv
+        const size_t m = (size_t)dm.B * dm.H * dm.T * dm.K * dm.C;
+        if (m > n) n = m;
+    } else if (conv_type == CONVNN_DEPTHWISE_SEPARABLE) {
+        const size_t m = (size_t)dm.B * dm.H * dm.T * dm.C;
+        if (m > n) n = m;
+    }
+    return n * dm.elt;
+}
 
-Workspace carve(const Dims& dm, void* base) {
+Workspace carve(const Dims& dm, int conv_type, void* base) {
     Workspace w;
     char* p = static_cast<char*>(base);
     size_t off = 0;
@@ -108,7 +118,7 @@ Workspace carve(const Dims& dm, void* base) {
     w.kstat = reinterpret_cast<float*>(take((size_t)dm.B * dm.H * dm.T * 4));
     w.val = reinterpret_cast<float*>(take((size_t)dm.B * dm.H * dm.T * dm.K * 4));
     w.idx = reinterpret_cast<int32_t*>(take((size_t)dm.B * dm.H * dm.T * dm.K * 4));
-    w.scratch = take(stage_scratch(dm));
+    w.scratch = take(stage_scratch(dm, conv_type));
     w.total = off;
     return w;
 }
@@ -169,13 +179,13 @@ int convnn_b200_head_channels(const convnn_desc* d) {
 size_t convnn_b200_stage_scratch_bytes(const convnn_desc* d) {
     Dims dm;
     if (validate(d, &dm) != CONVNN_OK) return 0;
-    return stage_scratch(dm);
+    return stage_scratch(dm, d->conv_type);
 }
 
 size_t convnn_b200_workspace_bytes(const convnn_desc* d) {
     Dims dm;
     if (validate(d, &dm) != CONVNN_OK) return 0;
-    return carve(dm, nullptr).total;
+    return carve(dm, d->conv_type, nullptr).total;
 }
 
 int convnn_b200_qkv_proj(const convnn_desc* d, const void* x, int64_t ldx, const void* w_qkv,
@@ -259,14 +269,14 @@ int convnn_b200_sim_topk(const convnn_desc* d, const void* q, const void* k, con
 }
 
 int convnn_b200_gather_conv(const convnn_desc* d, const void* v, const int32_t* idx, const float* val,
-                            const void* w_conv, const void* w_pw, void* o, void* stream) {
+                            const void* w_conv, const void* w_pw, void* o, void* scratch, void* stream) {
     Dims dm;
     int rc = validate(d, &dm);
     if (rc) return rc;
     REQUIRE_PTR(v); REQUIRE_PTR(idx); REQUIRE_PTR(val); REQUIRE_PTR(w_conv); REQUIRE_PTR(o);
     if (d->conv_type == CONVNN_DEPTHWISE_SEPARABLE) REQUIRE_PTR(w_pw);
     if ((rc = check_device())) return rc;
-    return launch_gather_conv_simt(d, dm, v, idx, val, w_conv, w_pw, o, static_cast<cudaStream_t>(stream));
+    return launch_gather_conv_simt(d, dm, v, idx, val, w_conv, w_pw, o, scratch, static_cast<cudaStream_t>(stream));
 }
 
 int convnn_b200_out_proj(const convnn_desc* d, const void* o, const void* w_o, const void* residual, int64_t ldr,
@@ -309,12 +319,12 @@ int convnn_b200_forward(const convnn_desc* d, const void* x, int64_t ldx, const 
     if (rc) return rc;
     REQUIRE_PTR(workspace);
     if (!aligned16(workspace)) return set_error(CONVNN_E_ALIGN, "workspace must be 16-byte aligned");
-    Workspace w = carve(dm, workspace);
+    Workspace w = carve(dm, d->conv_type, workspace);
     if (workspace_bytes < w.total)
         return set_error(CONVNN_E_WORKSPACE, "workspace has %zu bytes, %zu needed", workspace_bytes, w.total);
     if ((rc = convnn_b200_qkv_proj(d, x, ldx, w_qkv, cand, w.q, w.k, w.v, w.qstat, w.kstat, w.scratch, stream))) return rc;
     if ((rc = convnn_b200_sim_topk(d, w.q, w.k, w.qstat, w.kstat, cand, w.idx, w.val, stream))) return rc;
-    if ((rc = convnn_b200_gather_conv(d, w.v, w.idx, w.val, w_conv, w_pw, w.o, stream))) return rc;
+    if ((rc = convnn_b200_gather_conv(d, w.v, w.idx, w.val, w_conv, w_pw, w.o, w.scratch, stream))) return rc;
     return convnn_b200_out_proj(d, w.o, w_o, residual, ldr, out, ldo, w.scratch, stream);
 }
 

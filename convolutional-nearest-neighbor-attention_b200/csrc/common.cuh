@@ -116,7 +116,7 @@ int launch_gather_rows(int dtype, const void* x, long long ldx, const int32_t* c
 int launch_merge_heads(int dtype, const void* o, void* y, int B, int Tn, int H, int dk, cudaStream_t st);
 bool force_simt();   // debugging switch: environment variable CONVNN_B200_FORCE_SIMT=1
 int launch_gather_conv_simt(const convnn_desc* d, const Dims& dm, const void* v, const int32_t* idx,
-                            const float* val, const void* w_conv, const void* w_pw, void* o,
+                            const float* val, const void* w_conv, const void* w_pw, void* o, void* scratch,
                             cudaStream_t st);
 
 }  // namespace convnn

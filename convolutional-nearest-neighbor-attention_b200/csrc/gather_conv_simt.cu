@@ -6,7 +6,7 @@
 // global memory (they are L2-resident: every row is re-read K times on average but
 // fetched from HBM once) with 16-byte loads along the channel dimension.
 //   depthwise            o[t, c] = sum_j w[j, c] * p[t, j] * v[idx[t, j], c]
-//   standard             o[t, o] = sum_{j, c} w[j, c, o] * p[t, j] * v[idx[t, j], c]
+//   standard             o[t, o] = sum_{j, c} w[o, j, c] * p[t, j] * v[idx[t, j], c]
 //   depthwise-separable  depthwise (kept in fp32 in shared memory) then a C x d_k matrix
 // The K-times expanded tensor the reference builds three times never exists.
 #include "common.cuh"
@@ -160,7 +160,9 @@ __global__ void __launch_bounds__(THREADS) gather_conv_mat_kernel(
             P[tt * pstride + r] = x;
         }
         __syncthreads();
-        const T* wm = separable ? wpw : wconv + (long long)j0 * C * dk;   // (rows = jn*C, dk)
+        // standard: w[oc][j*C + c] (d_k, K*C);  separable stage 1: w[oc][c] (d_k, C)
+        const T* wm = separable ? wpw : wconv + (long long)j0 * C;
+        const long long wld = separable ? C : (long long)K * C;
 #pragma unroll
         for (int it = 0; it < ITEMS; ++it) {
             const int item = threadIdx.x + it * THREADS;
@@ -168,7 +170,7 @@ __global__ void __launch_bounds__(THREADS) gather_conv_mat_kernel(
                 const int oc = item % dk, tg = item / dk;
                 const float* p0 = P + (tg * 4) * pstride;
                 for (int r = 0; r < jn * C; ++r) {
-                    const float w = to_f32<T>(wm[(long long)r * dk + oc]);
+                    const float w = to_f32<T>(wm[(long long)oc * wld + r]);
 #pragma unroll
                     for (int e = 0; e < 4; ++e)
                         if (tg * 4 + e < TT) acc[it][e] = fmaf(w, p0[e * pstride + r], acc[it][e]);
@@ -237,10 +239,85 @@ int launch_mat(const convnn_desc* d, const Dims& dm, const void* v, const int32_
 int try_launch_gather_conv_dw_smem(const convnn_desc* d, const Dims& dm, const void* v, const int32_t* idx,
                                    const float* val, const void* w_conv, void* o, cudaStream_t st);
 
+namespace {
+// Weighted neighbour block for the tensor-core standard conv: P[(b,h,t), j*C + c] =
+// bf16(p[t,j] * v[idx[t,j], c]), the A operand of a GEMM with the (d_k, K*C) tap weights.
+template <int TT>
+__global__ void __launch_bounds__(THREADS) gather_weighted_kernel(
+    const __nv_bfloat16* __restrict__ v, const int32_t* __restrict__ idx, const float* __restrict__ val,
+    __nv_bfloat16* __restrict__ P, int T_, int H, int C, int Cp, int K, int maximum, int softmax) {
+    __shared__ float ps[TT][kMaxK];
+    __shared__ int ns[TT][kMaxK];
+    const int bh = blockIdx.y;
+    const int b = bh / H, h = bh - b * H;
+    const int t0 = blockIdx.x * TT;
+    const int nt = min(TT, T_ - t0);
+    const long long nbase = ((long long)bh * T_ + t0) * K;
+    for (int e = threadIdx.x; e < nt * K; e += THREADS) ns[e / K][e % K] = idx[nbase + e];
+    if (threadIdx.x < nt) token_weights(val + nbase + (long long)threadIdx.x * K, ps[threadIdx.x], K, maximum, softmax);
+    __syncthreads();
+    const __nv_bfloat16* vb = v + ((long long)b * T_ * H + h) * Cp;
+    const long long tstride = (long long)H * Cp;
+    const int groups = C / 8;
+    for (int item = threadIdx.x; item < nt * K * groups; item += THREADS) {
+        const int tt = item / (K * groups);
+        const int r = item - tt * K * groups;
+        const int j = r / groups, c = (r - j * groups) * 8;
+        float x[8];
+        VecLoad<__nv_bfloat16, 8>::load(vb + ns[tt][j] * tstride + c, x);
+        const float pj = ps[tt][j];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[e] *= pj;
+        VecLoad<__nv_bfloat16, 8>::store(P + (((long long)bh * T_ + t0 + tt) * K + j) * C + c, x);
+    }
+}
+}  // namespace
+
+// bfloat16 standard / depthwise-separable conv on the tensor cores: a gather kernel builds the
+// GEMM's A operand in `scratch`, the tap / pointwise weights are its (N, K) operand.
+// Returns CONVNN_E_UNSUPPORTED (last_error untouched) when the shape does not qualify.
+int try_launch_gather_conv_tc(const convnn_desc* d, const Dims& dm, const void* v, const int32_t* idx,
+                              const float* val, const void* w_conv, const void* w_pw, void* o, void* scratch,
+                              cudaStream_t st) {
+    if (d->dtype != CONVNN_BF16 || d->coord || !scratch || force_simt() || dm.C % 8 != 0 || !aligned16(v) ||
+        !aligned16(scratch))
+        return CONVNN_E_UNSUPPORTED;
+    const int M = dm.B * dm.H * dm.T;
+    void* cs[1] = {o};
+    int rc;
+    if (d->conv_type == CONVNN_STANDARD) {
+        const int Kd = dm.K * dm.C;
+        if (!gemm_tc_supported(scratch, Kd, w_conv, Kd, dm.dk, 1, cs, dm.dk)) return CONVNN_E_UNSUPPORTED;
+        constexpr int TT = 16;
+        dim3 grid((dm.T + TT - 1) / TT, dm.B * dm.H);
+        gather_weighted_kernel<TT><<<grid, THREADS, 0, st>>>(
+            static_cast<const __nv_bfloat16*>(v), idx, val, static_cast<__nv_bfloat16*>(scratch), dm.T, dm.H, dm.C,
+            dm.Cp, dm.K, d->metric != CONVNN_EUCLIDEAN, d->softmax);
+        CONVNN_CHECK_LAUNCH("gather_weighted");
+        return launch_gemm_tc(scratch, Kd, w_conv, M, dm.dk, Kd, 1, cs, dm.dk, GemmTcOpts(), st);
+    }
+    if (d->conv_type == CONVNN_DEPTHWISE_SEPARABLE) {
+        if (!gemm_tc_supported(scratch, dm.C, w_pw, dm.C, dm.dk, 1, cs, dm.dk)) return CONVNN_E_UNSUPPORTED;
+        // stage 0: the depthwise kernels with the (K, C) taps, result (B, H, T, C) rounded to bf16
+        rc = try_launch_gather_conv_dw_smem(d, dm, v, idx, val, w_conv, scratch, st);
+        if (rc == CONVNN_E_UNSUPPORTED) {
+            if (dm.dk % 8 != 0 || !aligned16(w_conv)) return CONVNN_E_UNSUPPORTED;
+            rc = launch_dw<__nv_bfloat16, 8>(d, dm, v, idx, val, w_conv, scratch, st);
+        }
+        if (rc) return rc;
+        return launch_gemm_tc(scratch, dm.C, w_pw, M, dm.dk, dm.C, 1, cs, dm.dk, GemmTcOpts(), st);
+    }
+    return CONVNN_E_UNSUPPORTED;
+}
+
 int launch_gather_conv_simt(const convnn_desc* d, const Dims& dm, const void* v, const int32_t* idx,
-                            const float* val, const void* w_conv, const void* w_pw, void* o,
+                            const float* val, const void* w_conv, const void* w_pw, void* o, void* scratch,
                             cudaStream_t st) {
     const bool f32 = d->dtype == CONVNN_F32;
+    if (d->conv_type != CONVNN_DEPTHWISE) {
+        const int rc = try_launch_gather_conv_tc(d, dm, v, idx, val, w_conv, w_pw, o, scratch, st);
+        if (rc != CONVNN_E_UNSUPPORTED) return rc;
+    }
     if (d->conv_type == CONVNN_DEPTHWISE) {
         const int rc = try_launch_gather_conv_dw_smem(d, dm, v, idx, val, w_conv, o, st);
         if (rc != CONVNN_E_UNSUPPORTED) return rc;

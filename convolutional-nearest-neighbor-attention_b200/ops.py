@@ -72,7 +72,7 @@ def _rows_view(x: torch.Tensor) -> Tuple[torch.Tensor, int]:
 
 def pack_weights(spec: LayerSpec, w_q, w_k, w_v, w_o, conv_weights, dtype, device):
     """Re-layout the module parameters into what the kernels read (see the header):
-    w_qkv (3, D, D) = [W_k; W_v; W_q]; conv taps tap-major; all in ``dtype``."""
+    w_qkv (3, D, D) = [W_k; W_v; W_q]; depthwise taps tap-major, standard taps (d_k, K*C); all in ``dtype``."""
     def cvt(t):
         return t.detach().to(device=device, dtype=dtype).contiguous()
     w_qkv = torch.stack([cvt(w_k), cvt(w_v), cvt(w_q)], dim=0).contiguous()
@@ -81,12 +81,12 @@ def pack_weights(spec: LayerSpec, w_q, w_k, w_v, w_o, conv_weights, dtype, devic
         (wc,) = conv_weights                       # (C, 1, K) -> (K, C)
         w_conv = cvt(wc[:, 0, :].t())
     elif spec.convolution_type == "standard":
-        (wc,) = conv_weights                       # (d_k, C, K) -> (K, C, d_k)
-        w_conv = cvt(wc.permute(2, 1, 0))
+        (wc,) = conv_weights                       # (d_k, C, K) -> (d_k, K, C)
+        w_conv = cvt(wc.permute(0, 2, 1))
     elif spec.convolution_type == "depthwise-separable":
-        w0, w1 = conv_weights                      # (C, 1, K) -> (K, C); (d_k, C, 1) -> (C, d_k)
+        w0, w1 = conv_weights                      # (C, 1, K) -> (K, C); (d_k, C, 1) -> (d_k, C)
         w_conv = cvt(w0[:, 0, :].t())
-        w_pw = cvt(w1[:, :, 0].t())
+        w_pw = cvt(w1[:, :, 0])
     else:
         raise ValueError(f"unknown convolution_type {spec.convolution_type!r}")
     return w_qkv, w_conv, w_pw, cvt(w_o)
@@ -145,8 +145,11 @@ def gather_conv(spec: LayerSpec, v, idx, val, w_conv, w_pw=None, S: Optional[int
     B, T, H, _ = v.shape
     d = descriptor(spec, B, T, T if spec.sampling_type == "all" else (S or T), v.dtype)
     o = torch.empty(B, H, T, spec.d_k, dtype=v.dtype, device=v.device)
+    scratch = None
+    if spec.convolution_type != "depthwise":
+        scratch = torch.empty(L.convnn_b200_stage_scratch_bytes(d), dtype=torch.uint8, device=v.device)
     _capi.check(L.convnn_b200_gather_conv(d, v.data_ptr(), idx.data_ptr(), val.data_ptr(), w_conv.data_ptr(),
-                                          _capi.ptr(w_pw), o.data_ptr(), _stream(v)))
+                                          _capi.ptr(w_pw), o.data_ptr(), _capi.ptr(scratch), _stream(v)))
     return o
 
 

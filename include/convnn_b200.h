@@ -33,8 +33,8 @@
  * Packed weights (all in `dtype`; the Python module packs and caches them)
  *   w_qkv    (3, D, D)       [W_k; W_v; W_q], each (out, in) as nn.Linear stores it
  *   w_conv   depthwise / depthwise-separable stage 0: (K, C) tap-major, from (C, 1, K)
- *            standard: (K, C, d_k) from (d_k, C, K)
- *   w_pw     depthwise-separable stage 1: (C, d_k) from (d_k, C, 1); else NULL
+ *            standard: (d_k, K, C) from (d_k, C, K), i.e. a (d_k, K*C) matrix
+ *   w_pw     depthwise-separable stage 1: (d_k, C) from (d_k, C, 1); else NULL
  *   w_o      (D, D) (out, in)
  */
 #ifndef CONVNN_B200_H
@@ -113,10 +113,11 @@ int convnn_b200_head_channels(const convnn_desc* d);
  * along layers.py:264-313. 0 on a bad descriptor. */
 size_t convnn_b200_workspace_bytes(const convnn_desc* d);
 
-/* Bytes of the optional `scratch` argument of the two projection stages: room for the
- * gathered candidate rows (B, S, D) / the head-merged activations (B, T, D).  With
- * scratch == NULL those stages still work but leave the tensor cores for the cases that
- * need it (sampled queries; H > 1 output projection).  No reference counterpart. */
+/* Bytes of the optional `scratch` argument of the stages: room for the gathered candidate
+ * rows (B, S, D), the GEMM operand of the standard (B, H, T, K*C) / separable (B, H, T, C)
+ * conv, and the head-merged activations (B, T, D).  With scratch == NULL the stages still
+ * work but leave the tensor cores for the cases that need it (sampled queries; standard and
+ * separable conv; H > 1 output projection).  No reference counterpart. */
 size_t convnn_b200_stage_scratch_bytes(const convnn_desc* d);
 
 /* K/V/Q projections, head split and (optional) coordinate channel, plus the per-row
@@ -139,7 +140,7 @@ int convnn_b200_sim_topk(const convnn_desc* d, const void* q, const void* k,
  * self.conv (layers.py:313, 187-228). */
 int convnn_b200_gather_conv(const convnn_desc* d, const void* v, const int32_t* idx,
                             const float* val, const void* w_conv, const void* w_pw,
-                            void* o, void* stream);
+                            void* o, void* scratch, void* stream);
 
 /* Head merge (including the reference's flat reinterpretation for H > 1) and the W_o
  * projection.  Replaces layers.py:317, 320 (247-259).  With `residual` != NULL (rows of D
