@@ -45,6 +45,16 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const T* __restrict__ x,
     const int lane = threadIdx.x & 31;
     const long long wpb = blockDim.x >> 5;
     const int nvec = D / V;
+    // this lane's slices of the affine parameters, fixed for every row it touches
+    float g[NV][V], bt[NV][V];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = lane + 32 * k;
+        if (i < nvec) {
+            load_vec<T>(gamma + i * V, g[k]);
+            load_vec<T>(beta + i * V, bt[k]);
+        }
+    }
     for (long long r = blockIdx.x * wpb + (threadIdx.x >> 5); r < rows + cls_rows; r += (long long)gridDim.x * wpb) {
         if (r >= rows) {                       // class-token row of image b: cls + pe[0]
             const long long b = r - rows;
@@ -97,11 +107,9 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const T* __restrict__ x,
         for (int k = 0; k < NV; ++k) {
             const int i = lane + 32 * k;
             if (i < nvec) {
-                float g[V], bt[V], o[V];
-                load_vec<T>(gamma + i * V, g);
-                load_vec<T>(beta + i * V, bt);
+                float o[V];
 #pragma unroll
-                for (int j = 0; j < V; ++j) o[j] = (v[k][j] - mean) * rstd * g[j] + bt[j];
+                for (int j = 0; j < V; ++j) o[j] = fmaf((v[k][j] - mean) * rstd, g[k][j], bt[k][j]);
                 if (perow) {
                     float pv[V];
                     load_vec<T>(perow + i * V, pv);
