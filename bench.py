@@ -302,6 +302,13 @@ def run_layer_sweep(args) -> int:
     return 0
 
 
+# dram__bytes_read + dram__bytes_write of one launch of each stage at the bench shape, from the
+# ncu captures summarised under profiles/ (outputs that are still in L2 when the kernel ends are
+# not in these figures, which is why they sit below the algorithmic bytes).
+NCU_TRAFFIC_BYTES = {"qkv_proj": 19.69e6 + 10.28e6, "sim_topk": 39.2e6 + 0.009e6, "gather_conv": 23.04e6,
+                     "out_proj": 19.5e6}
+
+
 def algorithmic_work(B, T, S, D, H, K, elt=2):
     """Compulsory bytes / flops per launch of each stage (one layer call)."""
     idxval = 8 * B * H * T * K
@@ -474,7 +481,7 @@ def run_ours(args) -> int:
                     "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": int(launches_eager) if graph is None else int(per_forward * args.steps),
             "roofline": {"bound": bound, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak,
-                         "traffic": None, "kernel": dom, "peak_source": pk["source"],
+                         "traffic": NCU_TRAFFIC_BYTES.get(dom), "kernel": dom, "peak_source": pk["source"],
                          "ms_per_launch": per_launch_ms, "stages": stages},
             "cpu_baseline": cpu,
             "clocks": clocks,
