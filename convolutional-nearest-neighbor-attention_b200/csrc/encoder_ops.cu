@@ -3,6 +3,7 @@
 // 16-byte loads and stores, statistics in fp32, one rounding to the storage type at each
 // point where the reference's eager ops would round (reference vit.py:100-135, 247-270).
 #include "common.cuh"
+#include "f32x2.cuh"
 
 namespace convnn {
 namespace {
@@ -45,16 +46,6 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const T* __restrict__ x,
     const int lane = threadIdx.x & 31;
     const long long wpb = blockDim.x >> 5;
     const int nvec = D / V;
-    // this lane's slices of the affine parameters, fixed for every row it touches
-    float g[NV][V], bt[NV][V];
-#pragma unroll
-    for (int k = 0; k < NV; ++k) {
-        const int i = lane + 32 * k;
-        if (i < nvec) {
-            load_vec<T>(gamma + i * V, g[k]);
-            load_vec<T>(beta + i * V, bt[k]);
-        }
-    }
     for (long long r = blockIdx.x * wpb + (threadIdx.x >> 5); r < rows + cls_rows; r += (long long)gridDim.x * wpb) {
         if (r >= rows) {                       // class-token row of image b: cls + pe[0]
             const long long b = r - rows;
@@ -107,9 +98,11 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const T* __restrict__ x,
         for (int k = 0; k < NV; ++k) {
             const int i = lane + 32 * k;
             if (i < nvec) {
-                float o[V];
+                float g[V], bt[V], o[V];
+                load_vec<T>(gamma + i * V, g);
+                load_vec<T>(beta + i * V, bt);
 #pragma unroll
-                for (int j = 0; j < V; ++j) o[j] = fmaf((v[k][j] - mean) * rstd, g[k][j], bt[k][j]);
+                for (int j = 0; j < V; ++j) o[j] = (v[k][j] - mean) * rstd * g[j] + bt[j];
                 if (perow) {
                     float pv[V];
                     load_vec<T>(perow + i * V, pv);
@@ -118,6 +111,54 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const T* __restrict__ x,
                 }
                 store_vec<T>(out + i * V, o);
             }
+        }
+    }
+}
+
+// bfloat16 rows of at most 256 channels: one 16-byte vector per lane, arithmetic on packed fp32
+// pairs, affine parameters held in registers.  Same results as the generic kernel.
+__global__ void __launch_bounds__(256) layernorm_bf16_row256_kernel(
+    const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bfloat16* __restrict__ gamma,
+    const __nv_bfloat16* __restrict__ beta, float eps, __nv_bfloat16* __restrict__ y, long long ldy, long long rows,
+    int D) {
+    const int lane = threadIdx.x & 31;
+    const long long wpb = blockDim.x >> 5;
+    const bool act = lane < D / 8;
+    const float invD = 1.0f / (float)D;
+    f32x2 g2[4], b2[4];
+    {
+        const uint4 z = make_uint4(0, 0, 0, 0);
+        bf16x8_to_f32x2(act ? *reinterpret_cast<const uint4*>(gamma + lane * 8) : z, g2);
+        bf16x8_to_f32x2(act ? *reinterpret_cast<const uint4*>(beta + lane * 8) : z, b2);
+    }
+    const long long stride = (long long)gridDim.x * wpb;
+    long long r = blockIdx.x * wpb + (threadIdx.x >> 5);
+    uint4 nxt = make_uint4(0, 0, 0, 0);
+    if (act && r < rows) nxt = *reinterpret_cast<const uint4*>(x + r * ldx + lane * 8);
+    for (; r < rows; r += stride) {
+        f32x2 v2[4];
+        bf16x8_to_f32x2(nxt, v2);
+        if (act && r + stride < rows)                     // next row's load overlaps this row's arithmetic
+            nxt = *reinterpret_cast<const uint4*>(x + (r + stride) * ldx + lane * 8);
+        float s0, s1;
+        unpack2(add2(add2(v2[0], v2[1]), add2(v2[2], v2[3])), s0, s1);
+        const float mean = warp_sum(s0 + s1) * invD;
+        const f32x2 nm = pack2(-mean, -mean);
+        f32x2 d2[4], q2 = 0ull;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            d2[e] = add2(v2[e], nm);
+            q2 = fma2(d2[e], d2[e], q2);
+        }
+        float q0, q1;
+        unpack2(q2, q0, q1);
+        const float rstd = rsqrtf(warp_sum(act ? q0 + q1 : 0.f) * invD + eps);
+        if (act) {
+            const f32x2 r2 = pack2(rstd, rstd);
+            f32x2 o2[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o2[e] = fma2(mul2(d2[e], r2), g2[e], b2[e]);
+            *reinterpret_cast<uint4*>(y + r * ldy + lane * 8) = f32x2_to_bf16x8(o2);
         }
     }
 }
@@ -188,6 +229,16 @@ int launch_layernorm(int dtype, const void* x, long long ldx, const void* gamma,
     if (D % V != 0 || ldx % V != 0 || ldy % V != 0 || !aligned16(x) || !aligned16(y) || !aligned16(gamma) ||
         !aligned16(beta) || (pe && (!aligned16(pe) || !aligned16(cls))))
         return set_error(CONVNN_E_ALIGN, "layernorm: D, strides and pointers must be multiples of 16 bytes");
+    if (dtype == CONVNN_BF16 && !pe && D <= 256) {
+        int blocks = (int)((rows + 7) / 8);
+        if (blocks > 148 * 16) blocks = 148 * 16;
+        if (blocks < 1) blocks = 1;
+        layernorm_bf16_row256_kernel<<<blocks, 256, 0, st>>>(
+            static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(gamma),
+            static_cast<const __nv_bfloat16*>(beta), eps, static_cast<__nv_bfloat16*>(y), ldy, rows, D);
+        CONVNN_CHECK_LAUNCH("layernorm_bf16_row256");
+        return CONVNN_OK;
+    }
     if (dtype == CONVNN_F32)
         return ln_dispatch<float>(x, ldx, gamma, beta, eps, y, ldy, rows, D, pe, cls, Np, cls_rows, st);
     return ln_dispatch<__nv_bfloat16>(x, ldx, gamma, beta, eps, y, ldy, rows, D, pe, cls, Np, cls_rows, st);

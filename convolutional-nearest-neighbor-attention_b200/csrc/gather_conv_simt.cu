@@ -10,6 +10,7 @@
 //   depthwise-separable  depthwise (kept in fp32 in shared memory) then a C x d_k matrix
 // The K-times expanded tensor the reference builds three times never exists.
 #include "common.cuh"
+#include "f32x2.cuh"
 
 namespace convnn {
 namespace {
@@ -334,40 +335,6 @@ int launch_gather_conv_simt(const convnn_desc* d, const Dims& dm, const void* v,
 
 }  // namespace convnn
 
-// Packed pairs of fp32 in one 64-bit register: sm_100 executes add / mul / fma on both halves
-// with one instruction (same IEEE results as two scalar operations), which halves the
-// floating-point instruction count of the tap loop.
-namespace convnn {
-namespace {
-typedef unsigned long long f32x2;
-__device__ __forceinline__ f32x2 pack2(float a, float b) {
-    f32x2 r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
-    return r;
-}
-__device__ __forceinline__ void unpack2(f32x2 v, float& a, float& b) {
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
-}
-__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
-    f32x2 r;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
-    f32x2 r;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-    return r;
-}
-// 8 bfloat16 (16 bytes) -> four packed fp32 pairs
-__device__ __forceinline__ void load_bf16x8_as_f32x2(const __nv_bfloat16* p, f32x2 (&out)[4]) {
-    const uint4 v = *reinterpret_cast<const uint4*>(p);
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int e = 0; e < 4; ++e) out[e] = pack2(__uint_as_float(w[e] << 16), __uint_as_float(w[e] & 0xffff0000u));
-}
-}  // namespace
-}  // namespace convnn
-
 // ---- depthwise with the value rows resident in shared memory --------------------------
 // When one (batch, head) slice of V (T x d_k) fits in shared memory, a CTA copies it in
 // once with coalesced 16-byte loads and serves all K-fold neighbour reads from there, so
@@ -432,7 +399,8 @@ __global__ void __launch_bounds__(256) gather_conv_dw_smem_kernel(
 #pragma unroll
             for (int j = 0; j < KT; ++j) {
                 f32x2 x2[4];
-                load_bf16x8_as_f32x2(reinterpret_cast<const __nv_bfloat16*>(vs) + (size_t)ns[t * KT + j] * dk + c, x2);
+                bf16x8_to_f32x2(*reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(vs) +
+                                                                (size_t)ns[t * KT + j] * dk + c), x2);
                 const float pj = ps[t * KT + j];
                 const f32x2 p2 = pack2(pj, pj);
 #pragma unroll

@@ -360,14 +360,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     if (rok[g] && cok) {
                         uint4 v = make_uint4(v0, v1, v2, v3);
                         if (RES) {
+                            // bf16 + bf16 rounded to bf16 (one packed instruction per pair): exactly
+                            // what the reference's `x + layer(x)` on bfloat16 tensors computes
                             const uint4 rv = resv[g];
                             __nv_bfloat162* vh = reinterpret_cast<__nv_bfloat162*>(&v);
                             const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&rv);
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const float2 a = __bfloat1622float2(vh[e]), b2 = __bfloat1622float2(rh[e]);
-                                vh[e] = __floats2bfloat162_rn(a.x + b2.x, a.y + b2.y);
-                            }
+                            for (int e = 0; e < 4; ++e) vh[e] = __hadd2(vh[e], rh[e]);
                         }
                         *reinterpret_cast<uint4*>(optr[g] + c) = v;
                     }
