@@ -1,0 +1,52 @@
+"""Drop-in against the reference's own vit.py, when a reference checkout is available
+(environment variable CONVNN_REF_PATH, or /root/reference).  Skipped otherwise: the golden
+fixtures carry the same contract (state_dict layouts) without the checkout."""
+import os
+import sys
+
+import pytest
+import torch
+
+import convnn_b200
+
+REF = os.environ.get("CONVNN_REF_PATH", "/root/reference")
+pytestmark = pytest.mark.skipif(not os.path.exists(os.path.join(REF, "vit.py")), reason="no reference checkout")
+
+
+@pytest.fixture()
+def reference_modules():
+    from oracle.pin_against_reference import load_reference
+    saved = {k: sys.modules.get(k) for k in ("layers", "vit", "utils")}
+    ref_layers, ref_vit = load_reference(REF)
+    yield ref_layers, ref_vit
+    convnn_b200.uninstall()
+    for k, v in saved.items():
+        if v is None:
+            sys.modules.pop(k, None)
+        else:
+            sys.modules[k] = v
+    if REF in sys.path:
+        sys.path.remove(REF)
+
+
+@pytest.mark.parametrize("layer", ["ConvNNAttention", "BranchAttention", "BranchConv"])
+def test_reference_vit_constructs_our_layers_and_shares_checkpoints(reference_modules, layer):
+    import types
+    ref_layers, ref_vit = reference_modules
+    args = dict(layer=layer, patch_size=16, num_layers=2, num_heads=3, d_hidden=96, d_mlp=192, dropout=0.0,
+                attention_dropout=0.0, convolution_type="standard", softmax_topk_val=True, K=9, sampling_type="all",
+                num_samples=-1, sample_padding=0, magnitude_type="cosine", coordinate_encoding=False,
+                branch_ratio=0.5, kernel_size=9, device="cpu", img_size=(3, 224, 224), num_classes=10)
+    stock = ref_vit.ViT(types.SimpleNamespace(**args))               # the reference's own layers
+    convnn_b200.install(ref_layers, ref_vit)
+    ours = ref_vit.ViT(types.SimpleNamespace(**args))                # same vit.py, our layers
+    attn = ours.transformer_encoder[0].attention
+    assert type(attn).__module__.startswith("convolutional-nearest-neighbor-attention_b200")
+    assert {k: tuple(v.shape) for k, v in ours.state_dict().items()} == \
+           {k: tuple(v.shape) for k, v in stock.state_dict().items()}
+    ours.load_state_dict(stock.state_dict(), strict=True)            # reference checkpoint -> drop-in
+    stock.load_state_dict(ours.state_dict(), strict=True)            # and back
+    mirror = convnn_b200.ViT(convnn_b200.make_args(**args))
+    mirror.load_state_dict(stock.state_dict(), strict=True)          # our ViT mirror takes it too
+    with torch.no_grad(), pytest.raises(RuntimeError, match="no CPU path"):
+        ours(torch.randn(1, 3, 224, 224))
