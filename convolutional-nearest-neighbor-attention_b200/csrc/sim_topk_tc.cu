@@ -261,22 +261,29 @@ sim_topk_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
                 if (!ok) { if (lane == 0) fail(abort_flag, 4); break; }
                 tc_fence_after_sync();
                 const uint32_t taddr = tmem_base + ((uint32_t)(lq * 32) << 16) + (grp * 2 + par) * p.BNpad;
-#pragma unroll 1
-                for (int c = 0; c < p.BN; c += CW) {
-                    const int col0 = ct * p.BN + c;
+                // a warp whose 32 rows all lie past the end of the sequence has nothing to select
+                const bool warp_live = pp * 2 * BM + grp * BM + lq * 32 < p.T;
+                auto stat_of = [&](int c, float& q1, int& c1) {
                     const int c4 = c >> 5;
-                    const float q1 = c4 == 0 ? qv[0] : (c4 == 1 ? qv[1] : (c4 == 2 ? qv[2] : qv[3]));
-                    const int c1 = c4 == 0 ? cv[0] : (c4 == 1 ? cv[1] : (c4 == 2 ? cv[2] : cv[3]));
-                    if (CW == 32 && c + 32 <= p.BN) {
-                        uint32_t acc[32];
-                        tmem_ld_x32(taddr + c, acc);
-                        tmem_ld_wait();
-                        consume<NSEL, 32>(top, acc, col0, 0, q1, c1, p, row, row_ok, sentinel, ks);
-                    } else {
-                        uint32_t acc[16];
-                        tmem_ld_x16(taddr + c, acc);
-                        tmem_ld_wait();
-                        consume<NSEL, 16>(top, acc, col0, c & 31, q1, c1, p, row, row_ok, sentinel, ks);
+                    q1 = c4 == 0 ? qv[0] : (c4 == 1 ? qv[1] : (c4 == 2 ? qv[2] : qv[3]));
+                    c1 = c4 == 0 ? cv[0] : (c4 == 1 ? cv[1] : (c4 == 2 ? cv[2] : cv[3]));
+                };
+                if (warp_live) {
+#pragma unroll 1
+                    for (int c = 0; c < p.BN; c += CW) {
+                        float q1; int c1;
+                        stat_of(c, q1, c1);
+                        if (CW == 32 && c + 32 <= p.BN) {
+                            uint32_t acc[32];
+                            tmem_ld_x32(taddr + c, acc);
+                            tmem_ld_wait();
+                            consume<NSEL, 32>(top, acc, ct * p.BN + c, 0, q1, c1, p, row, row_ok, sentinel, ks);
+                        } else {
+                            uint32_t acc[16];
+                            tmem_ld_x16(taddr + c, acc);
+                            tmem_ld_wait();
+                            consume<NSEL, 16>(top, acc, ct * p.BN + c, c & 31, q1, c1, p, row, row_ok, sentinel, ks);
+                        }
                     }
                 }
                 tc_fence_before_sync();
