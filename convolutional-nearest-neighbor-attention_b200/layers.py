@@ -170,6 +170,10 @@ class MultiHeadAttention(nn.Module):
         q = self.W_q(x).view(B, T, H, dk).transpose(1, 2)
         k = self.W_k(x).view(B, T, H, dk).transpose(1, 2)
         v = self.W_v(x).view(B, T, H, dk).transpose(1, 2)
+        if mask is None and x.is_cuda and not (self.training and self.dropout.p > 0):
+            # same softmax(QK^T / sqrt(d_k)) V, through torch's fused attention kernels
+            o = F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(B, T, self.d_hidden)
+            return self.W_o(o)
         s = torch.matmul(q, k.transpose(-2, -1)) / math.sqrt(dk)
         if mask is not None:
             s = s.masked_fill(mask == 0, -1e9)
