@@ -1,5 +1,5 @@
 """Drop-in against the reference's own vit.py, when a reference checkout is available
-(environment variable CONVNN_REF_PATH, or /root/reference).  Skipped otherwise: the golden
+(environment variable CONVNN_REF_PATH, default ../reference beside the repository).  Skipped otherwise: the golden
 fixtures carry the same contract (state_dict layouts) without the checkout."""
 import os
 import sys
@@ -9,7 +9,8 @@ import torch
 
 import convnn_b200
 
-REF = os.environ.get("CONVNN_REF_PATH", "/root/reference")
+_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF = os.environ.get("CONVNN_REF_PATH", os.path.join(os.path.dirname(_ROOT), "reference"))
 pytestmark = pytest.mark.skipif(not os.path.exists(os.path.join(REF, "vit.py")), reason="no reference checkout")
 
 
