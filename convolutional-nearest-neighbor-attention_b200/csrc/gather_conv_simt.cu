@@ -1,14 +1,21 @@
 // Neighbour weighting + gather + K-tap stride-K Conv1d (reference layers.py:389-406, 313).
 //
-// A CTA owns a tile of consecutive tokens of one (batch, head).  Weights over the K
-// selected values (softmax, raw value, or reciprocal distance) are computed once per
-// token into shared memory; the K neighbour rows of V are then read straight from
-// global memory (they are L2-resident: every row is re-read K times on average but
-// fetched from HBM once) with 16-byte loads along the channel dimension.
+// Weights over the K selected values (softmax, raw value, or reciprocal distance) are computed
+// once per token into shared memory, then
 //   depthwise            o[t, c] = sum_j w[j, c] * p[t, j] * v[idx[t, j], c]
 //   standard             o[t, o] = sum_{j, c} w[o, j, c] * p[t, j] * v[idx[t, j], c]
-//   depthwise-separable  depthwise (kept in fp32 in shared memory) then a C x d_k matrix
-// The K-times expanded tensor the reference builds three times never exists.
+//   depthwise-separable  depthwise, then a (d_k x C) matrix
+// Kernels in this file, in the order the dispatcher tries them:
+//   * depthwise, V slice of one (batch, head) resident in shared memory (one CTA per slice, the
+//     K-fold neighbour reads never leave the SM; HBM sees V once and o once);
+//   * depthwise, token tiles reading neighbour rows from global memory with 16-byte loads
+//     (long sequences: the rows are L2-resident, fetched from HBM once);
+//   * bfloat16 standard / separable on the tensor cores: a gather kernel writes the GEMM's A
+//     operand (the weighted neighbour block, or the depthwise result) and gemm_tc multiplies it
+//     with the (d_k, K*C) tap matrix / the (d_k, C) pointwise matrix;
+//   * float32 (and fallback) standard / separable: shared-memory staged block times the weights.
+// The three K-times expanded copies of V that the reference builds never exist (the tensor-core
+// standard conv materialises the weighted block once, in bfloat16).
 #include "common.cuh"
 #include "f32x2.cuh"
 
