@@ -10,12 +10,15 @@
 //   warp 1     MMA issuer, fp32 accumulators double-buffered in TMEM
 //   warps 2-5  epilogue of the even tiles (TMEM buffer 0), warps 6-9 of the odd tiles (buffer
 //              1): tcgen05.ld -> (+bias, GELU) -> bf16 -> swizzled shared-memory slab ->
-//              coalesced 16-byte global stores (+ residual); two tiles drain concurrently
+//              coalesced 16-byte global stores (+ residual); two tiles drain concurrently.
+//              The WIDE variant adds warps 10-17, which take the upper half of each tile's
+//              column chunks (same lane quarters, same two buffers).
 // The N range may be split into up to three equal parts with their own output tensors,
 // which lets one launch produce k, v and q from the packed [W_k; W_v; W_q].
 // Every mbarrier wait is bounded (see sm100.cuh); an expiry latches the device status.
 #include "common.cuh"
 #include "sm100.cuh"
+#include "f32x2.cuh"
 
 namespace convnn {
 
@@ -32,7 +35,8 @@ using namespace sm100;
 
 constexpr int BM = 128;
 constexpr int MAX_STAGES = 8;
-constexpr int NTHREADS = 320;    // TMA warp, MMA warp, 2 x 4 epilogue warps
+constexpr int NTHREADS = 320;         // TMA warp, MMA warp, 2 x 4 epilogue warps
+constexpr int NTHREADS_WIDE = 576;    // ... or 2 x 8 epilogue warps (each tile's columns split in two)
 
 struct GemmTcParams {
     __nv_bfloat16* c[3];
@@ -76,6 +80,20 @@ __device__ __forceinline__ float gelu_exact(float x) {
     return fmaf(half_x, th, half_x);
 }
 
+// The same function on a packed pair (identical roundings: every step is the packed form of
+// the scalar instruction above).
+__device__ __forceinline__ f32x2 gelu_pair(f32x2 x) {
+    const f32x2 c1 = pack2(0.0356774081f, 0.0356774081f), c0 = pack2(0.7978845608f, 0.7978845608f);
+    const f32x2 hf = pack2(0.5f, 0.5f);
+    const f32x2 inner = mul2(x, fma2(c1, mul2(x, x), c0));
+    float ia, ib, ta, tb;
+    unpack2(inner, ia, ib);
+    asm("tanh.approx.f32 %0, %1;" : "=f"(ta) : "f"(ia));
+    asm("tanh.approx.f32 %0, %1;" : "=f"(tb) : "f"(ib));
+    const f32x2 hx = mul2(hf, x);
+    return fma2(hx, pack2(ta, tb), hx);
+}
+
 // Epilogue, phase A (thread = one output row): 32 fp32 accumulators (+bias, GELU) -> bf16,
 // written as four 16-byte slots into this warp's 32 x 64-byte staging slab.  Slot s of row
 // l lands in physical slot s ^ ((l >> 1) & 3) (precomputed in `sts`), which makes both this
@@ -98,11 +116,14 @@ __device__ __forceinline__ float stage_chunk(const uint32_t (&sts)[4], const uin
         for (int e = 0; e < 4; ++e) {
             float a = __uint_as_float(acc[g * 8 + 2 * e]);
             float b = __uint_as_float(acc[g * 8 + 2 * e + 1]);
-            if (BIAS) {
-                a += __uint_as_float(bw[e] << 16);
-                b += __uint_as_float(bw[e] & 0xffff0000u);
+            if (BIAS || GELU) {
+                // both elements of the pair go through one packed instruction per step; the
+                // packed operations round like their scalar counterparts
+                f32x2 x = pack2(a, b);
+                if (BIAS) x = add2(x, pack2(__uint_as_float(bw[e] << 16), __uint_as_float(bw[e] & 0xffff0000u)));
+                if (GELU) x = gelu_pair(x);
+                unpack2(x, a, b);
             }
-            if (GELU) { a = gelu_exact(a); b = gelu_exact(b); }
             __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
             pk[e] = *reinterpret_cast<uint32_t*>(&h);
             if (STAT) {
@@ -118,8 +139,8 @@ __device__ __forceinline__ float stage_chunk(const uint32_t (&sts)[4], const uin
     return (s0 + s1) + (s2 + s3);
 }
 
-template <bool STAT, bool BIAS, bool GELU, bool RES>
-__global__ void __launch_bounds__(NTHREADS, 1)
+template <bool STAT, bool BIAS, bool GELU, bool RES, bool WIDE>
+__global__ void __launch_bounds__(WIDE ? NTHREADS_WIDE : NTHREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
                const GemmTcParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -129,8 +150,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const uint32_t STAGES = p.stages;
     uint8_t* sA = smem;                                        // [STAGES][128 x KCH]
     uint8_t* sB = smem + STAGES * a_bytes;                     // ring [STAGES] or resident [KC] chunks of W
-    uint8_t* slabs = sB + (p.wstat ? p.KC : STAGES) * b_bytes; // 8 epilogue warps x 2 KB
-    uint64_t* bars = reinterpret_cast<uint64_t*>(slabs + 8 * 2048);
+    uint8_t* slabs = sB + (p.wstat ? p.KC : STAGES) * b_bytes; // one 2 KB slab per epilogue warp
+    uint64_t* bars = reinterpret_cast<uint64_t*>(slabs + (WIDE ? 16 : 8) * 2048);
+    static_assert(!(STAT && WIDE), "the fused statistic needs a row's whole head in one warp");
     uint64_t* full = bars;
     uint64_t* empty = bars + MAX_STAGES;
     uint64_t* tfull = bars + 2 * MAX_STAGES;
@@ -149,7 +171,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&tfull[b], 1);
-            mbar_init(&tempty[b], 4);
+            mbar_init(&tempty[b], WIDE ? 8 : 4);
         }
         mbar_init(wfull, 1);
         *abort_flag = 0;
@@ -256,8 +278,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
         }
     } else {
-        const int half = (warp - 2) >> 2;        // which TMEM buffer / tile parity this warp drains
+        const int half = ((warp - 2) >> 2) & 1;  // which TMEM buffer / tile parity this warp drains
+        const int chalf = (warp - 2) >> 3;       // WIDE: which half of the tile's column chunks
         const int lq = warp & 3;
+        // columns [c_begin, c_end) of every tile belong to this warp (whole 32-column chunks)
+        const int nchunk = (p.BN + 31) >> 5;
+        const int csplit = WIDE ? min(p.BN, 32 * ((nchunk + 1) >> 1)) : p.BN;
+        const int c_begin = chalf ? csplit : 0, c_end = chalf ? p.BN : csplit;
         const int r = lq * 32 + lane;
         const uint32_t slab = smem_u32(slabs + (warp - 2) * 2048);
         // shared-memory addresses of this lane's four 16-byte slots, for the row-wise write
@@ -271,7 +298,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         uint32_t tile = half;
         bool ok = true;
-        const bool tr = g_gemm_trace_on && blockIdx.x == 0 && lq == 0 && lane == 0;
+        const bool tr = g_gemm_trace_on && blockIdx.x == 0 && lq == 0 && lane == 0 && chalf == 0;
         int tn = 0;
         for (int t = first + half * step; t < last && ok; t += 2 * step, tile += 2) {
             int mt, nt;
@@ -333,7 +360,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 }
             };
             auto finish = [&](int c, const uint32_t (&acc)[32], const uint4 (&resv)[4], uint4 (&resn)[4]) {
-                if (c + 32 < p.BN) load_res(c + 32, resn);    // next chunk's residual, a chunk ahead of its use
+                if (!WIDE && c + 32 < p.BN) load_res(c + 32, resn);    // next chunk's residual, a chunk ahead of its use
                 const float css = stage_chunk<STAT, BIAS, GELU>(sts, acc, BIAS ? p.bias + n0 + c : nullptr, ncol - c);
                 if (STAT) {
                     if (stat) {
@@ -373,16 +400,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 }
                 __syncwarp();
             };
-            issue(0, ra);
-            load_res(0, resa);
-            for (int c = 0; c < p.BN; c += 64) {
-                tmem_ld_wait();
-                if (c + 32 < p.BN) issue(c + 32, rb);
-                finish(c, ra, resa, resb);
-                if (c + 32 < p.BN) {
+            if constexpr (WIDE) {
+                // four warps per scheduler cover each other's latencies: one chunk in flight per warp
+                for (int c = c_begin; c < c_end; c += 32) {
+                    load_res(c, resa);
+                    issue(c, ra);
                     tmem_ld_wait();
-                    if (c + 64 < p.BN) issue(c + 64, ra);
-                    finish(c + 32, rb, resb, resa);
+                    finish(c, ra, resa, resa);
+                }
+            } else {
+                issue(0, ra);
+                load_res(0, resa);
+                for (int c = 0; c < p.BN; c += 64) {
+                    tmem_ld_wait();
+                    if (c + 32 < p.BN) issue(c + 32, rb);
+                    finish(c, ra, resa, resb);
+                    if (c + 32 < p.BN) {
+                        tmem_ld_wait();
+                        if (c + 64 < p.BN) issue(c + 64, ra);
+                        finish(c + 32, rb, resb, resa);
+                    }
                 }
             }
             tc_fence_before_sync();
@@ -473,7 +510,12 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     // W-resident mode when the whole BN x Kd tile of W fits beside a useful ring of A chunks and
     // a CTA sees several row tiles per W tile; otherwise both operands stream through the ring.
-    const size_t fixed = 1024 + 8 * 2048 + (2 * MAX_STAGES + 5) * 8 + 16;
+    const bool has_stat = p.stat[0] || p.stat[1] || p.stat[2];
+    // An epilogue that does more than convert and store (bias, GELU, skip connection) is bound by
+    // its own instruction latencies: sixteen epilogue warps (each tile's columns split between two
+    // warps per TMEM lane quarter) cover them better than eight warps with ping-pong registers.
+    const bool wide = !has_stat && (o.bias || o.gelu || o.residual);
+    const size_t fixed = 1024 + (wide ? 16 : 8) * 2048 + (2 * MAX_STAGES + 5) * 8 + 16;
     const size_t budget = 200 * 1024;
     const size_t a_bytes = (size_t)BM * pitch, b_bytes = (size_t)p.BN * pitch;
     const size_t w_tile = (size_t)p.KC * b_bytes;
@@ -492,24 +534,29 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
         p.stages = st_ab > 6 ? 6 : (st_ab < 2 ? 2 : st_ab);
         smem = fixed + (size_t)p.stages * (a_bytes + b_bytes);
     }
-    const bool has_stat = p.stat[0] || p.stat[1] || p.stat[2];
     if (has_stat && (p.bias || p.residual || p.gelu))
         return set_error(CONVNN_E_UNSUPPORTED, "gemm_tc: statistics cannot be combined with bias / GELU / residual");
     if (p.gelu && p.residual) return set_error(CONVNN_E_UNSUPPORTED, "gemm_tc: GELU with a residual is not built");
-#define CONVNN_GEMM_LAUNCH(S, B, G, R)                                                                      \
+#define CONVNN_GEMM_LAUNCH1(S, B, G, R, W)                                                                  \
     do {                                                                                                    \
-        auto kern = gemm_tc_kernel<S, B, G, R>;                                                             \
+        auto kern = gemm_tc_kernel<S, B, G, R, W>;                                                          \
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         if (e != cudaSuccess) return set_error(CONVNN_E_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e)); \
-        kern<<<grid, NTHREADS, smem, st>>>(tmA, tmW, p);                                                    \
+        kern<<<grid, W ? NTHREADS_WIDE : NTHREADS, smem, st>>>(tmA, tmW, p);                                \
     } while (0)
-    if (has_stat) CONVNN_GEMM_LAUNCH(true, false, false, false);
+#define CONVNN_GEMM_LAUNCH(S, B, G, R)                          \
+    do {                                                        \
+        if (wide) CONVNN_GEMM_LAUNCH1(false, B, G, R, true);    \
+        else CONVNN_GEMM_LAUNCH1(S, B, G, R, false);            \
+    } while (0)
+    if (has_stat) CONVNN_GEMM_LAUNCH1(true, false, false, false, false);
     else if (p.gelu) { if (p.bias) CONVNN_GEMM_LAUNCH(false, true, true, false); else CONVNN_GEMM_LAUNCH(false, false, true, false); }
     else if (p.bias && p.residual) CONVNN_GEMM_LAUNCH(false, true, false, true);
     else if (p.bias) CONVNN_GEMM_LAUNCH(false, true, false, false);
     else if (p.residual) CONVNN_GEMM_LAUNCH(false, false, false, true);
     else CONVNN_GEMM_LAUNCH(false, false, false, false);
 #undef CONVNN_GEMM_LAUNCH
+#undef CONVNN_GEMM_LAUNCH1
     CONVNN_CHECK_LAUNCH("gemm_tc");
     return CONVNN_OK;
 }

@@ -271,6 +271,7 @@ sim_topk_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
                 if (warp_live) {
 #pragma unroll 1
                     for (int c = 0; c < p.BN; c += CW) {
+                        if (ct * p.BN + c >= p.S) break;         // the rest of the tile is padding
                         float q1; int c1;
                         stat_of(c, q1, c1);
                         if (CW == 32 && c + 32 <= p.BN) {
