@@ -157,10 +157,11 @@ const char* convnn_b200_last_error(void) { return g_err; }
 
 int convnn_b200_device_status(int* code) {
     if (!code) return set_error(CONVNN_E_NULL, "convnn_b200_device_status: argument 'code' is NULL");
-    int a = 0, b = 0, rc;
+    int a = 0, b = 0, c = 0, rc;
     if ((rc = read_sim_topk_status(&a))) return rc;
     if ((rc = read_gemm_tc_status(&b))) return rc;
-    *code = a ? a : b;
+    if ((rc = read_sim_topk2_status(&c))) return rc;
+    *code = a ? a : (b ? b : c);
     return CONVNN_OK;
 }
 

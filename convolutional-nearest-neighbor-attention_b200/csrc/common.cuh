@@ -90,7 +90,11 @@ int launch_sim_topk_simt_bf16(const convnn_desc* d, const Dims& dm, const void* 
 bool sim_topk_tc_supported(const convnn_desc* d, const Dims& dm, const void* q, const void* k);
 int launch_sim_topk_tc(const convnn_desc* d, const Dims& dm, const void* q, const void* k, const float* qstat,
                        const float* kstat, const int32_t* cand, int32_t* idx, float* val, cudaStream_t st);
+bool sim_topk_tc2_wanted(const convnn_desc* d, const Dims& dm);
+int launch_sim_topk_tc2(const convnn_desc* d, const Dims& dm, const void* q, const void* k, const float* qstat,
+                        const float* kstat, const int32_t* cand, int32_t* idx, float* val, cudaStream_t st);
 int read_sim_topk_status(int* out);
+int read_sim_topk2_status(int* out);
 int read_gemm_tc_status(int* out);
 int gemm_tc_trace(int enable, unsigned long long* host_out, int n);
 // bfloat16 tensor-core GEMM C = A W^T (+bias, +GELU); `parts` outputs share M and split N evenly.

@@ -1,0 +1,102 @@
+// Selection step shared by the tensor-core similarity kernels: a thread owns one key row
+// (= its TMEM lane) and is handed W accumulator columns of that row at a time.
+#pragma once
+#include "common.cuh"
+#include "toplist.cuh"
+
+namespace convnn {
+
+constexpr int kSelGroup = 128;    // threads per epilogue group = stride of the key staging buffer
+
+// One chunk of W accumulator columns of this thread's row: keys, then either plain inserts
+// (the first 32 columns of a row, where most values enter the list anyway) or a threshold
+// mask followed by a drain loop that only visits the survivors.
+// qv / cv hold the column statistic / candidate token of column (32-aligned base + lane).
+// P needs the fields metric, sampled and S (number of candidate columns).
+template <int NSEL, int W, class P>
+__device__ __forceinline__ void consume(TopList<NSEL>& top, const uint32_t (&acc)[W], int col0, int lane_off,
+                                        float qv, int cv, const P& p, int row, bool row_ok, float sentinel,
+                                        float* ks) {
+    float key[W];
+#pragma unroll
+    for (int j = 0; j < W; ++j) {
+        const float dot = __uint_as_float(acc[j]);
+        float k = dot;
+        if (p.metric != CONVNN_MATMUL) {
+            const float s = __shfl_sync(0xffffffffu, qv, lane_off + j);
+            k = (p.metric == CONVNN_COSINE) ? dot * s : fmaf(2.0f, dot, -s);
+        }
+        if (p.sampled) {
+            const int cj = __shfl_sync(0xffffffffu, cv, lane_off + j);
+            if (cj == row) k = sentinel;
+        }
+        key[j] = k;
+    }
+    const int left = p.S - col0;                       // valid columns from col0 on
+    if (col0 < 32) {
+#pragma unroll
+        for (int j = 0; j < W; ++j)
+            if (row_ok && j < left) top.insert_sorted(key[j], col0 + j);
+        return;
+    }
+    const float thr = top.worst();
+    uint32_t mask = 0;
+#pragma unroll
+    for (int j = 0; j < W; ++j) mask |= (key[j] > thr) ? (1u << j) : 0u;
+    if (left < W) mask &= (left <= 0) ? 0u : ((1u << left) - 1u);
+    if (!row_ok) mask = 0;
+    if (__any_sync(0xffffffffu, mask != 0)) {
+        // keys go through shared memory so the drain loop can pick column j per lane
+#pragma unroll
+        for (int j = 0; j < W; ++j) ks[j * kSelGroup] = key[j];
+        while (__any_sync(0xffffffffu, mask != 0)) {
+            if (mask) {
+                const int j = __ffs(mask) - 1;
+                mask &= mask - 1;
+                const float k = ks[j * kSelGroup];
+                if (k > top.worst()) top.insert_sorted(k, col0 + j);
+            }
+        }
+    }
+}
+
+// Ranking key of a sampled row's own column: the finite stand-in the reference uses
+// (-0.1 for the "larger is better" metrics, +1.1 for the distance), expressed in key units.
+__device__ __forceinline__ float self_sentinel(int metric, float kst, float sqrt_dk) {
+    if (metric == CONVNN_COSINE) return -0.1f / kst;
+    if (metric == CONVNN_MATMUL) return -0.1f * sqrt_dk;
+    return kst - 1.21f;
+}
+
+// Writes one row's selected (token, value) pairs: keys back to similarity values, candidate
+// columns back to token indices, the row itself in slot 0 for the sampled modes.
+template <int NSEL, class P>
+__device__ __forceinline__ void write_selection(const TopList<NSEL>& top, const P& p, long long obase, int row,
+                                                float kst) {
+    int off = 0;
+    if (p.sampled) {
+        p.idx[obase] = row;
+        p.val[obase] = 1.0f;
+        off = 1;
+    }
+#pragma unroll
+    for (int s = 0; s < NSEL; ++s) {
+        if (s < p.nsel) {
+            const int col = top.i[s];
+            const float key = top.v[s];
+            float v;
+            if (p.metric == CONVNN_COSINE) v = key * kst;
+            else if (p.metric == CONVNN_MATMUL) v = key / p.sqrt_dk;
+            else v = sqrtf(fmaxf(kst - key, 0.f));
+            int tok = col;
+            if (p.sampled) {
+                tok = p.cand[col];
+                if (tok == row) v = (p.metric == CONVNN_EUCLIDEAN) ? 1.1f : -0.1f;
+            }
+            p.idx[obase + off + s] = tok;
+            p.val[obase + off + s] = v;
+        }
+    }
+}
+
+}  // namespace convnn

@@ -23,6 +23,7 @@
 #include "common.cuh"
 #include "sm100.cuh"
 #include "toplist.cuh"
+#include "sim_topk_select.cuh"
 
 namespace convnn {
 
@@ -35,7 +36,7 @@ using namespace sm100;
 constexpr int BM = 128;
 constexpr int MAX_STAGES = 3;
 constexpr int NTHREADS = 320;     // TMA warp, MMA warp, 2 x 4 epilogue warps
-constexpr int GROUP = 128;        // threads per epilogue group
+constexpr int GROUP = kSelGroup;  // threads per epilogue group
 // Two launch shapes.  SMALL (short candidate lists, d_k <= 256): BN <= 64, 2 stages, 16-column
 // epilogue chunks and two CTAs per SM, so four epilogue warps per scheduler hide each other's
 // latency -- this regime is bound by the selection, not by the MMAs.  LARGE: BN <= 128, 3 stages,
@@ -60,57 +61,6 @@ struct TcParams {
 __device__ __forceinline__ void fail(volatile int* abort_flag, int code) {
     *abort_flag = 1;
     atomicCAS(&g_sim_topk_status, 0, code);
-}
-
-// One chunk of W accumulator columns of this thread's row: keys, then either plain inserts
-// (the first 32 columns of a row, where most values enter the list anyway) or a threshold
-// mask followed by a drain loop that only visits the survivors.
-// qv / cv hold the column statistic / candidate token of column (32-aligned base + lane).
-template <int NSEL, int W>
-__device__ __forceinline__ void consume(TopList<NSEL>& top, const uint32_t (&acc)[W], int col0, int lane_off,
-                                        float qv, int cv, const TcParams& p, int row, bool row_ok, float sentinel,
-                                        float* ks) {
-    float key[W];
-#pragma unroll
-    for (int j = 0; j < W; ++j) {
-        const float dot = __uint_as_float(acc[j]);
-        float k = dot;
-        if (p.metric != CONVNN_MATMUL) {
-            const float s = __shfl_sync(0xffffffffu, qv, lane_off + j);
-            k = (p.metric == CONVNN_COSINE) ? dot * s : fmaf(2.0f, dot, -s);
-        }
-        if (p.sampled) {
-            const int cj = __shfl_sync(0xffffffffu, cv, lane_off + j);
-            if (cj == row) k = sentinel;
-        }
-        key[j] = k;
-    }
-    const int left = p.S - col0;                       // valid columns from col0 on
-    if (col0 < 32) {
-#pragma unroll
-        for (int j = 0; j < W; ++j)
-            if (row_ok && j < left) top.insert_sorted(key[j], col0 + j);
-        return;
-    }
-    const float thr = top.worst();
-    uint32_t mask = 0;
-#pragma unroll
-    for (int j = 0; j < W; ++j) mask |= (key[j] > thr) ? (1u << j) : 0u;
-    if (left < W) mask &= (left <= 0) ? 0u : ((1u << left) - 1u);
-    if (!row_ok) mask = 0;
-    if (__any_sync(0xffffffffu, mask != 0)) {
-        // keys go through shared memory so the drain loop can pick column j per lane
-#pragma unroll
-        for (int j = 0; j < W; ++j) ks[j * GROUP] = key[j];
-        while (__any_sync(0xffffffffu, mask != 0)) {
-            if (mask) {
-                const int j = __ffs(mask) - 1;
-                mask &= mask - 1;
-                const float k = ks[j * GROUP];
-                if (k > top.worst()) top.insert_sorted(k, col0 + j);
-            }
-        }
-    }
 }
 
 template <int NSEL, int MINB, int CW>
@@ -233,12 +183,7 @@ sim_topk_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
             const float* qs_row = p.qstat ? p.qstat + (long long)bh * p.S : nullptr;
             float kst = 1.0f;
             if (row_ok && p.metric != CONVNN_MATMUL) kst = p.kstat[(long long)bh * p.T + row];
-            float sentinel = 0.f;
-            if (p.sampled) {
-                if (p.metric == CONVNN_COSINE) sentinel = -0.1f / kst;
-                else if (p.metric == CONVNN_MATMUL) sentinel = -0.1f * p.sqrt_dk;
-                else sentinel = kst - 1.21f;
-            }
+            const float sentinel = p.sampled ? self_sentinel(p.metric, kst, p.sqrt_dk) : 0.f;
             TopList<NSEL> top;
             top.init();
             // column statistics (4 x 32 columns cover BN <= 128), fetched one tile ahead
@@ -294,31 +239,7 @@ sim_topk_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
                 for (int c4 = 0; c4 < 4; ++c4) { qv[c4] = qn[c4]; cv[c4] = cn[c4]; }
             }
             if (ok && row_ok) {
-                const long long obase = ((long long)bh * p.T + row) * p.K;
-                int off = 0;
-                if (p.sampled) {
-                    p.idx[obase] = row;
-                    p.val[obase] = 1.0f;
-                    off = 1;
-                }
-#pragma unroll
-                for (int s = 0; s < NSEL; ++s) {
-                    if (s < p.nsel) {
-                        const int col = top.i[s];
-                        const float key = top.v[s];
-                        float v;
-                        if (p.metric == CONVNN_COSINE) v = key * kst;
-                        else if (p.metric == CONVNN_MATMUL) v = key / p.sqrt_dk;
-                        else v = sqrtf(fmaxf(kst - key, 0.f));
-                        int tok = col;
-                        if (p.sampled) {
-                            tok = p.cand[col];
-                            if (tok == row) v = (p.metric == CONVNN_EUCLIDEAN) ? 1.1f : -0.1f;
-                        }
-                        p.idx[obase + off + s] = tok;
-                        p.val[obase + off + s] = v;
-                    }
-                }
+                write_selection<NSEL>(top, p, ((long long)bh * p.T + row) * p.K, row, kst);
             }
         }
     }
@@ -351,6 +272,7 @@ bool sim_topk_tc_supported(const convnn_desc* d, const Dims& dm, const void* q, 
 
 int launch_sim_topk_tc(const convnn_desc* d, const Dims& dm, const void* q, const void* k, const float* qstat,
                        const float* kstat, const int32_t* cand, int32_t* idx, float* val, cudaStream_t st) {
+    if (sim_topk_tc2_wanted(d, dm)) return launch_sim_topk_tc2(d, dm, q, k, qstat, kstat, cand, idx, val, st);
     TcParams p{};
     p.qstat = qstat; p.kstat = kstat; p.cand = cand; p.idx = idx; p.val = val;
     p.T = dm.T; p.S = dm.S; p.H = dm.H; p.K = dm.K; p.nsel = dm.nsel; p.metric = d->metric; p.sampled = d->sampled;

@@ -50,6 +50,25 @@ struct TopList {
         v[0] = g0 ? key : v[0];
         i[0] = g0 ? col : i[0];
     }
+
+    // Insert under the full (key, column) order: among equal keys the lower column ranks
+    // first wherever it came from.  Used to merge lists built over interleaved column ranges,
+    // where "inserted first" no longer means "lower column".
+    __device__ __forceinline__ static bool ranks_before(float k, int c, float v0, int i0) {
+        return k > v0 || (k == v0 && c < i0);
+    }
+    __device__ __forceinline__ void insert_ordered(float key, int col) {
+#pragma unroll
+        for (int s = N - 1; s >= 1; --s) {
+            const bool gt = ranks_before(key, col, v[s], i[s]);
+            const bool gtp = ranks_before(key, col, v[s - 1], i[s - 1]);
+            v[s] = gt ? (gtp ? v[s - 1] : key) : v[s];
+            i[s] = gt ? (gtp ? i[s - 1] : col) : i[s];
+        }
+        const bool g0 = ranks_before(key, col, v[0], i[0]);
+        v[0] = g0 ? key : v[0];
+        i[0] = g0 ? col : i[0];
+    }
 };
 
 }  // namespace convnn

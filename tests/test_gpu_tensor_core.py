@@ -1,6 +1,7 @@
 """The tcgen05 similarity/top-K kernel on shapes that exercise every tiling path:
 several row tiles, several column tiles with a ragged last tile, the 128/64/32-byte
-swizzle chunkings (d_k multiple of 64 / 32 / 16), K up to 32, sampled masks."""
+swizzle chunkings (d_k multiple of 64 / 32 / 16), K up to 32, sampled masks, and the
+CTA-pair kernel that takes over on long sequences."""
 import pytest
 import torch
 
@@ -21,6 +22,11 @@ CASES = [
     (1, 130, 130, 48, 1, 32, "euclidean", "all"),
     (1, 1030, 1030, 64, 1, 4, "cosine", "all"),
     (2, 50, 17, 32, 1, 16, "matmul", "random"),
+    # long key and candidate lists: the CTA-pair kernel (256-row units, 256-column tiles, ragged ends)
+    (2, 1536, 1200, 128, 2, 9, "euclidean", "random"),
+    (1, 2048, 2048, 192, 1, 16, "matmul", "all"),
+    (1, 1300, 1300, 64, 1, 9, "cosine", "all"),
+    (1, 1100, 1100, 64, 1, 25, "cosine", "all"),      # list too long for the pair kernel's merge buffer
 ]
 
 
@@ -67,3 +73,24 @@ def test_tensor_core_and_simt_kernels_agree_bitwise_on_indices():
     same = (i16 == i32).all(-1)
     assert float(same.float().mean()) > 0.999
     assert float((v16 - v32).abs().max()) < 1e-4
+
+
+def test_pair_kernel_orders_exact_ties_by_column():
+    """Two identical candidate rows whose columns fall into different column halves of
+    different tiles (130: upper half of tile 0, 300: lower half of tile 1): both are selected
+    by the key rows that resemble them, and the lower column comes first."""
+    g = torch.Generator().manual_seed(11)
+    T = S = 1024
+    q = torch.randn(1, S, 1, 64, generator=g).to(torch.bfloat16)
+    k = torch.randn(1, T, 1, 64, generator=g).to(torch.bfloat16)
+    q[0, 300] = q[0, 130]
+    k[0, 5] = q[0, 130]
+    k[0, 700] = q[0, 130]
+    cfg = ConvNNConfig(d_hidden=64, num_heads=1, K=9, magnitude_type="matmul", seq_length=T)
+    idx, val = ops.sim_topk(spec_of(cfg), q.to(DEV), k.to(DEV), None, None)
+    torch.cuda.synchronize()
+    assert _capi.device_status() == 0
+    for row in (5, 700):
+        got = idx[0, 0, row].tolist()
+        assert got[0] == 130 and got[1] == 300, got
+        assert float(val[0, 0, row, 0]) == float(val[0, 0, row, 1])
