@@ -39,7 +39,6 @@ constexpr int STAGES = 5;
 constexpr int NTHREADS = 320;
 constexpr int CW = 32;             // accumulator columns per tcgen05.ld
 constexpr uint32_t A_BYTES = BM * KCH * 2, B_BYTES = BNH * KCH * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int MAX_NSEL2 = 16;      // the merge buffer holds 16 (key, column) pairs per row
 
 struct Tc2Params {
     const float* qstat;
@@ -67,8 +66,8 @@ sim_topk_tc2_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* stages = smem;                                                   // [STAGES][A | B]
     float* keybuf = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES);    // [2 column halves][CW][128]
-    float* mbuf = keybuf + 2 * CW * kSelGroup;                                // [2 * MAX_NSEL2][128] merge hand-over
-    uint64_t* bars = reinterpret_cast<uint64_t*>(mbuf + 2 * MAX_NSEL2 * kSelGroup);
+    float* mbuf = keybuf + 2 * CW * kSelGroup;                                // [2 * NSEL][128] merge hand-over
+    uint64_t* bars = reinterpret_cast<uint64_t*>(mbuf + 2 * NSEL * kSelGroup);
     uint64_t* full = bars;                      // used in the leader only
     uint64_t* empty = bars + STAGES;
     uint64_t* tfull = bars + 2 * STAGES;
@@ -277,11 +276,14 @@ sim_topk_tc2_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
 }  // namespace
 
 // The pair kernel pays off where the tensor pipe is the limiter: long key and candidate
-// lists, full 64-channel chunks, lists short enough for the merge buffer.
+// lists, full 64-channel chunks.
 bool sim_topk_tc2_wanted(const convnn_desc* d, const Dims& dm) {
     static const int env = [] { const char* e = getenv("CONVNN_B200_SIM_PAIR"); return e ? atoi(e) : -1; }();
     if (env == 0) return false;
-    if (d->dtype != CONVNN_BF16 || dm.Cp % 64 != 0 || dm.nsel > MAX_NSEL2) return false;
+    if (d->dtype != CONVNN_BF16 || dm.Cp % 64 != 0) return false;
+    // Lists longer than 16 double the cost of keeping two lists per row; measured break-even
+    // is at many units per cluster and a few thousand candidates.
+    if (dm.nsel > 16) return dm.T >= 8192 && dm.S >= 4096;
     return dm.T >= 1024 && dm.S >= 1024;
 }
 
@@ -306,12 +308,13 @@ int launch_sim_topk_tc2(const convnn_desc* d, const Dims& dm, const void* q, con
     if (!encode_tensor_map_bf16(&tmK, k, 4, dimsK, strK, boxK, KCH * 2)) return CONVNN_E_CUDA;
     if (!encode_tensor_map_bf16(&tmQ, q, 4, dimsQ, strQ, boxQ, KCH * 2)) return CONVNN_E_CUDA;
 
-    const size_t smem = 1024 + (size_t)STAGES * STAGE_BYTES + 2 * CW * kSelGroup * sizeof(float) +
-                        2 * MAX_NSEL2 * kSelGroup * sizeof(float) + (2 * STAGES + 12) * 8 + 16;
+    const size_t smem_fixed = 1024 + (size_t)STAGES * STAGE_BYTES + 2 * CW * kSelGroup * sizeof(float) +
+                              (2 * STAGES + 12) * 8 + 16;
 
 #define CONVNN_TC2_LAUNCH(N)                                                                                     \
     do {                                                                                                         \
         auto kern = sim_topk_tc2_kernel<N>;                                                                      \
+        const size_t smem = smem_fixed + 2 * N * kSelGroup * sizeof(float);                                      \
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
         if (e != cudaSuccess) return set_error(CONVNN_E_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e)); \
         cudaLaunchConfig_t cfg{};                                                                                \
@@ -335,7 +338,10 @@ int launch_sim_topk_tc2(const convnn_desc* d, const Dims& dm, const void* q, con
     else if (n <= 8) CONVNN_TC2_LAUNCH(8);
     else if (n == 9) CONVNN_TC2_LAUNCH(9);
     else if (n <= 12) CONVNN_TC2_LAUNCH(12);
-    else CONVNN_TC2_LAUNCH(16);
+    else if (n <= 16) CONVNN_TC2_LAUNCH(16);
+    else if (n <= 24) CONVNN_TC2_LAUNCH(24);
+    else if (n == 25) CONVNN_TC2_LAUNCH(25);
+    else CONVNN_TC2_LAUNCH(32);
 #undef CONVNN_TC2_LAUNCH
     CONVNN_CHECK_LAUNCH("sim_topk_tc2");
     return CONVNN_OK;

@@ -26,7 +26,9 @@ CASES = [
     (2, 1536, 1200, 128, 2, 9, "euclidean", "random"),
     (1, 2048, 2048, 192, 1, 16, "matmul", "all"),
     (1, 1300, 1300, 64, 1, 9, "cosine", "all"),
-    (1, 1100, 1100, 64, 1, 25, "cosine", "all"),      # list too long for the pair kernel's merge buffer
+    (1, 1100, 1100, 64, 1, 25, "cosine", "all"),      # long lists on short sequences stay on the single-CTA kernel
+    (1, 8200, 4100, 64, 1, 25, "cosine", "spatial"),  # ... and move to the pair kernel on long ones
+    (1, 8192, 4096, 64, 1, 32, "euclidean", "random"),
 ]
 
 
