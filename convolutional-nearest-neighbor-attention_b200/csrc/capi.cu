@@ -161,6 +161,7 @@ int convnn_b200_device_status(int* code) {
     if ((rc = read_sim_topk_status(&a))) return rc;
     if ((rc = read_gemm_tc_status(&b))) return rc;
     if ((rc = read_sim_topk2_status(&c))) return rc;
+    if (!c && (rc = read_dw_stream_status(&c))) return rc;
     *code = a ? a : (b ? b : c);
     return CONVNN_OK;
 }

@@ -95,6 +95,9 @@ int launch_sim_topk_tc2(const convnn_desc* d, const Dims& dm, const void* q, con
                         const float* kstat, const int32_t* cand, int32_t* idx, float* val, cudaStream_t st);
 int read_sim_topk_status(int* out);
 int read_sim_topk2_status(int* out);
+int try_launch_gather_conv_dw_stream(const convnn_desc* d, const Dims& dm, const void* v, const int32_t* idx,
+                                     const float* val, const void* w_conv, void* o, cudaStream_t st);
+int read_dw_stream_status(int* out);
 int read_gemm_tc_status(int* out);
 int gemm_tc_trace(int enable, unsigned long long* host_out, int n);
 // bfloat16 tensor-core GEMM C = A W^T (+bias, +GELU); `parts` outputs share M and split N evenly.

@@ -18,32 +18,12 @@
 // standard conv materialises the weighted block once, in bfloat16).
 #include "common.cuh"
 #include "f32x2.cuh"
+#include "token_weights.cuh"
 
 namespace convnn {
 namespace {
 
 constexpr int THREADS = 256;
-
-// p[j] for one token (layers.py:352-355, 394-397): softmax(+-val), val, or 1/(val+1e-8).
-__device__ __forceinline__ void token_weights(const float* __restrict__ val, float* __restrict__ p, int K,
-                                              bool maximum, bool softmax) {
-    if (softmax) {
-        float m = -3.402823466e38f;
-        for (int j = 0; j < K; ++j) {
-            float x = maximum ? val[j] : -val[j];
-            m = fmaxf(m, x);
-        }
-        float s = 0.f;
-        for (int j = 0; j < K; ++j) {
-            float e = expf((maximum ? val[j] : -val[j]) - m);
-            p[j] = e;
-            s += e;
-        }
-        for (int j = 0; j < K; ++j) p[j] = p[j] / s;
-    } else {
-        for (int j = 0; j < K; ++j) p[j] = maximum ? val[j] : 1.0f / (val[j] + 1e-8f);
-    }
-}
 
 template <typename T, int VEC> struct VecLoad;
 template <> struct VecLoad<float, 4> {
@@ -475,6 +455,8 @@ int launch_dw_smem(const convnn_desc* d, const Dims& dm, const void* v, const in
 // last_error) when the slice does not fit or the layout is not vectorisable.
 int try_launch_gather_conv_dw_smem(const convnn_desc* d, const Dims& dm, const void* v, const int32_t* idx,
                                    const float* val, const void* w_conv, void* o, cudaStream_t st) {
+    const int rcs = try_launch_gather_conv_dw_stream(d, dm, v, idx, val, w_conv, o, st);
+    if (rcs != CONVNN_E_UNSUPPORTED) return rcs;
     const bool f32 = d->dtype == CONVNN_F32;
     const int vec = f32 ? 4 : 8;
     if (dm.dk % vec != 0 || dm.Cp % vec != 0 || dm.dk / vec > 256 || !aligned16(v) || !aligned16(o) || !aligned16(w_conv))
