@@ -13,6 +13,9 @@
 //              coalesced 16-byte global stores (+ residual); two tiles drain concurrently.
 //              The WIDE variant adds warps 10-17, which take the upper half of each tile's
 //              column chunks (same lane quarters, same two buffers).
+// A bias whose rows fit in 24 KB of shared memory is not added in the epilogue: one extra
+// K = 16 MMA per tile (a 128 x 16 operand of ones times a [BN x 16] operand holding the bias)
+// preloads the accumulator with it.
 // The N range may be split into up to three equal parts with their own output tensors,
 // which lets one launch produce k, v and q from the packed [W_k; W_v; W_q].
 // Every mbarrier wait is bounded (see sm100.cuh); an expiry latches the device status.
@@ -41,7 +44,8 @@ constexpr int NTHREADS_WIDE = 576;    // ... or 2 x 8 epilogue warps (each tile'
 struct GemmTcParams {
     __nv_bfloat16* c[3];
     long long ldc;
-    const __nv_bfloat16* bias;
+    const __nv_bfloat16* bias;       // added in the epilogue, or
+    const __nv_bfloat16* mma_bias;   // preloaded into the accumulator by one extra K = 16 MMA per tile
     const __nv_bfloat16* residual;   // added after rounding the GEMM result (torch: y = x + linear(...))
     long long ldr;
     float* stat[3];        // per part: per-(row, head) statistic of the stored values, or nullptr
@@ -151,7 +155,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint8_t* sA = smem;                                        // [STAGES][128 x KCH]
     uint8_t* sB = smem + STAGES * a_bytes;                     // ring [STAGES] or resident [KC] chunks of W
     uint8_t* slabs = sB + (p.wstat ? p.KC : STAGES) * b_bytes; // one 2 KB slab per epilogue warp
-    uint64_t* bars = reinterpret_cast<uint64_t*>(slabs + (WIDE ? 16 : 8) * 2048);
+    // bias through the tensor cores: a 128 x 16 operand of ones (4 KB) and, per output column, a
+    // 16-element row holding the bias in element 0 (32 B per column, all column tiles)
+    uint8_t* ones = slabs + (WIDE ? 16 : 8) * 2048;
+    uint8_t* btile = ones + (p.mma_bias ? 4096 : 0);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(btile + (p.mma_bias ? (size_t)p.n_n_tiles * p.BN * 32 : 0));
     static_assert(!(STAT && WIDE), "the fused statistic needs a row's whole head in one warp");
     uint64_t* full = bars;
     uint64_t* empty = bars + MAX_STAGES;
@@ -182,6 +190,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (warp == 1) {
         tmem_alloc(tmem_slot, ncols);
         tmem_relinquish();
+    }
+    if (p.mma_bias) {
+        // D = ones * btile^T = bias[n] in every row.  Both 16-byte halves of a row of `ones`
+        // start with 1.0 and a btile row holds its bias in exactly one half, so the product
+        // does not depend on how the 32-byte swizzle orders the halves.
+        const uint4 one_v = make_uint4(0x00003F80u, 0u, 0u, 0u);      // bf16 1.0 in element 0
+        for (int i = threadIdx.x; i < BM * 2; i += blockDim.x) reinterpret_cast<uint4*>(ones)[i] = one_v;
+        const int ncols_all = p.n_n_tiles * p.BN;
+        for (int n = threadIdx.x; n < ncols_all; n += blockDim.x) {
+            uint32_t b = 0;
+            if (n < p.N) b = *reinterpret_cast<const unsigned short*>(p.mma_bias + n);
+            reinterpret_cast<uint4*>(btile)[2 * n] = make_uint4(b, 0u, 0u, 0u);
+            reinterpret_cast<uint4*>(btile)[2 * n + 1] = make_uint4(0u, 0u, 0u, 0u);
+        }
+        fence_proxy_async();                    // generic-proxy writes -> visible to the MMA's reads
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -244,6 +267,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const uint64_t dhi = kmajor_desc_hi(pitch);
             const int nk16 = p.KCH / 16;
             const uint32_t tfull0 = smem_u32(tfull), tempty0 = smem_u32(tempty);
+            const bool mbias = p.mma_bias != nullptr;
+            const uint64_t dhi32 = kmajor_desc_hi(32);
+            const uint64_t ones_desc = dhi32 | (uint64_t)((smem_u32(ones) & 0x3FFFFu) >> 4);
+            const uint32_t btile0 = smem_u32(btile) & 0x3FFFFu;
             uint32_t s = 0, ph = 0, tile = 0, wloads = 0;
             int cur_nt = -1;
             bool ok = true;
@@ -253,9 +280,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 const uint32_t buf = tile & 1u, u = tile >> 1;
                 if (!mbar_wait_a(tempty0 + 8 * buf, (u & 1u) ^ 1u, abort_flag)) { fail(abort_flag, 12); ok = false; break; }
                 trace(tr, 1, tn);                           // accumulator buffer free
+                int mt = 0, nt = 0;
+                if (p.wstat || mbias) tile_mn(t, mt, nt);
                 if (p.wstat) {
-                    int mt, nt;
-                    tile_mn(t, mt, nt);
                     if (nt != cur_nt) {
                         if (!mbar_wait_a(wfull_a, wloads & 1u, abort_flag)) { fail(abort_flag, 16); ok = false; break; }
                         cur_nt = nt;
@@ -264,12 +291,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 }
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + buf * p.BNpad;
+                if (mbias)                                   // accumulator := bias, the chunks add to it
+                    mma_bf16_ss(d_tmem, ones_desc, dhi32 | (uint64_t)((btile0 + (uint32_t)nt * p.BN * 32u) >> 4), idesc, 0);
                 for (int kc = 0; kc < p.KC; ++kc) {
                     if (!mbar_wait_a(full0 + 8 * s, ph, abort_flag)) { fail(abort_flag, 13); ok = false; break; }
                     tc_fence_after_sync();
                     const uint64_t adesc = dhi | (uint64_t)((sA0 + s * a_bytes) >> 4);
                     const uint64_t bdesc = dhi | (uint64_t)((sB0 + (p.wstat ? (uint32_t)kc : s) * b_bytes) >> 4);
-                    mma_chunk(d_tmem, adesc, bdesc, idesc, nk16, kc != 0);
+                    mma_chunk(d_tmem, adesc, bdesc, idesc, nk16, (kc != 0) | mbias);
                     mma_commit_a(empty0 + 8 * s);
                     if (++s == STAGES) { s = 0; ph ^= 1u; }
                 }
@@ -480,6 +509,7 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
         p.stat[i] = i < parts ? o.stat[i] : nullptr;
     }
     p.ldc = ldc; p.bias = static_cast<const __nv_bfloat16*>(o.bias); p.gelu = o.gelu;
+    p.mma_bias = nullptr;
     p.residual = static_cast<const __nv_bfloat16*>(o.residual); p.ldr = o.ldr;
     p.stat_mode = o.stat_mode; p.dk = o.dk > 0 ? o.dk : 32; p.heads = o.heads; p.rows_per_batch = o.rows_per_batch > 0 ? o.rows_per_batch : 1;
     p.M = M; p.N = N;
@@ -511,12 +541,23 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
     // W-resident mode when the whole BN x Kd tile of W fits beside a useful ring of A chunks and
     // a CTA sees several row tiles per W tile; otherwise both operands stream through the ring.
     const bool has_stat = p.stat[0] || p.stat[1] || p.stat[2];
-    // An epilogue that does more than convert and store (bias, GELU, skip connection) is bound by
-    // its own instruction latencies: sixteen epilogue warps (each tile's columns split between two
-    // warps per TMEM lane quarter) cover them better than eight warps with ping-pong registers.
-    const bool wide = !has_stat && (o.bias || o.gelu || o.residual);
-    const size_t fixed = 1024 + (wide ? 16 : 8) * 2048 + (2 * MAX_STAGES + 5) * 8 + 16;
-    const size_t budget = 200 * 1024;
+    // Bias through the tensor cores (one extra K = 16 MMA per tile instead of an unpack and an add
+    // per element in the epilogue) when the bias rows of all column tiles fit in 24 KB.
+    const size_t bias_rows = (size_t)p.n_n_tiles * p.BN * 32;
+    const bool bias_by_mma = p.bias && !has_stat && bias_rows <= 24 * 1024;
+    // An epilogue that does more than convert and store (bias added per element, GELU, skip
+    // connection) is bound by its own instruction latencies: sixteen epilogue warps (each tile's
+    // columns split between two warps per TMEM lane quarter) cover them better than eight warps
+    // with ping-pong registers.
+    const bool wide = !has_stat && ((o.bias && !bias_by_mma) || o.gelu || o.residual);
+    size_t fixed = 1024 + (wide ? 16 : 8) * 2048 + (2 * MAX_STAGES + 5) * 8 + 16;
+    size_t budget = 200 * 1024;
+    if (bias_by_mma) {
+        p.mma_bias = p.bias;
+        p.bias = nullptr;
+        fixed += 4096 + bias_rows;
+        budget = 226 * 1024;
+    }
     const size_t a_bytes = (size_t)BM * pitch, b_bytes = (size_t)p.BN * pitch;
     const size_t w_tile = (size_t)p.KC * b_bytes;
     p.wstat = (w_tile + 3 * a_bytes + fixed <= budget && p.n_tiles >= 2 * sms) ? 1 : 0;
