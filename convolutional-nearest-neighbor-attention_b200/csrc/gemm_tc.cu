@@ -551,7 +551,11 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
     // with ping-pong registers.
     const bool wide = !has_stat && ((o.bias && !bias_by_mma) || o.gelu || o.residual);
     size_t fixed = 1024 + (wide ? 16 : 8) * 2048 + (2 * MAX_STAGES + 5) * 8 + 16;
+    // W-resident mode is judged against 200 KB (with more, shapes whose W tile barely fits would
+    // be left with a ring too short to cover the TMA latency); the streaming ring takes all the
+    // shared memory there is, which is worth 5-10 % on deep reductions (K >= 384).
     size_t budget = 200 * 1024;
+    const size_t budget_stream = 226 * 1024;
     if (bias_by_mma) {
         p.mma_bias = p.bias;
         p.bias = nullptr;
@@ -571,7 +575,7 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
         smem = fixed + w_tile + (size_t)p.stages * a_bytes;
     } else {
         grid = p.n_tiles < sms ? p.n_tiles : sms;
-        int st_ab = (int)((budget - fixed) / (a_bytes + b_bytes));
+        int st_ab = (int)((budget_stream - fixed) / (a_bytes + b_bytes));
         p.stages = st_ab > 6 ? 6 : (st_ab < 2 ? 2 : st_ab);
         smem = fixed + (size_t)p.stages * (a_bytes + b_bytes);
     }
