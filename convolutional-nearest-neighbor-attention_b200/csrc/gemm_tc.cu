@@ -64,6 +64,11 @@ __device__ __forceinline__ void fail(volatile int* abort_flag, int code) {
     *abort_flag = 1;
     atomicCAS(&g_gemm_tc_status, 0, code);
 }
+// CTA-pair variant: the peer's waits give up as well
+__device__ __forceinline__ void fail_pair(volatile int* abort_flag, uint32_t peer_abort, int code) {
+    st_cluster_u32(peer_abort, 1u);
+    fail(abort_flag, code);
+}
 
 __device__ __forceinline__ void trace(bool on, int region, int& n) {
     if (on && n < 512) g_gemm_trace[region * 512 + n++] = clock64();
@@ -75,17 +80,8 @@ __device__ __forceinline__ void trace(bool on, int region, int& n) {
 // step of the stored activations), and this costs 7 instructions per element instead of ~17
 // for a faithful erf: the activation runs in the GEMM epilogue, where instruction issue is
 // what bounds the kernel.  The float32 path (SIMT GEMM) uses erff.
-__device__ __forceinline__ float gelu_exact(float x) {
-    const float x2 = x * x;
-    const float inner = x * fmaf(0.0356774081f, x2, 0.7978845608f);   // sqrt(2/pi) * (x + 0.044715 x^3)
-    float th;
-    asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(inner));
-    const float half_x = 0.5f * x;
-    return fmaf(half_x, th, half_x);
-}
-
-// The same function on a packed pair (identical roundings: every step is the packed form of
-// the scalar instruction above).
+// Evaluated on packed pairs: x * (c0 + c1 x^2) -> tanh -> 0.5 x (1 + tanh), every step one packed
+// instruction that rounds like its scalar counterpart.
 __device__ __forceinline__ f32x2 gelu_pair(f32x2 x) {
     const f32x2 c1 = pack2(0.0356774081f, 0.0356774081f), c0 = pack2(0.7978845608f, 0.7978845608f);
     const f32x2 hf = pack2(0.5f, 0.5f);
@@ -143,15 +139,26 @@ __device__ __forceinline__ float stage_chunk(const uint32_t (&sts)[4], const uin
     return (s0 + s1) + (s2 + s3);
 }
 
-template <bool STAT, bool BIAS, bool GELU, bool RES, bool WIDE>
+// PAIR: two CTAs of a cluster form one MMA unit (tcgen05 cta_group::2): a tile is 256 rows (128
+// per CTA) by BN columns of which each CTA stages BN / 2 rows of W, so every CTA reads and
+// fetches half the W bytes per flop.  The even CTA issues the MMAs; loads of both CTAs credit its
+// "full" barriers, completions are committed to the barriers of both CTAs, and the epilogue
+// warps of both release the accumulator on the leader's "tempty" barriers.  Streaming mode only.
+template <bool STAT, bool BIAS, bool GELU, bool RES, bool WIDE, bool PAIR>
 __global__ void __launch_bounds__(WIDE ? NTHREADS_WIDE : NTHREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
                const GemmTcParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t pitch = p.KCH * 2;
-    const uint32_t a_bytes = BM * pitch, b_bytes = p.BN * pitch;
+    const int bn_cta = PAIR ? p.BN / 2 : p.BN;               // rows of W staged by this CTA
+    const uint32_t a_bytes = BM * pitch, b_bytes = bn_cta * pitch;
     const uint32_t STAGES = p.stages;
+    static_assert(!(PAIR && STAT), "the pair schedule has no fused statistic");
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;     // 0 = leader
+    const int cta_id = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int n_ctas = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+    constexpr int TM = PAIR ? 2 * BM : BM;                    // rows per tile
     uint8_t* sA = smem;                                        // [STAGES][128 x KCH]
     uint8_t* sB = smem + STAGES * a_bytes;                     // ring [STAGES] or resident [KC] chunks of W
     uint8_t* slabs = sB + (p.wstat ? p.KC : STAGES) * b_bytes; // one 2 KB slab per epilogue warp
@@ -159,7 +166,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // 16-element row holding the bias in element 0 (32 B per column, all column tiles)
     uint8_t* ones = slabs + (WIDE ? 16 : 8) * 2048;
     uint8_t* btile = ones + (p.mma_bias ? 4096 : 0);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(btile + (p.mma_bias ? (size_t)p.n_n_tiles * p.BN * 32 : 0));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(btile + (p.mma_bias ? (size_t)p.n_n_tiles * bn_cta * 32 : 0));
     static_assert(!(STAT && WIDE), "the fused statistic needs a row's whole head in one warp");
     uint64_t* full = bars;
     uint64_t* empty = bars + MAX_STAGES;
@@ -179,7 +186,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&tfull[b], 1);
-            mbar_init(&tempty[b], WIDE ? 8 : 4);
+            mbar_init(&tempty[b], (WIDE ? 8 : 4) * (PAIR ? 2 : 1));
         }
         mbar_init(wfull, 1);
         *abort_flag = 0;
@@ -187,9 +194,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         prefetch_tensormap(&tmA);
         prefetch_tensormap(&tmW);
     }
+    if (PAIR) __syncthreads();                  // barriers initialised before the pair-wide allocation returns
     if (warp == 1) {
-        tmem_alloc(tmem_slot, ncols);
-        tmem_relinquish();
+        if (PAIR) { tmem_alloc_pair(tmem_slot, ncols); tmem_relinquish_pair(); }
+        else { tmem_alloc(tmem_slot, ncols); tmem_relinquish(); }
     }
     if (p.mma_bias) {
         // D = ones * btile^T = bias[n] in every row.  Both 16-byte halves of a row of `ones`
@@ -197,10 +205,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // does not depend on how the 32-byte swizzle orders the halves.
         const uint4 one_v = make_uint4(0x00003F80u, 0u, 0u, 0u);      // bf16 1.0 in element 0
         for (int i = threadIdx.x; i < BM * 2; i += blockDim.x) reinterpret_cast<uint4*>(ones)[i] = one_v;
-        const int ncols_all = p.n_n_tiles * p.BN;
+        const int ncols_all = p.n_n_tiles * bn_cta;
         for (int n = threadIdx.x; n < ncols_all; n += blockDim.x) {
             uint32_t b = 0;
-            if (n < p.N) b = *reinterpret_cast<const unsigned short*>(p.mma_bias + n);
+            // row n of this CTA's bias tile: column tile n / bn_cta, this CTA's part of its columns
+            const int col = (n / bn_cta) * p.BN + (int)rank * bn_cta + n % bn_cta;
+            if (col < p.N) b = *reinterpret_cast<const unsigned short*>(p.mma_bias + col);
             reinterpret_cast<uint4*>(btile)[2 * n] = make_uint4(b, 0u, 0u, 0u);
             reinterpret_cast<uint4*>(btile)[2 * n + 1] = make_uint4(0u, 0u, 0u, 0u);
         }
@@ -208,14 +218,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     tc_fence_before_sync();
     __syncthreads();
+    if (PAIR) cluster_sync_all();               // both CTAs' barriers exist before any remote signal
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    const uint32_t peer_abort = PAIR ? map_to_cta(smem_u32(const_cast<int*>(abort_flag)), rank ^ 1u) : 0u;
+    auto give_up = [&](int code) {
+        if (PAIR) fail_pair(abort_flag, peer_abort, code);
+        else fail(abort_flag, code);
+    };
 
     // Tile order.  Streaming mode: tile k of this CTA is blockIdx.x + k * gridDim.x in the m-major
     // list (n fastest).  W-resident mode: a contiguous range of the n-major list (m fastest), so
     // the W tile changes at most a few times per CTA.
-    const int first = p.wstat ? blockIdx.x * p.tiles_per_cta : blockIdx.x;
-    const int step = p.wstat ? 1 : gridDim.x;
+    const int first = p.wstat ? cta_id * p.tiles_per_cta : cta_id;
+    const int step = p.wstat ? 1 : n_ctas;
     const int last = p.wstat ? min(first + p.tiles_per_cta, p.n_tiles) : p.n_tiles;
     auto tile_mn = [&](int t, int& mt, int& nt) {
         if (p.wstat) { nt = t / p.n_m_tiles; mt = t - nt * p.n_m_tiles; }
@@ -232,17 +248,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             bool any = false;
             int cur_nt = -1;
             bool ok = true;
-            const bool tr = g_gemm_trace_on && blockIdx.x == 0;
+            const bool tr = !PAIR && g_gemm_trace_on && blockIdx.x == 0;
             int tn = 0;
             trace(tr, 0, tn);
-            const uint32_t tx = a_bytes + (p.wstat ? 0u : b_bytes);
+            const uint32_t tx = (a_bytes + (p.wstat ? 0u : b_bytes)) * (PAIR ? 2u : 1u);
+            const uint32_t lead_full0 = PAIR ? map_to_cta(full0, 0) : full0;
             for (int t = first; t < last && ok; t += step) {
                 int mt, nt;
                 tile_mn(t, mt, nt);
                 if (p.wstat && nt != cur_nt) {
                     // every MMA that reads the old W tile has completed once the most recently
                     // filled ring stage has been released
-                    if (any && !mbar_wait_a(empty0 + 8 * last_s, last_ph, abort_flag)) { fail(abort_flag, 15); ok = false; break; }
+                    if (any && !mbar_wait_a(empty0 + 8 * last_s, last_ph, abort_flag)) { give_up(15); ok = false; break; }
                     mbar_expect_tx_a(wfull_a, p.KC * b_bytes);
                     for (int kc = 0; kc < p.KC; ++kc)
                         tma_load_2d_a(sB0 + kc * b_bytes, &tmW, wfull_a, kc * p.KCH, nt * p.BN);
@@ -250,20 +267,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     ++wloads;
                 }
                 trace(tr, 0, tn);
-                const int m0 = mt * BM, n0 = nt * p.BN;
+                const int m0 = mt * TM + (int)rank * BM, n0 = nt * p.BN + (int)rank * bn_cta;
                 for (int kc = 0; kc < p.KC; ++kc) {
-                    if (!mbar_wait_a(empty0 + 8 * s, ph ^ 1u, abort_flag)) { fail(abort_flag, 11); ok = false; break; }
-                    mbar_expect_tx_a(full0 + 8 * s, tx);
-                    tma_load_2d_a(sA0 + s * a_bytes, &tmA, full0 + 8 * s, kc * p.KCH, m0);
-                    if (!p.wstat) tma_load_2d_a(sB0 + s * b_bytes, &tmW, full0 + 8 * s, kc * p.KCH, n0);
+                    if (!mbar_wait_a(empty0 + 8 * s, ph ^ 1u, abort_flag)) { give_up(11); ok = false; break; }
+                    if (PAIR) {
+                        if (rank == 0) mbar_expect_tx_a(full0 + 8 * s, tx);
+                        tma_load_2d_pair(sA0 + s * a_bytes, &tmA, lead_full0 + 8 * s, kc * p.KCH, m0);
+                        tma_load_2d_pair(sB0 + s * b_bytes, &tmW, lead_full0 + 8 * s, kc * p.KCH, n0);
+                    } else {
+                        mbar_expect_tx_a(full0 + 8 * s, tx);
+                        tma_load_2d_a(sA0 + s * a_bytes, &tmA, full0 + 8 * s, kc * p.KCH, m0);
+                        if (!p.wstat) tma_load_2d_a(sB0 + s * b_bytes, &tmW, full0 + 8 * s, kc * p.KCH, n0);
+                    }
                     last_s = s; last_ph = ph; any = true;
                     if (++s == STAGES) { s = 0; ph ^= 1u; }
                 }
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            const uint32_t idesc = make_idesc_bf16_f32(BM, p.BN);
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = make_idesc_bf16_f32(TM, p.BN);
             const uint64_t dhi = kmajor_desc_hi(pitch);
             const int nk16 = p.KCH / 16;
             const uint32_t tfull0 = smem_u32(tfull), tempty0 = smem_u32(tempty);
@@ -274,35 +297,49 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             uint32_t s = 0, ph = 0, tile = 0, wloads = 0;
             int cur_nt = -1;
             bool ok = true;
-            const bool tr = g_gemm_trace_on && blockIdx.x == 0;
+            const bool tr = !PAIR && g_gemm_trace_on && blockIdx.x == 0;
             int tn = 0;
+            const uint32_t peer_empty0 = PAIR ? map_to_cta(empty0, 1) : 0u;
+            const uint32_t peer_tfull0 = PAIR ? map_to_cta(tfull0, 1) : 0u;
             for (int t = first; t < last && ok; t += step, ++tile) {
                 const uint32_t buf = tile & 1u, u = tile >> 1;
-                if (!mbar_wait_a(tempty0 + 8 * buf, (u & 1u) ^ 1u, abort_flag)) { fail(abort_flag, 12); ok = false; break; }
+                if (!mbar_wait_a(tempty0 + 8 * buf, (u & 1u) ^ 1u, abort_flag)) { give_up(12); ok = false; break; }
                 trace(tr, 1, tn);                           // accumulator buffer free
                 int mt = 0, nt = 0;
                 if (p.wstat || mbias) tile_mn(t, mt, nt);
                 if (p.wstat) {
                     if (nt != cur_nt) {
-                        if (!mbar_wait_a(wfull_a, wloads & 1u, abort_flag)) { fail(abort_flag, 16); ok = false; break; }
+                        if (!mbar_wait_a(wfull_a, wloads & 1u, abort_flag)) { give_up(16); ok = false; break; }
                         cur_nt = nt;
                         ++wloads;
                     }
                 }
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + buf * p.BNpad;
-                if (mbias)                                   // accumulator := bias, the chunks add to it
-                    mma_bf16_ss(d_tmem, ones_desc, dhi32 | (uint64_t)((btile0 + (uint32_t)nt * p.BN * 32u) >> 4), idesc, 0);
+                if (mbias) {                                 // accumulator := bias, the chunks add to it
+                    const uint64_t bias_desc = dhi32 | (uint64_t)((btile0 + (uint32_t)nt * bn_cta * 32u) >> 4);
+                    if (PAIR) mma_bf16_ss_pair(d_tmem, ones_desc, bias_desc, idesc, 0);
+                    else mma_bf16_ss(d_tmem, ones_desc, bias_desc, idesc, 0);
+                }
                 for (int kc = 0; kc < p.KC; ++kc) {
-                    if (!mbar_wait_a(full0 + 8 * s, ph, abort_flag)) { fail(abort_flag, 13); ok = false; break; }
+                    if (!mbar_wait_a(full0 + 8 * s, ph, abort_flag)) { give_up(13); ok = false; break; }
                     tc_fence_after_sync();
-                    const uint64_t adesc = dhi | (uint64_t)((sA0 + s * a_bytes) >> 4);
-                    const uint64_t bdesc = dhi | (uint64_t)((sB0 + (p.wstat ? (uint32_t)kc : s) * b_bytes) >> 4);
-                    mma_chunk(d_tmem, adesc, bdesc, idesc, nk16, (kc != 0) | mbias);
-                    mma_commit_a(empty0 + 8 * s);
+                    const uint64_t adesc = dhi | (uint64_t)(((sA0 + s * a_bytes) & 0x3FFFFu) >> 4);
+                    const uint64_t bdesc = dhi | (uint64_t)(((sB0 + (p.wstat ? (uint32_t)kc : s) * b_bytes) & 0x3FFFFu) >> 4);
+                    if (PAIR) {
+                        mma_chunk_pair(d_tmem, adesc, bdesc, idesc, nk16, (kc != 0) | mbias);
+                        mma_commit_pair(empty0 + 8 * s);
+                        mma_commit_pair(peer_empty0 + 8 * s);
+                    } else {
+                        mma_chunk(d_tmem, adesc, bdesc, idesc, nk16, (kc != 0) | mbias);
+                        mma_commit_a(empty0 + 8 * s);
+                    }
                     if (++s == STAGES) { s = 0; ph ^= 1u; }
                 }
-                if (ok) mma_commit_a(tfull0 + 8 * buf);
+                if (ok) {
+                    if (PAIR) { mma_commit_pair(tfull0 + 8 * buf); mma_commit_pair(peer_tfull0 + 8 * buf); }
+                    else mma_commit_a(tfull0 + 8 * buf);
+                }
                 trace(tr, 1, tn);                           // tile issued
             }
         }
@@ -327,13 +364,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         uint32_t tile = half;
         bool ok = true;
-        const bool tr = g_gemm_trace_on && blockIdx.x == 0 && lq == 0 && lane == 0 && chalf == 0;
+        const bool tr = !PAIR && g_gemm_trace_on && blockIdx.x == 0 && lq == 0 && lane == 0 && chalf == 0;
+        const uint32_t lead_tempty0 = PAIR ? map_to_cta(smem_u32(tempty), 0) : 0u;
         int tn = 0;
         for (int t = first + half * step; t < last && ok; t += 2 * step, tile += 2) {
             int mt, nt;
             tile_mn(t, mt, nt);
             const uint32_t buf = tile & 1u, u = tile >> 1;
-            const int row = mt * BM + r;
+            const int row = mt * TM + (int)rank * BM + r;
             const int n0 = nt * p.BN;
             const int part = n0 / p.part_cols;
             const int pc0 = n0 - part * p.part_cols;          // first column inside the part
@@ -346,7 +384,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             bool rok[4];
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
-                const int grow = mt * BM + lq * 32 + g * 8 + (lane >> 2);
+                const int grow = mt * TM + (int)rank * BM + lq * 32 + g * 8 + (lane >> 2);
                 rok[g] = grow < p.M;
                 optr[g] = cbase + (long long)grow * p.ldc + pc0 + (lane & 3) * 8;
                 rptr[g] = RES ? p.residual + (long long)grow * p.ldr + n0 + (lane & 3) * 8 : nullptr;
@@ -362,7 +400,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
             ok = mbar_wait(&tfull[buf], u & 1u, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
-            if (!ok) { if (lane == 0) fail(abort_flag, 14); break; }
+            if (!ok) { if (lane == 0) give_up(14); break; }
             trace(tr, 2 + half, tn);                        // accumulator ready
             tc_fence_after_sync();
             const uint32_t taddr = tmem_base + ((uint32_t)(lq * 32) << 16) + buf * p.BNpad;
@@ -453,7 +491,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&tempty[buf]);
+            if (lane == 0) {
+                if (PAIR) mbar_arrive_cluster(lead_tempty0 + 8 * buf);
+                else mbar_arrive(&tempty[buf]);
+            }
             trace(tr, 2 + half, tn);                        // tile drained
         }
     }
@@ -464,9 +505,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         for (int i = 0; i < 2000; ++i) __nanosleep(1000);
         __syncthreads();
     }
+    if (PAIR) cluster_sync_all();               // the peer no longer signals or reads this CTA
     if (warp == 1) {
         tc_fence_after_sync();
-        tmem_dealloc(tmem_base, ncols);
+        if (PAIR) tmem_dealloc_pair(tmem_base, ncols);
+        else tmem_dealloc(tmem_base, ncols);
     }
 }
 
@@ -528,13 +571,6 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
     p.n_tiles = p.n_m_tiles * p.n_n_tiles;
 
     const int pitch = p.KCH * 2;
-    CUtensorMap tmA, tmW;
-    const uint64_t dimsA[2] = {(uint64_t)Kd, (uint64_t)M}, dimsW[2] = {(uint64_t)Kd, (uint64_t)N};
-    const uint64_t strA[1] = {(uint64_t)lda * 2}, strW[1] = {(uint64_t)Kd * 2};
-    const uint32_t boxA[2] = {(uint32_t)p.KCH, (uint32_t)BM}, boxW[2] = {(uint32_t)p.KCH, (uint32_t)p.BN};
-    if (!encode_tensor_map_bf16(&tmA, a, 2, dimsA, strA, boxA, pitch)) return CONVNN_E_CUDA;
-    if (!encode_tensor_map_bf16(&tmW, w, 2, dimsW, strW, boxW, pitch)) return CONVNN_E_CUDA;
-
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -565,9 +601,44 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
     const size_t a_bytes = (size_t)BM * pitch, b_bytes = (size_t)p.BN * pitch;
     const size_t w_tile = (size_t)p.KC * b_bytes;
     p.wstat = (w_tile + 3 * a_bytes + fixed <= budget && p.n_tiles >= 2 * sms) ? 1 : 0;
+    // CTA pairs (M = 256 tiles, each CTA staging half of the W rows) where both operands stream and
+    // the reduction is deep enough for operand traffic to matter.
+    static const bool pair_allowed = [] { const char* e = getenv("CONVNN_B200_GEMM_PAIR"); return !(e && e[0] == '0'); }();
+    // Measured: +5-7 % with many column tiles (N >= 1024), a loss with one to three of them, and
+    // never worth a worse last wave (tiles of 256 rows on sms / 2 clusters quantise differently).
+    bool pair = pair_allowed && !p.wstat && parts == 1 && !has_stat && p.KCH == 64 && Kd >= 384 && N >= 1024 &&
+                p.BN % 32 == 0;
+    if (pair) {
+        const long long tp = (long long)((M + 2 * BM - 1) / (2 * BM)) * p.n_n_tiles, nc = sms / 2;
+        const double eff_pair = (double)tp / (double)(((tp + nc - 1) / nc) * nc);
+        const double eff_one = (double)p.n_tiles / (double)(((p.n_tiles + sms - 1) / sms) * sms);
+        pair = tp >= 2 * nc && eff_pair >= 0.97 * eff_one;
+    }
+    if (pair && o.bias && !bias_by_mma) {
+        // each CTA keeps the bias rows of its half of the columns only
+        const size_t rows_cta = bias_rows / 2;
+        if (rows_cta <= 24 * 1024) {
+            p.mma_bias = p.bias;
+            p.bias = nullptr;
+            fixed += 4096 + rows_cta;
+        } else {
+            pair = false;
+        }
+    } else if (pair && bias_by_mma) {
+        fixed -= bias_rows / 2;
+    }
+    if (pair && wide && !(o.gelu || o.residual)) fixed -= 8 * 2048;   // the plain pair epilogue has eight warps
     int grid;
     size_t smem;
-    if (p.wstat) {
+    if (pair) {
+        p.n_m_tiles = (M + 2 * BM - 1) / (2 * BM);
+        p.n_tiles = p.n_m_tiles * p.n_n_tiles;
+        const size_t stage = a_bytes + b_bytes / 2;
+        int st = (int)((budget_stream - fixed) / stage);
+        p.stages = st > MAX_STAGES ? MAX_STAGES : st;
+        smem = fixed + (size_t)p.stages * stage;
+        grid = 0;                                  // clusters are counted at launch
+    } else if (p.wstat) {
         p.tiles_per_cta = (p.n_tiles + sms - 1) / sms;
         grid = (p.n_tiles + p.tiles_per_cta - 1) / p.tiles_per_cta;
         int st_a = (int)((budget - fixed - w_tile) / a_bytes);
@@ -579,21 +650,54 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
         p.stages = st_ab > 6 ? 6 : (st_ab < 2 ? 2 : st_ab);
         smem = fixed + (size_t)p.stages * (a_bytes + b_bytes);
     }
+    CUtensorMap tmA, tmW;
+    const uint64_t dimsA[2] = {(uint64_t)Kd, (uint64_t)M}, dimsW[2] = {(uint64_t)Kd, (uint64_t)N};
+    const uint64_t strA[1] = {(uint64_t)lda * 2}, strW[1] = {(uint64_t)Kd * 2};
+    const uint32_t boxA[2] = {(uint32_t)p.KCH, (uint32_t)BM};
+    const uint32_t boxW[2] = {(uint32_t)p.KCH, (uint32_t)(pair ? p.BN / 2 : p.BN)};
+    if (!encode_tensor_map_bf16(&tmA, a, 2, dimsA, strA, boxA, pitch)) return CONVNN_E_CUDA;
+    if (!encode_tensor_map_bf16(&tmW, w, 2, dimsW, strW, boxW, pitch)) return CONVNN_E_CUDA;
     if (has_stat && (p.bias || p.residual || p.gelu))
         return set_error(CONVNN_E_UNSUPPORTED, "gemm_tc: statistics cannot be combined with bias / GELU / residual");
     if (p.gelu && p.residual) return set_error(CONVNN_E_UNSUPPORTED, "gemm_tc: GELU with a residual is not built");
 #define CONVNN_GEMM_LAUNCH1(S, B, G, R, W)                                                                  \
     do {                                                                                                    \
-        auto kern = gemm_tc_kernel<S, B, G, R, W>;                                                          \
+        auto kern = gemm_tc_kernel<S, B, G, R, W, false>;                                                   \
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         if (e != cudaSuccess) return set_error(CONVNN_E_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e)); \
         kern<<<grid, W ? NTHREADS_WIDE : NTHREADS, smem, st>>>(tmA, tmW, p);                                \
+    } while (0)
+#define CONVNN_GEMM_LAUNCH_PAIR(G, R, W)                                                                    \
+    do {                                                                                                    \
+        auto kern = gemm_tc_kernel<false, false, G, R, W, true>;                                            \
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (e != cudaSuccess) return set_error(CONVNN_E_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e)); \
+        cudaLaunchConfig_t cfg{};                                                                           \
+        cudaLaunchAttribute attr[1];                                                                        \
+        attr[0].id = cudaLaunchAttributeClusterDimension;                                                   \
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;           \
+        cfg.blockDim = dim3(W ? NTHREADS_WIDE : NTHREADS); cfg.dynamicSmemBytes = smem; cfg.stream = st;    \
+        cfg.attrs = attr; cfg.numAttrs = 1;                                                                 \
+        cfg.gridDim = dim3(2);                                                                              \
+        int max_clusters = 0;                                                                               \
+        e = cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg);                                      \
+        if (e != cudaSuccess || max_clusters < 1)                                                           \
+            return set_error(CONVNN_E_CUDA, "cudaOccupancyMaxActiveClusters: %s", cudaGetErrorString(e));   \
+        const int nc = p.n_tiles < max_clusters ? p.n_tiles : max_clusters;                                 \
+        cfg.gridDim = dim3(2 * nc);                                                                         \
+        e = cudaLaunchKernelEx(&cfg, kern, tmA, tmW, p);                                                    \
+        if (e != cudaSuccess) return set_error(CONVNN_E_CUDA, "gemm_tc pair launch: %s", cudaGetErrorString(e)); \
     } while (0)
 #define CONVNN_GEMM_LAUNCH(S, B, G, R)                          \
     do {                                                        \
         if (wide) CONVNN_GEMM_LAUNCH1(false, B, G, R, true);    \
         else CONVNN_GEMM_LAUNCH1(S, B, G, R, false);            \
     } while (0)
+    if (pair) {
+        if (p.gelu) CONVNN_GEMM_LAUNCH_PAIR(true, false, true);
+        else if (p.residual) CONVNN_GEMM_LAUNCH_PAIR(false, true, true);
+        else CONVNN_GEMM_LAUNCH_PAIR(false, false, false);
+    } else
     if (has_stat) CONVNN_GEMM_LAUNCH1(true, false, false, false, false);
     else if (p.gelu) { if (p.bias) CONVNN_GEMM_LAUNCH(false, true, true, false); else CONVNN_GEMM_LAUNCH(false, false, true, false); }
     else if (p.bias && p.residual) CONVNN_GEMM_LAUNCH(false, true, false, true);
@@ -602,6 +706,7 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
     else CONVNN_GEMM_LAUNCH(false, false, false, false);
 #undef CONVNN_GEMM_LAUNCH
 #undef CONVNN_GEMM_LAUNCH1
+#undef CONVNN_GEMM_LAUNCH_PAIR
     CONVNN_CHECK_LAUNCH("gemm_tc");
     return CONVNN_OK;
 }

@@ -240,6 +240,14 @@ __device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* m, uint32_t bar_cluster, int c0,
+                                                 int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster), "r"(c0), "r"(c1)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_dst, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)),
                  "r"(ncols)
@@ -259,6 +267,17 @@ __device__ __forceinline__ void mma_bf16_ss_pair(uint32_t tmem_d, uint64_t adesc
         "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
+}
+__device__ __forceinline__ void mma_chunk_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               int nk16, uint32_t accumulate_first) {
+    mma_bf16_ss_pair(d_tmem, adesc, bdesc, idesc, accumulate_first);
+    if (nk16 == 4) {
+        mma_bf16_ss_pair(d_tmem, adesc + 2, bdesc + 2, idesc, 1);
+        mma_bf16_ss_pair(d_tmem, adesc + 4, bdesc + 4, idesc, 1);
+        mma_bf16_ss_pair(d_tmem, adesc + 6, bdesc + 6, idesc, 1);
+    } else if (nk16 == 2) {
+        mma_bf16_ss_pair(d_tmem, adesc + 2, bdesc + 2, idesc, 1);
+    }
 }
 // One arrival on the barrier at `bar_cluster` (own or peer CTA) when every MMA this thread
 // has issued so far has completed in both CTAs.

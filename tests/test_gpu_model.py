@@ -3,7 +3,7 @@ import pytest
 import torch
 
 import convnn_b200
-from convnn_b200 import ops
+from convnn_b200 import _capi, ops
 from oracle.convnn_oracle import ConvNNConfig, bf16_round, make_input, make_layer_weights
 from oracle.vit_oracle import vit_forward
 from golden_util import VIT_NAMES, vit_case
@@ -125,3 +125,53 @@ def test_residual_is_folded_into_the_output_projection():
             y = m(x)
             z = m(x, residual=x)
         assert torch.equal(z, x + y)
+
+
+def test_linear_with_many_row_tiles():
+    """Enough row tiles for the weight-resident schedule (a CTA keeps one W tile and walks the
+    rows), ragged last tile, bias values large enough that a misplaced bias cannot hide in the
+    tolerance; bf16 inputs, fp32 reference."""
+    g = torch.Generator().manual_seed(3)
+    M = 20000 + 37
+    x = torch.randn(M, 192, generator=g).to(DEV, torch.bfloat16)
+    W1 = (torch.randn(768, 192, generator=g) / 14).to(DEV, torch.bfloat16)
+    b1 = (4.0 * torch.randn(768, generator=g)).to(DEV, torch.bfloat16)
+    want = x.float() @ W1.float().t() + b1.float()
+    got = ops.linear(x, W1, b1)
+    assert rel_err(got, want) < 6e-3
+    assert float((got.float() - want).abs().max()) < 0.08          # one bf16 step at |y| <= 16
+    h = ops.linear(x, W1, b1, gelu=True)
+    assert rel_err(h, torch.nn.functional.gelu(want)) < 1.2e-2
+    W2 = (torch.randn(192, 768, generator=g) / 28).to(DEV, torch.bfloat16)
+    b2 = (4.0 * torch.randn(192, generator=g)).to(DEV, torch.bfloat16)
+    y = ops.linear(h, W2, b2, residual=x)
+    assert rel_err(y, x.float() + (h.float() @ W2.float().t() + b2.float())) < 1.2e-2
+    torch.cuda.synchronize()
+    assert _capi.device_status() == 0
+
+
+def test_linear_on_cta_pairs():
+    """Deep reductions with many row tiles run on CTA pairs (M = 256 tiles, W rows split between the
+    two CTAs): plain, bias + GELU and bias + skip epilogues, ragged last row tile, fp32 reference."""
+    g = torch.Generator().manual_seed(4)
+    M = 40000 + 77
+    x = torch.randn(M, 384, generator=g).to(DEV, torch.bfloat16)
+    W1 = (torch.randn(1536, 384, generator=g) / 20).to(DEV, torch.bfloat16)
+    b1 = (2.0 * torch.randn(1536, generator=g)).to(DEV, torch.bfloat16)
+    want = x.float() @ W1.float().t()
+    assert rel_err(ops.linear(x, W1), want) < 6e-3
+    got = ops.linear(x, W1, b1)
+    assert rel_err(got, want + b1.float()) < 6e-3
+    assert float((got.float() - (want + b1.float())).abs().max()) < 0.08
+    h = ops.linear(x, W1, b1, gelu=True)
+    assert rel_err(h, torch.nn.functional.gelu(want + b1.float())) < 1.2e-2
+    W2 = (torch.randn(384, 1536, generator=g) / 40).to(DEV, torch.bfloat16)
+    b2 = (2.0 * torch.randn(384, generator=g)).to(DEV, torch.bfloat16)
+    y = ops.linear(h, W2, b2, residual=x)
+    assert rel_err(y, x.float() + (h.float() @ W2.float().t() + b2.float())) < 1.2e-2
+    # skip connection on a wide output (the pair schedule is only chosen for N >= 1024)
+    W3 = (torch.randn(1536, 384, generator=g) / 20).to(DEV, torch.bfloat16)
+    z = ops.linear(x, W3, b1, residual=h)
+    assert rel_err(z, h.float() + (x.float() @ W3.float().t() + b1.float())) < 1.2e-2
+    torch.cuda.synchronize()
+    assert _capi.device_status() == 0

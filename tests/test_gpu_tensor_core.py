@@ -96,3 +96,17 @@ def test_pair_kernel_orders_exact_ties_by_column():
         got = idx[0, 0, row].tolist()
         assert got[0] == 130 and got[1] == 300, got
         assert float(val[0, 0, row, 0]) == float(val[0, 0, row, 1])
+
+
+def test_pair_kernel_and_simt_kernel_agree_on_long_sequences():
+    """Same q / k through the float32 SIMT path (q, k upcast) and the CTA-pair tensor-core path."""
+    g = torch.Generator().manual_seed(7)
+    q = torch.randn(1, 2100, 1, 128, generator=g).to(torch.bfloat16)
+    k = torch.randn(1, 2100, 1, 128, generator=g).to(torch.bfloat16)
+    cfg = ConvNNConfig(d_hidden=128, num_heads=1, K=9, magnitude_type="matmul", seq_length=2100)
+    spec = spec_of(cfg)
+    i16, v16 = ops.sim_topk(spec, q.to(DEV), k.to(DEV), None, None)
+    i32, v32 = ops.sim_topk(spec, q.float().to(DEV), k.float().to(DEV), None, None)
+    same = (i16 == i32).all(-1)
+    assert float(same.float().mean()) > 0.999
+    assert float((v16 - v32).abs().max()) < 1e-4
