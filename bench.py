@@ -335,6 +335,8 @@ def run_ours(args) -> int:
         raise SystemExit("bench.py needs a CUDA device: the ConvNN path has no CPU fallback")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    from convnn_b200.sharded import bind_host_to_device
+    numa_bound = bind_host_to_device(dev) if world > 1 else False   # before any pinned allocation
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     lib = _capi.lib()
@@ -476,7 +478,7 @@ def run_ours(args) -> int:
                                    "d=192 12 layers 1000 classes K=9 cosine/all/depthwise",
                        "batch_per_gpu": B, "global_batch": total, "parallelism": f"batch-shard x{world}",
                        "l2": f"{NBUF} distinct resident input batches (231 MB) rotate, larger than L2",
-                       "launch": graph_note},
+                       "launch": graph_note, "host_numa_bound": bool(numa_bound)},
             "e2e": {"value": total * args.steps / (ms_e2e / 1e3), "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": int(launches_eager) if graph is None else int(per_forward * args.steps),

@@ -56,3 +56,22 @@ def sharded_forward(model, images: torch.Tensor, group=None, gather: bool = True
     lo, hi = shard_bounds(images.shape[0], world, rank)
     local = model(images[lo:hi])
     return gather_logits(local, images.shape[0], group) if gather else local
+
+
+def bind_host_to_device(device) -> bool:
+    """Restrict the calling process to the CPU cores next to `device` (NVML's ideal affinity for
+    that GPU) so that pinned host buffers allocated afterwards come from the memory of the socket
+    the GPU hangs off.  With eight ranks streaming input batches at the same time, host buffers on
+    the far socket make every copy cross the inter-socket link.  Only the process's own CPU
+    affinity changes (no GPU setting is touched).  Returns False, and changes nothing, when NVML
+    or the PCI identity of the device is unavailable."""
+    try:
+        import pynvml
+        props = torch.cuda.get_device_properties(device)
+        bus = "%08x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
+        pynvml.nvmlInit()
+        handle = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+        pynvml.nvmlDeviceSetCpuAffinity(handle)
+        return True
+    except Exception:
+        return False
