@@ -209,22 +209,32 @@ int convnn_b200_qkv_proj(const convnn_desc* d, const void* x, int64_t ldx, const
     if (d->dtype == CONVNN_BF16 && !d->coord && !force_simt()) {
         const char* wb = static_cast<const char*>(w_qkv);
         void* kvq[3] = {k, v, q};
-        const bool fuse = stats && gemm_tc_can_fuse_stats(dm.D, dm.dk);
+        // Fused statistics: always when a tile holds whole heads; for heads that span several
+        // tiles the partial sums need room in `scratch` behind the gathered candidate rows
+        // (pieces x B x H x (T + S) floats).
+        const int pieces = stats ? gemm_tc_stat_pieces(dm.D, dm.dk) : 0;
+        const size_t gathered = d->sampled ? up256((size_t)dm.B * dm.S * dm.D * dm.elt) : 0;
+        const size_t part_k = up256((size_t)pieces * dm.B * dm.H * dm.T * 4);
+        const size_t part_q = up256((size_t)pieces * dm.B * dm.H * dm.S * 4);
+        const size_t scratch_min = (size_t)dm.B * (dm.T > dm.S ? dm.T : dm.S) * dm.D * dm.elt;   // what every caller provides
+        const bool fuse = pieces == 1 || (pieces > 1 && scratch && gathered + part_k + part_q <= scratch_min);
+        float* sc_k = pieces > 1 && fuse ? reinterpret_cast<float*>(static_cast<char*>(scratch) + gathered) : nullptr;
+        float* sc_q = sc_k ? reinterpret_cast<float*>(static_cast<char*>(scratch) + gathered + part_k) : nullptr;
         GemmTcOpts o;
         o.stat_mode = d->metric; o.dk = dm.dk; o.heads = dm.H;
         bool done = false;
         if (!d->sampled && gemm_tc_supported(x, ldx, w_qkv, dm.D, 3 * dm.D, 3, kvq, dm.D)) {
-            if (fuse) { o.stat[0] = kstat; o.stat[2] = qstat; o.rows_per_batch = dm.T; }
+            if (fuse) { o.stat[0] = kstat; o.stat[2] = qstat; o.rows_per_batch = dm.T; o.stat_scratch = sc_k; }
             if ((rc = launch_gemm_tc(x, ldx, w_qkv, dm.B * dm.T, 3 * dm.D, dm.D, 3, kvq, dm.D, o, st))) return rc;
             done = true;
         } else if (d->sampled && scratch && gemm_tc_supported(x, ldx, w_qkv, dm.D, 2 * dm.D, 2, kvq, dm.D) &&
                    gemm_tc_supported(scratch, dm.D, wb + 2 * wsz, dm.D, dm.D, 1, &kvq[2], dm.D)) {
-            if (fuse) { o.stat[0] = kstat; o.rows_per_batch = dm.T; }
+            if (fuse) { o.stat[0] = kstat; o.rows_per_batch = dm.T; o.stat_scratch = sc_k; }
             if ((rc = launch_gemm_tc(x, ldx, w_qkv, dm.B * dm.T, 2 * dm.D, dm.D, 2, kvq, dm.D, o, st))) return rc;
             if ((rc = launch_gather_rows(d->dtype, x, ldx, cand, scratch, dm.B, dm.T, dm.S, dm.D, st))) return rc;
             GemmTcOpts oq;
             oq.stat_mode = d->metric; oq.dk = dm.dk; oq.heads = dm.H;
-            if (fuse) { oq.stat[0] = qstat; oq.rows_per_batch = dm.S; }
+            if (fuse) { oq.stat[0] = qstat; oq.rows_per_batch = dm.S; oq.stat_scratch = sc_q; }
             if ((rc = launch_gemm_tc(scratch, dm.D, wb + 2 * wsz, dm.B * dm.S, dm.D, dm.D, 1, &kvq[2], dm.D, oq, st)))
                 return rc;
             done = true;

@@ -110,8 +110,14 @@ struct GemmTcOpts {
     int gelu = 0;
     float* stat[3] = {nullptr, nullptr, nullptr};   // per part: fused per-(row, head) statistic
     int stat_mode = 0, dk = 0, heads = 1, rows_per_batch = 1;
+    // heads wider than a tile: room for gemm_tc_stat_pieces() x M x heads floats per part with a
+    // statistic (the tiles' partial sums, combined by a second small kernel)
+    float* stat_scratch = nullptr;
 };
 bool gemm_tc_can_fuse_stats(int part_cols, int dk);
+// Column tiles a head is spread over when the statistic is fused: 1 = a tile holds whole heads,
+// m >= 2 = each head spans m tiles (partial sums + combine), 0 = cannot be fused.
+int gemm_tc_stat_pieces(int part_cols, int dk);
 int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, int Kd, int parts, void* const* c,
                    long long ldc, const GemmTcOpts& o, cudaStream_t st);
 int launch_layernorm(int dtype, const void* x, long long ldx, const void* gamma, const void* beta, float eps, void* y,

@@ -50,6 +50,8 @@ struct GemmTcParams {
     long long ldr;
     float* stat[3];        // per part: per-(row, head) statistic of the stored values, or nullptr
     int stat_mode;         // CONVNN_COSINE: 1/max(norm, 1e-12); otherwise the squared norm
+    int stat_pieces;       // 1, or the number of column tiles a head spans (stat[] then holds raw partial sums,
+    long long stat_plane;  // one plane of stat_plane floats per piece)
     int dk, heads, rows_per_batch;   // head geometry of the statistic: stat[(b*heads + h)*rows_per_batch + r]
     int part_cols;         // output columns per part (N for a single output)
     int M, N, gelu;
@@ -392,9 +394,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             // statistic bookkeeping without divisions in the chunk loop
             int head = 0, head_left = 0;
             long long stat_base = 0;
+            long long stat_piece = 0;
             if (STAT) {
                 head = pc0 / p.dk;
                 head_left = p.dk;
+                if (p.stat_pieces > 1) {              // this tile is one piece of one head
+                    stat_piece = (long long)((pc0 - head * p.dk) / p.BN) * p.stat_plane;
+                    head_left = p.BN;
+                }
                 const int bb = row / p.rows_per_batch, rr = row - bb * p.rows_per_batch;
                 stat_base = (long long)bb * p.heads * p.rows_per_batch + rr;
             }
@@ -435,8 +442,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         head_left -= 32;
                         if (head_left == 0) {                 // chunk ends a head (dk % 32 == 0)
                             if (row < p.M)
-                                stat[stat_base + (long long)head * p.rows_per_batch] =
-                                    p.stat_mode == CONVNN_COSINE ? 1.0f / fmaxf(sqrtf(ss), 1e-12f) : ss;
+                                stat[stat_piece + stat_base + (long long)head * p.rows_per_batch] =
+                                    (p.stat_mode == CONVNN_COSINE && p.stat_pieces == 1) ? 1.0f / fmaxf(sqrtf(ss), 1e-12f) : ss;
                             ss = 0.f;
                             head_left = p.dk;
                             ++head;
@@ -544,6 +551,26 @@ bool gemm_tc_can_fuse_stats(int part_cols, int dk) {
     return bn != 0 && dk % 32 == 0 && bn % dk == 0;
 }
 
+int gemm_tc_stat_pieces(int part_cols, int dk) {
+    const int bn = dividing_tile(part_cols);
+    if (bn == 0 || dk % 32 != 0) return 0;
+    if (bn % dk == 0) return 1;
+    if (bn % 32 == 0 && dk % bn == 0 && dk / bn <= 8) return dk / bn;
+    return 0;
+}
+
+namespace {
+// out[i] = f(sum over pieces of partial[piece][i]): the statistic of heads that span several tiles
+__global__ void stat_combine_kernel(const float* __restrict__ partial, long long plane, int pieces, long long n,
+                                    int cosine, float* __restrict__ out) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float s = 0.f;
+    for (int p = 0; p < pieces; ++p) s += partial[(long long)p * plane + i];
+    out[i] = cosine ? 1.0f / fmaxf(sqrtf(s), 1e-12f) : s;
+}
+}  // namespace
+
 int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, int Kd, int parts, void* const* c,
                    long long ldc, const GemmTcOpts& o, cudaStream_t st) {
     GemmTcParams p{};
@@ -554,6 +581,7 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
     p.ldc = ldc; p.bias = static_cast<const __nv_bfloat16*>(o.bias); p.gelu = o.gelu;
     p.mma_bias = nullptr;
     p.residual = static_cast<const __nv_bfloat16*>(o.residual); p.ldr = o.ldr;
+    p.stat_pieces = 1; p.stat_plane = 0;
     p.stat_mode = o.stat_mode; p.dk = o.dk > 0 ? o.dk : 32; p.heads = o.heads; p.rows_per_batch = o.rows_per_batch > 0 ? o.rows_per_batch : 1;
     p.M = M; p.N = N;
     p.part_cols = N / parts;
@@ -566,6 +594,20 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
         p.BN = (((N + nt - 1) / nt) + 15) / 16 * 16;
     }
     p.BNpad = pow2_at_least(p.BN, 32);
+    float* stat_final[3] = {p.stat[0], p.stat[1], p.stat[2]};
+    if (o.stat[0] || o.stat[1] || o.stat[2]) {
+        const int pieces = gemm_tc_stat_pieces(p.part_cols, p.dk);
+        if (pieces == 0 || (pieces > 1 && !o.stat_scratch))
+            return set_error(CONVNN_E_UNSUPPORTED, "gemm_tc: the statistic cannot be fused for d_k=%d with %d-column tiles",
+                             p.dk, p.BN);
+        if (pieces > 1) {
+            p.stat_pieces = pieces;
+            p.stat_plane = (long long)M * p.heads;
+            float* sc = o.stat_scratch;
+            for (int i = 0; i < parts; ++i)
+                if (p.stat[i]) { p.stat[i] = sc; sc += (long long)pieces * p.stat_plane; }
+        }
+    }
     p.n_m_tiles = (M + BM - 1) / BM;
     p.n_n_tiles = (N + p.BN - 1) / p.BN;
     p.n_tiles = p.n_m_tiles * p.n_n_tiles;
@@ -708,6 +750,15 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
 #undef CONVNN_GEMM_LAUNCH1
 #undef CONVNN_GEMM_LAUNCH_PAIR
     CONVNN_CHECK_LAUNCH("gemm_tc");
+    if (p.stat_pieces > 1) {
+        for (int i = 0; i < parts; ++i) {
+            if (!stat_final[i]) continue;
+            const long long n = p.stat_plane;
+            stat_combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(p.stat[i], p.stat_plane, p.stat_pieces, n,
+                                                                            p.stat_mode == CONVNN_COSINE, stat_final[i]);
+            CONVNN_CHECK_LAUNCH("stat_combine");
+        }
+    }
     return CONVNN_OK;
 }
 

@@ -114,7 +114,8 @@ int convnn_b200_head_channels(const convnn_desc* d);
 size_t convnn_b200_workspace_bytes(const convnn_desc* d);
 
 /* Bytes of the optional `scratch` argument of the stages: room for the gathered candidate
- * rows (B, S, D), the GEMM operand of the standard (B, H, T, K*C) / separable (B, H, T, C)
+ * rows (B, S, D) and, behind them, the partial row statistics of heads wider than a GEMM
+ * tile, the GEMM operand of the standard (B, H, T, K*C) / separable (B, H, T, C)
  * conv, and the head-merged activations (B, T, D).  With scratch == NULL the stages still
  * work but leave the tensor cores for the cases that need it (sampled queries; standard and
  * separable conv; H > 1 output projection).  No reference counterpart. */
