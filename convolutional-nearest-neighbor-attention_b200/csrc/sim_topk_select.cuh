@@ -45,17 +45,23 @@ __device__ __forceinline__ void consume(TopList<NSEL>& top, const uint32_t (&acc
     for (int j = 0; j < W; ++j) mask |= (key[j] > thr) ? (1u << j) : 0u;
     if (left < W) mask &= (left <= 0) ? 0u : ((1u << left) - 1u);
     if (!row_ok) mask = 0;
-    if (__any_sync(0xffffffffu, mask != 0)) {
+    // The warp runs as many drain steps as its busiest lane has survivors (one reduction instead of
+    // a vote per step); each step loads the next survivor's key while the current one is inserted.
+    const int steps = __reduce_max_sync(0xffffffffu, __popc(mask));
+    if (steps) {
         // keys go through shared memory so the drain loop can pick column j per lane
 #pragma unroll
         for (int j = 0; j < W; ++j) ks[j * kSelGroup] = key[j];
-        while (__any_sync(0xffffffffu, mask != 0)) {
-            if (mask) {
-                const int j = __ffs(mask) - 1;
-                mask &= mask - 1;
-                const float k = ks[j * kSelGroup];
-                if (k > top.worst()) top.insert_sorted(k, col0 + j);
-            }
+        int j = mask ? __ffs(mask) - 1 : 0;
+        float k = ks[j * kSelGroup];
+        for (int it = 0; it < steps; ++it) {
+            const bool live = mask != 0;
+            const float kc = k;
+            const int jc = j;
+            mask &= mask - 1;
+            j = mask ? __ffs(mask) - 1 : 0;
+            k = ks[j * kSelGroup];
+            if (live && kc > top.worst()) top.insert_sorted(kc, col0 + jc);
         }
     }
 }
