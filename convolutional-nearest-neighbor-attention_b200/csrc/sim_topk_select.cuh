@@ -3,6 +3,7 @@
 #pragma once
 #include "common.cuh"
 #include "toplist.cuh"
+#include "f32x2.cuh"
 
 namespace convnn {
 
@@ -11,26 +12,42 @@ constexpr int kSelGroup = 128;    // threads per epilogue group = stride of the 
 // One chunk of W accumulator columns of this thread's row: keys, then either plain inserts
 // (the first 32 columns of a row, where most values enter the list anyway) or a threshold
 // mask followed by a drain loop that only visits the survivors.
-// qv / cv hold the column statistic / candidate token of column (32-aligned base + lane).
-// P needs the fields metric, sampled and S (number of candidate columns).
+// qs points at the W column statistics of this chunk in shared memory (16-byte aligned, the same
+// for every lane: broadcast loads); cv holds the candidate token of column (32-aligned base +
+// lane).  P needs the fields metric, sampled and S (number of candidate columns).
 template <int NSEL, int W, class P>
 __device__ __forceinline__ void consume(TopList<NSEL>& top, const uint32_t (&acc)[W], int col0, int lane_off,
-                                        float qv, int cv, const P& p, int row, bool row_ok, float sentinel,
+                                        const float* qs, int cv, const P& p, int row, bool row_ok, float sentinel,
                                         float* ks) {
     float key[W];
+    if (p.metric != CONVNN_MATMUL) {
+        const f32x2 two = pack2(2.0f, 2.0f);
 #pragma unroll
-    for (int j = 0; j < W; ++j) {
-        const float dot = __uint_as_float(acc[j]);
-        float k = dot;
-        if (p.metric != CONVNN_MATMUL) {
-            const float s = __shfl_sync(0xffffffffu, qv, lane_off + j);
-            k = (p.metric == CONVNN_COSINE) ? dot * s : fmaf(2.0f, dot, -s);
+        for (int j4 = 0; j4 < W / 4; ++j4) {
+            const float4 s4 = *reinterpret_cast<const float4*>(qs + 4 * j4);
+            const f32x2 d01 = pack2(__uint_as_float(acc[4 * j4]), __uint_as_float(acc[4 * j4 + 1]));
+            const f32x2 d23 = pack2(__uint_as_float(acc[4 * j4 + 2]), __uint_as_float(acc[4 * j4 + 3]));
+            f32x2 k01, k23;
+            if (p.metric == CONVNN_COSINE) {
+                k01 = mul2(d01, pack2(s4.x, s4.y));
+                k23 = mul2(d23, pack2(s4.z, s4.w));
+            } else {
+                k01 = fma2(two, d01, pack2(-s4.x, -s4.y));
+                k23 = fma2(two, d23, pack2(-s4.z, -s4.w));
+            }
+            unpack2(k01, key[4 * j4], key[4 * j4 + 1]);
+            unpack2(k23, key[4 * j4 + 2], key[4 * j4 + 3]);
         }
-        if (p.sampled) {
+    } else {
+#pragma unroll
+        for (int j = 0; j < W; ++j) key[j] = __uint_as_float(acc[j]);
+    }
+    if (p.sampled) {
+#pragma unroll
+        for (int j = 0; j < W; ++j) {
             const int cj = __shfl_sync(0xffffffffu, cv, lane_off + j);
-            if (cj == row) k = sentinel;
+            if (cj == row) key[j] = sentinel;
         }
-        key[j] = k;
     }
     const int left = p.S - col0;                       // valid columns from col0 on
     if (col0 < 32) {

@@ -75,7 +75,8 @@ sim_topk_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     const uint32_t STAGES = p.stages;
     uint8_t* stages = smem;                                            // [STAGES][A0 | A1 | B]
     float* keybuf = reinterpret_cast<float*>(smem + STAGES * stage_bytes);   // [2 groups][CW][GROUP]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(keybuf + 2 * CW * GROUP);
+    float* statbuf = keybuf + 2 * CW * GROUP;                                 // [8 warps][128] column statistics of the tile
+    uint64_t* bars = reinterpret_cast<uint64_t*>(statbuf + 8 * 128);
     uint64_t* full = bars;
     uint64_t* empty = bars + MAX_STAGES;
     uint64_t* tfull = bars + 2 * MAX_STAGES;
@@ -174,6 +175,7 @@ sim_topk_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         const int lq = warp & 3;                 // TMEM lane quarter this warp may read
         const int r = lq * 32 + lane;            // row within the tile
         float* ks = keybuf + grp * CW * GROUP + r;
+        float* sq = statbuf + (warp - 2) * 128;
         uint32_t tile = 0;
         bool ok = true;
         for (int unit = blockIdx.x; unit < p.n_units && ok; unit += gridDim.x) {
@@ -208,27 +210,30 @@ sim_topk_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
                 const uint32_t taddr = tmem_base + ((uint32_t)(lq * 32) << 16) + (grp * 2 + par) * p.BNpad;
                 // a warp whose 32 rows all lie past the end of the sequence has nothing to select
                 const bool warp_live = pp * 2 * BM + grp * BM + lq * 32 < p.T;
-                auto stat_of = [&](int c, float& q1, int& c1) {
+                auto cand_of = [&](int c) {
                     const int c4 = c >> 5;
-                    q1 = c4 == 0 ? qv[0] : (c4 == 1 ? qv[1] : (c4 == 2 ? qv[2] : qv[3]));
-                    c1 = c4 == 0 ? cv[0] : (c4 == 1 ? cv[1] : (c4 == 2 ? cv[2] : cv[3]));
+                    return c4 == 0 ? cv[0] : (c4 == 1 ? cv[1] : (c4 == 2 ? cv[2] : cv[3]));
                 };
+                // this tile's column statistics, readable by every lane as broadcast vectors
+                __syncwarp();
+#pragma unroll
+                for (int c4 = 0; c4 < 4; ++c4) sq[c4 * 32 + lane] = qv[c4];
+                __syncwarp();
                 if (warp_live) {
 #pragma unroll 1
                     for (int c = 0; c < p.BN; c += CW) {
                         if (ct * p.BN + c >= p.S) break;         // the rest of the tile is padding
-                        float q1; int c1;
-                        stat_of(c, q1, c1);
+                        const int c1 = cand_of(c);
                         if (CW == 32 && c + 32 <= p.BN) {
                             uint32_t acc[32];
                             tmem_ld_x32(taddr + c, acc);
                             tmem_ld_wait();
-                            consume<NSEL, 32>(top, acc, ct * p.BN + c, 0, q1, c1, p, row, row_ok, sentinel, ks);
+                            consume<NSEL, 32>(top, acc, ct * p.BN + c, 0, sq + c, c1, p, row, row_ok, sentinel, ks);
                         } else {
                             uint32_t acc[16];
                             tmem_ld_x16(taddr + c, acc);
                             tmem_ld_wait();
-                            consume<NSEL, 16>(top, acc, ct * p.BN + c, c & 31, q1, c1, p, row, row_ok, sentinel, ks);
+                            consume<NSEL, 16>(top, acc, ct * p.BN + c, c & 31, sq + c, c1, p, row, row_ok, sentinel, ks);
                         }
                     }
                 }
@@ -302,7 +307,7 @@ int launch_sim_topk_tc(const convnn_desc* d, const Dims& dm, const void* q, cons
 
     const int cw = small_cfg ? 16 : 32;
     const size_t smem = 1024 + (size_t)p.stages * (2 * BM + p.BN) * pitch + 2 * cw * GROUP * sizeof(float) +
-                        (2 * MAX_STAGES + 4) * 8 + 16;
+                        8 * 128 * sizeof(float) + (2 * MAX_STAGES + 4) * 8 + 16;
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

@@ -58,16 +58,18 @@ __device__ __forceinline__ void fail(volatile int* abort_flag, uint32_t peer_abo
     atomicCAS(&g_sim_topk2_status, 0, code);
 }
 
-template <int NSEL>
+// NST: depth of the shared-memory ring (5; 4 where the merge buffer of a long list needs the room)
+template <int NSEL, int NST>
 __global__ void __launch_bounds__(NTHREADS, 1)
 sim_topk_tc2_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmQ,
                     const Tc2Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* stages = smem;                                                   // [STAGES][A | B]
-    float* keybuf = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES);    // [2 column halves][CW][128]
+    float* keybuf = reinterpret_cast<float*>(smem + NST * STAGE_BYTES);       // [2 column halves][CW][128]
     float* mbuf = keybuf + 2 * CW * kSelGroup;                                // [2 * NSEL][128] merge hand-over
-    uint64_t* bars = reinterpret_cast<uint64_t*>(mbuf + 2 * NSEL * kSelGroup);
+    float* statbuf = mbuf + 2 * NSEL * kSelGroup;                             // [8 warps][128] column statistics of the tile
+    uint64_t* bars = reinterpret_cast<uint64_t*>(statbuf + 8 * 128);
     uint64_t* full = bars;                      // used in the leader only
     uint64_t* empty = bars + STAGES;
     uint64_t* tfull = bars + 2 * STAGES;
@@ -83,7 +85,7 @@ sim_topk_tc2_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
     const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < NST; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
@@ -133,7 +135,7 @@ sim_topk_tc2_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
                         if (rank == 0) mbar_expect_tx_a(full0 + 8 * s, 2 * STAGE_BYTES);
                         tma_load_4d_pair(st, &tmK, lead_full0 + 8 * s, kc * KCH, h, row0, b);
                         tma_load_4d_pair(st + A_BYTES, &tmQ, lead_full0 + 8 * s, kc * KCH, h, col0, b);
-                        if (++s == STAGES) { s = 0; ph ^= 1u; }
+                        if (++s == NST) { s = 0; ph ^= 1u; }
                     }
                 }
             }
@@ -163,7 +165,7 @@ sim_topk_tc2_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
                         mma_bf16_ss_pair(d, ad + 6, bd + 6, idesc, 1);
                         mma_commit_pair(empty0 + 8 * s);
                         mma_commit_pair(peer_empty0 + 8 * s);
-                        if (++s == STAGES) { s = 0; ph ^= 1u; }
+                        if (++s == NST) { s = 0; ph ^= 1u; }
                     }
                     if (ok) {
                         mma_commit_pair(tfull0 + 8 * par);
@@ -177,6 +179,7 @@ sim_topk_tc2_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
         const int lq = warp & 3;                 // TMEM lane quarter this warp may read
         const int r = lq * 32 + lane;            // row within this CTA's 128
         float* ks = keybuf + chalf * CW * kSelGroup + r;
+        float* sq = statbuf + (warp - 2) * 128;
         uint32_t it = 0;                         // units done by this CTA (phase of the merge barriers)
         const uint32_t lead_tempty0 = map_to_cta(tempty0, 0);
         uint32_t tile = 0;
@@ -213,6 +216,11 @@ sim_topk_tc2_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
                 tc_fence_after_sync();
                 const uint32_t taddr = tmem_base + ((uint32_t)(lq * 32) << 16) + par * BN + chalf * BNH;
                 const int cbase = ct * BN + chalf * BNH;
+                // this tile's column statistics, readable by every lane as broadcast vectors
+                __syncwarp();
+#pragma unroll
+                for (int c4 = 0; c4 < 4; ++c4) sq[c4 * 32 + lane] = qv[c4];
+                __syncwarp();
                 if (warp_live) {
 #pragma unroll
                     for (int c4 = 0; c4 < 4; ++c4) {
@@ -220,7 +228,7 @@ sim_topk_tc2_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
                             uint32_t acc[32];
                             tmem_ld_x32(taddr + c4 * 32, acc);
                             tmem_ld_wait();
-                            consume<NSEL, 32>(top, acc, cbase + c4 * 32, 0, qv[c4], cv[c4], p, row, row_ok, sentinel, ks);
+                            consume<NSEL, 32>(top, acc, cbase + c4 * 32, 0, sq + c4 * 32, cv[c4], p, row, row_ok, sentinel, ks);
                         }
                     }
                 }
@@ -308,13 +316,14 @@ int launch_sim_topk_tc2(const convnn_desc* d, const Dims& dm, const void* q, con
     if (!encode_tensor_map_bf16(&tmK, k, 4, dimsK, strK, boxK, KCH * 2)) return CONVNN_E_CUDA;
     if (!encode_tensor_map_bf16(&tmQ, q, 4, dimsQ, strQ, boxQ, KCH * 2)) return CONVNN_E_CUDA;
 
-    const size_t smem_fixed = 1024 + (size_t)STAGES * STAGE_BYTES + 2 * CW * kSelGroup * sizeof(float) +
+    const size_t smem_fixed = 1024 + 2 * CW * kSelGroup * sizeof(float) + 8 * 128 * sizeof(float) +
                               (2 * STAGES + 12) * 8 + 16;
 
 #define CONVNN_TC2_LAUNCH(N)                                                                                     \
     do {                                                                                                         \
-        auto kern = sim_topk_tc2_kernel<N>;                                                                      \
-        const size_t smem = smem_fixed + 2 * N * kSelGroup * sizeof(float);                                      \
+        constexpr int NST = N > 24 ? STAGES - 1 : STAGES;                                                        \
+        auto kern = sim_topk_tc2_kernel<N, NST>;                                                                 \
+        const size_t smem = smem_fixed + (size_t)NST * STAGE_BYTES + 2 * N * kSelGroup * sizeof(float);          \
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
         if (e != cudaSuccess) return set_error(CONVNN_E_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e)); \
         cudaLaunchConfig_t cfg{};                                                                                \
