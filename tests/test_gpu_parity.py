@@ -86,6 +86,14 @@ BASELINE_SHAPES = {
     "cfg5_long_spatial": (1, 1024, dict(d_hidden=768, num_heads=1, K=9, magnitude_type="cosine",
                                         sampling_type="spatial", num_samples=256)),
     "h3_matmul": (2, 197, dict(d_hidden=192, num_heads=3, K=9, magnitude_type="matmul")),
+    # kernel variants the baseline shapes leave out: standard conv over 192 channels (24 channel
+    # groups), separable conv on 64-channel heads (one slice per head in the streaming kernel),
+    # a head three GEMM tiles wide with the cosine statistic, a long sequence on the pair kernel
+    "std_d192": (2, 197, dict(d_hidden=192, num_heads=1, K=9, magnitude_type="cosine", convolution_type="standard")),
+    "dwsep_h3": (2, 197, dict(d_hidden=192, num_heads=3, K=9, magnitude_type="euclidean",
+                              convolution_type="depthwise-separable")),
+    "d768_cosine_short": (2, 197, dict(d_hidden=768, num_heads=1, K=9, magnitude_type="cosine")),
+    "long_pair": (1, 1536, dict(d_hidden=128, num_heads=1, K=9, magnitude_type="cosine", seq_length=1536)),
 }
 
 
