@@ -19,6 +19,8 @@
 // The N range may be split into up to three equal parts with their own output tensors,
 // which lets one launch produce k, v and q from the packed [W_k; W_v; W_q].
 // Every mbarrier wait is bounded (see sm100.cuh); an expiry latches the device status.
+#include <atomic>
+
 #include "common.cuh"
 #include "sm100.cuh"
 #include "f32x2.cuh"
@@ -721,10 +723,18 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
         cfg.blockDim = dim3(W ? NTHREADS_WIDE : NTHREADS); cfg.dynamicSmemBytes = smem; cfg.stream = st;    \
         cfg.attrs = attr; cfg.numAttrs = 1;                                                                 \
         cfg.gridDim = dim3(2);                                                                              \
+        /* co-resident clusters for this kernel and shared-memory size, asked once per process */       \
+        static std::atomic<long long> occ_cache{-1};                                                        \
         int max_clusters = 0;                                                                               \
-        e = cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg);                                      \
-        if (e != cudaSuccess || max_clusters < 1)                                                           \
-            return set_error(CONVNN_E_CUDA, "cudaOccupancyMaxActiveClusters: %s", cudaGetErrorString(e));   \
+        const long long seen = occ_cache.load(std::memory_order_relaxed);                                   \
+        if (seen >= 0 && (size_t)(seen >> 20) == smem) {                                                    \
+            max_clusters = (int)(seen & 0xFFFFF);                                                           \
+        } else {                                                                                            \
+            e = cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg);                                  \
+            if (e != cudaSuccess || max_clusters < 1)                                                       \
+                return set_error(CONVNN_E_CUDA, "cudaOccupancyMaxActiveClusters: %s", cudaGetErrorString(e)); \
+            occ_cache.store(((long long)smem << 20) | max_clusters, std::memory_order_relaxed);             \
+        }                                                                                                   \
         const int nc = p.n_tiles < max_clusters ? p.n_tiles : max_clusters;                                 \
         cfg.gridDim = dim3(2 * nc);                                                                         \
         e = cudaLaunchKernelEx(&cfg, kern, tmA, tmW, p);                                                    \

@@ -18,6 +18,8 @@
 //                           through shared memory at the end of the unit (mbarrier hand-over)
 // Every wait on an mbarrier is bounded; an expiry latches a status code, raises the abort
 // flag of both CTAs and lets every role run to the common exit (cluster barrier, TMEM free).
+#include <atomic>
+
 #include "common.cuh"
 #include "sm100.cuh"
 #include "toplist.cuh"
@@ -333,10 +335,18 @@ int launch_sim_topk_tc2(const convnn_desc* d, const Dims& dm, const void* q, con
         cfg.blockDim = dim3(NTHREADS); cfg.dynamicSmemBytes = smem; cfg.stream = st;                             \
         cfg.attrs = attr; cfg.numAttrs = 1;                                                                      \
         cfg.gridDim = dim3(2);                                                                                   \
-        int max_clusters = 0;                                                                                    \
-        e = cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg);                                           \
-        if (e != cudaSuccess || max_clusters < 1)                                                                \
-            return set_error(CONVNN_E_CUDA, "cudaOccupancyMaxActiveClusters: %s", cudaGetErrorString(e));        \
+        /* co-resident clusters for this kernel and shared-memory size, asked once per process */       \
+        static std::atomic<long long> occ_cache{-1};                                                        \
+        int max_clusters = 0;                                                                               \
+        const long long seen = occ_cache.load(std::memory_order_relaxed);                                   \
+        if (seen >= 0 && (size_t)(seen >> 20) == smem) {                                                    \
+            max_clusters = (int)(seen & 0xFFFFF);                                                           \
+        } else {                                                                                            \
+            e = cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg);                                  \
+            if (e != cudaSuccess || max_clusters < 1)                                                       \
+                return set_error(CONVNN_E_CUDA, "cudaOccupancyMaxActiveClusters: %s", cudaGetErrorString(e)); \
+            occ_cache.store(((long long)smem << 20) | max_clusters, std::memory_order_relaxed);             \
+        }                                                                                                   \
         const int nc = p.n_units < max_clusters ? p.n_units : max_clusters;                                      \
         cfg.gridDim = dim3(2 * nc);                                                                              \
         e = cudaLaunchKernelEx(&cfg, kern, tmK, tmQ, p);                                                         \
