@@ -9,6 +9,15 @@ namespace convnn {
 
 constexpr int kSelGroup = 128;    // threads per epilogue group = stride of the key staging buffer
 
+// Columns 0 .. W-1 of a row: insertion number j only touches the first j + 1 slots.
+template <int NSEL, int W, int J>
+__device__ __forceinline__ void prefix_insert(TopList<NSEL>& top, const float (&key)[W], bool row_ok, int left) {
+    if constexpr (J < W) {
+        if (row_ok && J < left) top.template insert_sorted_first<J>(key[J], J);
+        prefix_insert<NSEL, W, J + 1>(top, key, row_ok, left);
+    }
+}
+
 // One chunk of W accumulator columns of this thread's row: keys, then either plain inserts
 // (the first 32 columns of a row, where most values enter the list anyway) or a threshold
 // mask followed by a drain loop that only visits the survivors.
@@ -51,9 +60,13 @@ __device__ __forceinline__ void consume(TopList<NSEL>& top, const uint32_t (&acc
     }
     const int left = p.S - col0;                       // valid columns from col0 on
     if (col0 < 32) {
+        if (col0 == 0) {                               // the list is still filling up
+            prefix_insert<NSEL, W, 0>(top, key, row_ok, left);
+        } else {
 #pragma unroll
-        for (int j = 0; j < W; ++j)
-            if (row_ok && j < left) top.insert_sorted(key[j], col0 + j);
+            for (int j = 0; j < W; ++j)
+                if (row_ok && j < left) top.insert_sorted(key[j], col0 + j);
+        }
         return;
     }
     const float thr = top.worst();

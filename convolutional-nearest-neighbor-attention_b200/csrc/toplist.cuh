@@ -51,6 +51,23 @@ struct TopList {
         i[0] = g0 ? col : i[0];
     }
 
+    // insert_sorted() for a list that has received at most J insertions so far: slots above J
+    // still hold the initial -inf and would only be shifted onto each other, so they are left out.
+    template <int J>
+    __device__ __forceinline__ void insert_sorted_first(float key, int col) {
+        constexpr int TOP = J < N - 1 ? J : N - 1;
+#pragma unroll
+        for (int s = TOP; s >= 1; --s) {
+            const bool gt = key > v[s];
+            const bool gtp = key > v[s - 1];
+            v[s] = gt ? (gtp ? v[s - 1] : key) : v[s];
+            i[s] = gt ? (gtp ? i[s - 1] : col) : i[s];
+        }
+        const bool g0 = key > v[0];
+        v[0] = g0 ? key : v[0];
+        i[0] = g0 ? col : i[0];
+    }
+
     // Insert under the full (key, column) order: among equal keys the lower column ranks
     // first wherever it came from.  Used to merge lists built over interleaved column ranges,
     // where "inserted first" no longer means "lower column".
