@@ -231,10 +231,21 @@ def run_single_stage(args) -> int:
     q, k, v, qs, ks = ops.qkv_proj(spec, x, w_qkv)
     idx, val = ops.sim_topk(spec, q, k, qs, ks)
     o = ops.gather_conv(spec, v, idx, val, w_conv, w_pw)
+    F = cfg.d_mlp
+    h = torch.randn(B, T, F, device=dev).to(torch.bfloat16)
+    W1 = (torch.randn(F, D, device=dev) / 14).to(torch.bfloat16)
+    W2 = (torch.randn(D, F, device=dev) / 28).to(torch.bfloat16)
+    b1, b2 = torch.randn(F, device=dev).to(torch.bfloat16), torch.randn(D, device=dev).to(torch.bfloat16)
+    gam, bet = torch.ones(D, device=dev).to(torch.bfloat16), torch.zeros(D, device=dev).to(torch.bfloat16)
     fns = {"qkv_proj": lambda: ops.qkv_proj(spec, x, w_qkv),
            "sim_topk": lambda: ops.sim_topk(spec, q, k, qs, ks),
            "gather_conv": lambda: ops.gather_conv(spec, v, idx, val, w_conv, w_pw),
-           "out_proj": lambda: ops.out_proj(spec, o, w_o)}
+           "out_proj": lambda: ops.out_proj(spec, o, w_o),
+           # the encoder's kernels around the layer (same GEMM kernel, other epilogues)
+           "out_proj_skip": lambda: ops.out_proj(spec, o, w_o, residual=x),
+           "mlp0": lambda: ops.linear(x, W1, b1, gelu=True),
+           "mlp3": lambda: ops.linear(h, W2, b2, residual=x),
+           "layernorm": lambda: ops.layernorm(x, gam, bet)}
     fn = fns[args.stage]
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -502,7 +513,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--stage", choices=["qkv_proj", "sim_topk", "gather_conv", "out_proj"],
+    ap.add_argument("--stage", choices=["qkv_proj", "sim_topk", "gather_conv", "out_proj", "out_proj_skip", "mlp0",
+                                        "mlp3", "layernorm"],
                     help="run only this stage of one layer (profiling aid)")
     ap.add_argument("--layer-sweep", action="store_true",
                     help="standalone layer on long sequences (8 x N x 768), per-stage time and roofline")
