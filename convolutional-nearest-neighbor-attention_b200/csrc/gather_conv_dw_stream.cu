@@ -117,7 +117,7 @@ gather_conv_dw_stream_kernel(const __grid_constant__ CUtensorMap tmV, const DwsP
 #pragma unroll
             for (int j = 0; j < KT; ++j) np[t * KT + j] = make_int2(ni[j] * (CH * 2), __float_as_int(pw[j]));
         }
-        // the V slice: bounded wait by one thread, verdict shared through the barrier below
+        // the V slice: bounded wait by one thread, outcome shared through the barrier below
         if (threadIdx.x == 0 && !mbar_wait(&full[buf], (it >> 1) & 1u, (volatile int*)&s_fail)) {
             s_fail = 1;
             atomicCAS(&g_dw_stream_status, 0, 31);
