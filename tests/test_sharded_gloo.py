@@ -73,3 +73,14 @@ def test_two_ranks_reproduce_single_process(total):
 def test_gather_is_identity_without_process_group():
     x = torch.randn(3, 4)
     assert gather_logits(x, 3) is x
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="on a GPU box the call does bind the process")
+def test_host_binding_is_a_no_op_without_a_gpu():
+    """bind_host_to_device only narrows the process's CPU affinity when NVML knows the device;
+    on a machine without one it reports False and leaves the affinity alone."""
+    import os
+    from convnn_b200.sharded import bind_host_to_device
+    before = os.sched_getaffinity(0)
+    assert bind_host_to_device("cuda:0") is False
+    assert os.sched_getaffinity(0) == before
