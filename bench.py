@@ -486,7 +486,7 @@ def run_ours(args) -> int:
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "cfg-2 ViT-Tiny ConvNNAttention bf16 inference 224x224 patch16 (197 tokens) "
-                                   "d=192 12 layers 1000 classes K=9 cosine/all/depthwise",
+                                   "d=192 heads=1 12 layers 1000 classes K=9 cosine/all/depthwise",
                        "batch_per_gpu": B, "global_batch": total, "parallelism": f"batch-shard x{world}",
                        "l2": f"{NBUF} distinct resident input batches (231 MB) rotate, larger than L2",
                        "launch": graph_note, "host_numa_bound": bool(numa_bound)},
