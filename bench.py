@@ -36,6 +36,8 @@ WORKLOAD = dict(layer="ConvNNAttention", img_size=(3, 224, 224), patch_size=16, 
                 convolution_type="depthwise", softmax_topk_val=True, dropout=0.0, attention_dropout=0.0)
 BATCH_PER_GPU = 256
 METRIC, UNIT = "ConvNN-ViT images/sec", "images/s"
+WORKLOAD_NAME = ("cfg-2 ViT-Tiny ConvNNAttention inference 224x224 patch16 (197 tokens) d=192 heads=1 12 layers "
+                 "1000 classes K=9 cosine/all/depthwise")
 
 
 def peaks():
@@ -87,8 +89,8 @@ def run_reference_arm(args) -> int:
         "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": done,
         "warmup": max(1, min(args.warmup, 2)), "ms_per_step": per * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "cfg-2 ViT-Tiny ConvNNAttention 224x224 patch16 K=9 cosine/all/depthwise",
-                   "batch_per_step": batch},
+        "config": {"workload": WORKLOAD_NAME, "batch_per_step": batch,
+                   "note": "fp32 CPU arm of the same model; each step is a 32-image sample of the 256-image batch"},
         "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
                          "sample": f"{done} forwards of {batch} images (of the 256-image batch), fp32, torch CPU"},
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -485,8 +487,7 @@ def run_ours(args) -> int:
             "metric": METRIC, "value": total * args.steps / (ms / 1e3), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "cfg-2 ViT-Tiny ConvNNAttention bf16 inference 224x224 patch16 (197 tokens) "
-                                   "d=192 heads=1 12 layers 1000 classes K=9 cosine/all/depthwise",
+            "config": {"workload": WORKLOAD_NAME,
                        "batch_per_gpu": B, "global_batch": total, "parallelism": f"batch-shard x{world}",
                        "l2": f"{NBUF} distinct resident input batches (231 MB) rotate, larger than L2",
                        "launch": graph_note, "host_numa_bound": bool(numa_bound)},
