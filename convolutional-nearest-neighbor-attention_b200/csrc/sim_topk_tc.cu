@@ -37,7 +37,7 @@ constexpr int BM = 128;
 constexpr int MAX_STAGES = 3;
 constexpr int NTHREADS = 320;     // TMA warp, MMA warp, 2 x 4 epilogue warps
 constexpr int GROUP = kSelGroup;  // threads per epilogue group
-// Two launch shapes.  SMALL (short candidate lists, d_k <= 256): BN <= 64, 2 stages, 16-column
+// Two launch shapes.  SMALL (short candidate lists, d_k <= 256, or <= 512 on short sequences): BN <= 64, 2 stages, 16-column
 // epilogue chunks and two CTAs per SM, so four epilogue warps per scheduler hide each other's
 // latency -- this regime is bound by the selection, not by the MMAs.  LARGE: BN <= 128, 3 stages,
 // one CTA per SM, for long sequences where the tensor pipe is the limiter.
@@ -283,7 +283,9 @@ int launch_sim_topk_tc(const convnn_desc* d, const Dims& dm, const void* q, cons
     p.T = dm.T; p.S = dm.S; p.H = dm.H; p.K = dm.K; p.nsel = dm.nsel; p.metric = d->metric; p.sampled = d->sampled;
     p.KCH = dm.Cp % 64 == 0 ? 64 : (dm.Cp % 32 == 0 ? 32 : 16);
     p.KC = dm.Cp / p.KCH;
-    const bool small_cfg = dm.Cp <= 256 && dm.nsel <= 12;
+    // (heads of 257-512 channels on short sequences: 19.3 against 22.8 us at B=256, T=197, S=64, d_k=384;
+    // with 768 channels the small shape measured slower)
+    const bool small_cfg = dm.nsel <= 12 && (dm.Cp <= 256 || (dm.Cp <= 512 && dm.T <= 512));
     const int bn_cap = small_cfg ? 64 : 128;
     p.stages = small_cfg ? 2 : 3;
     const int ntile = (dm.S + bn_cap - 1) / bn_cap;
