@@ -110,3 +110,27 @@ def test_pair_kernel_and_simt_kernel_agree_on_long_sequences():
     same = (i16 == i32).all(-1)
     assert float(same.float().mean()) > 0.999
     assert float((v16 - v32).abs().max()) < 1e-4
+
+
+def test_long_sequence_layer_replays_from_a_cuda_graph():
+    """The cluster launch of the pair kernel (and everything else in the layer) can be captured:
+    a replayed graph reproduces the eager result bit for bit."""
+    import convnn_b200
+    layer = convnn_b200.MultiHeadConvNNAttention(128, 1, 0.0, 9, "all", -1, 0, "cosine", seq_length=1280)
+    layer = layer.eval().to(DEV, torch.bfloat16)
+    x = torch.randn(2, 1280, 128, generator=torch.Generator().manual_seed(9)).to(DEV, torch.bfloat16)
+    with torch.no_grad():
+        want = layer(x)
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            layer(x)
+        torch.cuda.current_stream().wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            got = layer(x)
+        g.replay()
+        torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    assert _capi.device_status() == 0
