@@ -7,13 +7,23 @@ bfloat16 inference, batch 256 x 3 x 224 x 224 synthetic N(0,1) images, patch 16 
 tokens, d=192, 12 layers, 1000 classes, K=9, cosine similarity, sampling 'all', depthwise
 conv, random-init weights.  A step is one forward of the whole model on one batch per GPU.
 
+A step is `inner_iters` batches per GPU (stated in `config`), chosen so that the timed region
+of `steps` steps lasts about a second; `ms_per_step` x `steps` is the timed region.
+
 One JSON line on stdout (rank 0).  `value` = images/s with inputs resident in HBM, timed
 with CUDA events on the launching stream, max over ranks.  `e2e` = the same through the
-public module call with HOST (pinned) images: the host->device copy and the device->host
-read of the logits are inside the timed region.  `roofline` describes the layer kernel
-with the largest share of device time, timed with CUDA events around the stage calls.
-`cpu_baseline` / `--impl reference` time the CPU oracle port of the same model on the host
-cores (the reference is eager PyTorch; its checkout does not travel to the GPU box).
+public module call with HOST (pinned, bfloat16) images: the host->device copy and the
+device->host read of the logits are inside the timed region.  `roofline` describes the layer
+kernel with the largest share of device time, timed with CUDA events around the stage calls.
+At N=1 the line also carries `configs` (whole-model images/s of the baseline's ViT-Small and
+ViT-Base BranchAttention configurations) and `layer_sweep` (the standalone layer on 4096 and
+16384 tokens of 768 channels: tokens/s, similarity TFLOP/s and gather/conv GB/s against the
+measured peaks, each case with its own clock record); at N>1 a `strong` record (global batch
+256 split over the ranks).
+`cpu_baseline` / `--impl reference` time the model on the host cores: the reference's own
+vit.ViT when a checkout is reachable ($CONVNN_REF_PATH, ../reference, baseline/_ref), else
+the CPU oracle port of the same model (the reference is eager PyTorch; its checkout does not
+travel to the GPU box).
 """
 from __future__ import annotations
 
@@ -54,26 +64,64 @@ def peaks():
 # CPU arm: the oracle port of the reference model on the host cores
 # ---------------------------------------------------------------------------------------
 
+def find_reference_checkout():
+    for p in (os.environ.get("CONVNN_REF_PATH"), os.path.join(os.path.dirname(ROOT), "reference"),
+              os.path.join(ROOT, "baseline", "_ref")):
+        if p and os.path.exists(os.path.join(p, "vit.py")) and os.path.exists(os.path.join(p, "layers.py")):
+            return p
+    return None
+
+
 def cpu_model_throughput(batch: int, steps: int, warmup: int, budget_s: float = 30.0):
-    """images/s of the CPU oracle (fp32, all host threads) on ``batch`` images per step."""
+    """images/s of the model on the host cores (fp32, all host threads), ``batch`` images per
+    step: the reference's own vit.ViT when its checkout is reachable, else the oracle port.
+    -> (images/s, seconds per step, threads, steps done, kind)."""
     from oracle.vit_oracle import ViTConfig, make_images, make_vit_weights, vit_forward
     cfg = ViTConfig(**WORKLOAD)
     sd = make_vit_weights(cfg, seed=1)
     img = make_images(batch, cfg, seed=2)
     cores = torch.get_num_threads()
+    kind, fwd = "port", (lambda: vit_forward(img, sd, cfg))
+    ref = find_reference_checkout()
+    if ref is not None:
+        try:
+            import types
+            from oracle.pin_against_reference import load_reference
+            _, ref_vit = load_reference(ref)
+            a = {f: getattr(cfg, f) for f in cfg.__dataclass_fields__}
+            a.update(device="cpu", img_size=tuple(cfg.img_size))
+            model = ref_vit.ViT(types.SimpleNamespace(**a)).eval()
+            model.load_state_dict(sd, strict=True)
+            kind, fwd = "reference", (lambda: model(img))
+        except Exception as e:  # noqa: BLE001
+            print(f"reference checkout at {ref} could not be used ({type(e).__name__}: {e}); timing the port",
+                  file=sys.stderr)
     with torch.no_grad():
         for _ in range(warmup):
-            vit_forward(img, sd, cfg)
+            fwd()
         times = []
         t_start = time.perf_counter()
         for _ in range(steps):
             t0 = time.perf_counter()
-            vit_forward(img, sd, cfg)
+            fwd()
             times.append(time.perf_counter() - t0)
             if time.perf_counter() - t_start > budget_s:
                 break
     per = sum(times) / len(times)
-    return batch / per, per, cores, len(times)
+    return batch / per, per, cores, len(times), kind
+
+
+def inner_iters_for(steps: int) -> int:
+    """Batches per step such that `steps` steps last about a second at ~1.6-2 ms per batch."""
+    return max(1, -(-640 // max(1, steps)))
+
+
+def config_record(world: int, inner: int) -> dict:
+    return {"workload": WORKLOAD_NAME, "batch_per_gpu": BATCH_PER_GPU, "global_batch": BATCH_PER_GPU * world,
+            "inner_iters": inner, "images_per_step": BATCH_PER_GPU * world * inner,
+            "parallelism": f"batch-shard x{world}",
+            "l2": "3 distinct resident input batches (231 MB) rotate, larger than L2",
+            "launch": "cuda_graph"}
 
 
 def run_reference_arm(args) -> int:
@@ -83,16 +131,17 @@ def run_reference_arm(args) -> int:
     # torchrun pins OMP_NUM_THREADS=1; the CPU arm is meant to use every host core
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     batch = 32
-    steps = max(1, min(args.steps, 10))
-    v, per, cores, done = cpu_model_throughput(batch, steps, max(1, min(args.warmup, 2)), budget_s=120.0)
+    warm = max(1, min(args.warmup, 3))
+    v, per, cores, done, kind = cpu_model_throughput(batch, args.steps, warm, budget_s=150.0)
+    what = "the reference's own vit.ViT" if kind == "reference" else "the CPU oracle port of the model"
     line = {
         "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": done,
-        "warmup": max(1, min(args.warmup, 2)), "ms_per_step": per * 1e3, "higher_is_better": True,
+        "warmup": warm, "ms_per_step": per * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD_NAME, "batch_per_step": batch,
-                   "note": "fp32 CPU arm of the same model; each step is a 32-image sample of the 256-image batch"},
-        "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": f"{done} forwards of {batch} images (of the 256-image batch), fp32, torch CPU"},
+        "config": config_record(int(os.environ.get("WORLD_SIZE", "1")), args.inner_iters),
+        "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": kind,
+                         "sample": f"{done} forwards of {batch} images (a sample of the workload's 256-image batches), "
+                                   f"fp32, torch CPU, {what}"},
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -105,22 +154,68 @@ def run_reference_arm(args) -> int:
 # ---------------------------------------------------------------------------------------
 
 class ClockSampler:
-    """nvidia-smi clock / throttle samples taken while the timed region runs."""
+    """SM clock / throttle-reason samples taken while a timed region runs: an NVML polling thread
+    (about one sample per 2 ms; the main thread sits in cudaStreamSynchronize meanwhile), or an
+    nvidia-smi subprocess at 20 ms where NVML cannot be loaded.  Read-only."""
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
+    _nvml = None
 
-    def __init__(self, index: int):
-        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+    @classmethod
+    def _handle(cls, dev_index: int):
+        import pynvml
+        if cls._nvml is None:
+            pynvml.nvmlInit()
+            cls._nvml = pynvml
+        props = torch.cuda.get_device_properties(dev_index)
+        bus = "%08x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
+        return pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+
+    def __init__(self, index: int, period_s: float = 0.002):
+        import threading
+        self.rows, self.p, self.f, self.thread = [], None, None, None
+        self.stop_flag = threading.Event()
         try:
-            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                       "-lms", "20", "-i", str(index)], stdout=self.f, stderr=subprocess.DEVNULL)
-        except OSError:
-            self.p = None
+            h = self._handle(index)
+            nv = self._nvml
+            self.smax = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            reasons_fn = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                nv.nvmlDeviceGetCurrentClocksThrottleReasons
+            bits = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
+
+            def poll():
+                while not self.stop_flag.is_set():
+                    try:
+                        mhz = float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                        r = int(reasons_fn(h))
+                        self.rows.append((mhz, {n for n, b in bits.items() if r & b}))
+                    except Exception:  # noqa: BLE001
+                        pass
+                    time.sleep(period_s)
+            self.thread = threading.Thread(target=poll, daemon=True)
+            self.thread.start()
+            self.how = "nvml thread"
+        except Exception:  # noqa: BLE001
+            self.thread = None
+            self.how = "nvidia-smi -lms 20"
+            self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            try:
+                self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                           "-lms", "20", "-i", str(index)], stdout=self.f, stderr=subprocess.DEVNULL)
+            except OSError:
+                self.p = None
 
     def stop(self) -> dict:
+        if self.thread is not None:
+            self.stop_flag.set()
+            self.thread.join(timeout=2)
+            sm = sorted(r[0] for r in self.rows)
+            reasons = set().union(*[r[1] for r in self.rows]) if self.rows else set()
+            return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_min_mhz": sm[0] if sm else None,
+                    "sm_max_mhz": self.smax, "samples": len(sm), "reasons": sorted(reasons), "how": self.how}
         if self.p is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "samples": 0, "reasons": ["nvidia-smi unavailable"]}
         self.p.terminate()
         try:
             self.p.wait(timeout=5)
@@ -145,8 +240,8 @@ class ClockSampler:
                 if v.strip().lower() == "active":
                     reasons.add(n)
         sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": smax, "samples": len(sm),
-                "reasons": sorted(reasons)}
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_min_mhz": sm[0] if sm else None, "sm_max_mhz": smax,
+                "samples": len(sm), "reasons": sorted(reasons), "how": self.how}
 
 
 class StageTimer:
@@ -261,17 +356,39 @@ def run_single_stage(args) -> int:
     return 0
 
 
-def run_layer_sweep(args) -> int:
+def timed_loop(fn, min_reps: int, min_ms: float):
+    """Average device time of fn() in ms: CUDA events on the launching stream around a loop of at
+    least `min_reps` calls lasting at least `min_ms` (sized from a short trial)."""
+    for _ in range(2):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(3):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    est = max(e0.elapsed_time(e1) / 3, 1e-3)
+    reps = max(min_reps, int(min_ms / est) + 1)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps, reps
+
+
+def layer_sweep(dev, sweep_n, min_reps=20, min_ms=120.0):
     """Standalone ConvNN layer on long sequences (cfg-5 of the baseline): x ~ N(0,1) of shape
     8 x N x 768 bf16, cosine, depthwise, sampling 'all' and 'spatial' (N/4 candidates), K in {9, 25}.
-    Prints one JSON line per case with per-stage device time, tokens/s and roofline fractions."""
+    One record per case: per-stage device time (>= 20 launches and >= 120 ms each, inputs of a
+    few hundred MB, larger than L2), tokens/s, roofline fractions and the clocks sampled meanwhile."""
     import convnn_b200
     from convnn_b200 import ops
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(dev)
     pk = peaks()
     B, D = 8, 768
-    for N in args.sweep_n:
+    out = []
+    for N in sweep_n:
         for K in (9, 25):
             for sampling in ("all", "spatial"):
                 S = N if sampling == "all" else N // 4
@@ -280,39 +397,112 @@ def run_layer_sweep(args) -> int:
                 spec = layer._spec()
                 w_qkv, w_conv, w_pw, w_o = layer.packed_weights(torch.bfloat16, dev)
                 cand = layer.candidates(N, dev)
-                x = torch.randn(B, N, D, device=dev).to(torch.bfloat16)
-                q, k, v, qs, ks = ops.qkv_proj(spec, x, w_qkv, cand)
-                idx, val = ops.sim_topk(spec, q, k, qs, ks, cand)
-                o = ops.gather_conv(spec, v, idx, val, w_conv, w_pw, S=S)
-                fns = {"qkv_proj": lambda: ops.qkv_proj(spec, x, w_qkv, cand),
-                       "sim_topk": lambda: ops.sim_topk(spec, q, k, qs, ks, cand),
-                       "gather_conv": lambda: ops.gather_conv(spec, v, idx, val, w_conv, w_pw, S=S),
-                       "out_proj": lambda: ops.out_proj(spec, o, w_o, S=S)}
-                times = {}
+                # distinct buffer sets visited in turn, together larger than L2 (one set is 4 x 50 MB at
+                # N=4096, 4 x 201 MB at N=16384); each stage is captured in a CUDA graph that runs it once
+                # per set, so back-to-back launches carry no host time and find nothing cached
+                sets = 1 if N >= 16384 else 3
+                data = []
+                for _ in range(sets):
+                    x = torch.randn(B, N, D, device=dev).to(torch.bfloat16)
+                    q, k, v, qs, ks = ops.qkv_proj(spec, x, w_qkv, cand)
+                    idx, val = ops.sim_topk(spec, q, k, qs, ks, cand)
+                    o = ops.gather_conv(spec, v, idx, val, w_conv, w_pw, S=S)
+                    data.append(dict(x=x, q=q, k=k, v=v, qs=qs, ks=ks, idx=idx, val=val, o=o))
+                fns = {"qkv_proj": lambda d: ops.qkv_proj(spec, d["x"], w_qkv, cand),
+                       "sim_topk": lambda d: ops.sim_topk(spec, d["q"], d["k"], d["qs"], d["ks"], cand),
+                       "gather_conv": lambda d: ops.gather_conv(spec, d["v"], d["idx"], d["val"], w_conv, w_pw, S=S),
+                       "out_proj": lambda d: ops.out_proj(spec, d["o"], w_o, S=S)}
+                torch.cuda.synchronize()
+                sampler = ClockSampler(dev.index or 0)
+                times, reps = {}, {}
                 for name, fn in fns.items():
-                    fn()
-                    torch.cuda.synchronize()
-                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    reps = 3
-                    e0.record()
-                    for _ in range(reps):
-                        fn()
-                    e1.record()
-                    torch.cuda.synchronize()
-                    times[name] = e0.elapsed_time(e1) / reps
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph):
+                        keep = [fn(d) for d in data]
+                    ms, n = timed_loop(graph.replay, -(-min_reps // sets), min_ms)
+                    times[name], reps[name] = ms / sets, n * sets
+                    del keep, graph
+                clocks = sampler.stop()
                 work = algorithmic_work(B, N, S, D, 1, K)
                 total = sum(times.values())
                 sim_tf = work["sim_topk"]["flops"] / times["sim_topk"] / 1e9
-                print(json.dumps({
+                gc_gbs = work["gather_conv"]["bytes"] / times["gather_conv"] / 1e6
+                out.append({
                     "case": f"N={N} K={K} {sampling} S={S}", "tokens_per_s": B * N / (total / 1e3),
-                    "ms": {k2: round(v2, 4) for k2, v2 in times.items()},
-                    "sim_topk_TFLOPs": sim_tf, "sim_topk_frac_of_tensor_peak": sim_tf / pk["tf_burst"],
-                    "gather_conv_GBps": work["gather_conv"]["bytes"] / times["gather_conv"] / 1e6,
-                    "gather_conv_frac_of_hbm_peak": work["gather_conv"]["bytes"] / times["gather_conv"] / 1e6 / pk["hbm"],
-                    "peak_source": pk["source"]}))
-                del layer, x, q, k, v, idx, val, o
+                    "ms": {k2: round(v2, 4) for k2, v2 in times.items()}, "launches_timed": reps,
+                    "sim_topk_TFLOPs": sim_tf, "sim_topk_frac_of_tensor_peak_burst": sim_tf / pk["tf_burst"],
+                    "sim_topk_frac_of_tensor_peak_sustained": sim_tf / pk["tf_sustained"],
+                    "gather_conv_GBps": gc_gbs, "gather_conv_frac_of_hbm_peak": gc_gbs / pk["hbm"],
+                    "peak_source": pk["source"], "clocks": clocks})
+                del layer, data, x, q, k, v, idx, val, o, fns
                 torch.cuda.empty_cache()
+    return out
+
+
+def run_layer_sweep(args) -> int:
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    with torch.no_grad():
+        for rec in layer_sweep(dev, args.sweep_n):
+            print(json.dumps(rec))
     return 0
+
+
+# Other configurations of the baseline, whole model, bfloat16 (cfg-3: ViT-Small, euclidean, 64 random
+# candidates shared by all layers, separable conv; cfg-4: ViT-Base BranchAttention, 12 heads, standard conv).
+OTHER_CONFIGS = {
+    "cfg-3 ViT-Small ConvNNAttention euclidean/random-64/depthwise-separable B=256": (256, dict(
+        layer="ConvNNAttention", d_hidden=384, d_mlp=1536, num_heads=1, num_layers=12, magnitude_type="euclidean",
+        sampling_type="random", num_samples=64, convolution_type="depthwise-separable")),
+    "cfg-4 ViT-Base BranchAttention 12 heads cosine/all/standard B=128": (128, dict(
+        layer="BranchAttention", d_hidden=768, d_mlp=3072, num_heads=12, num_layers=12, magnitude_type="cosine",
+        convolution_type="standard", branch_ratio=0.5)),
+}
+
+
+def graph_model(model, x):
+    """Capture model(x) in a CUDA graph (after two eager warm-up calls) -> (graph, static output)."""
+    for _ in range(2):
+        model(x)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        y = model(x)
+    return g, y
+
+
+def other_configs(dev, min_ms=400.0):
+    """Whole-model images/s of the baseline's other ViT configurations (device-resident inputs, two
+    distinct input batches alternating, CUDA graph, >= 10 forwards and >= 400 ms each)."""
+    import convnn_b200
+    from oracle.vit_oracle import ViTConfig, make_vit_weights  # seeded weights only (not on the timed path)
+    out = {}
+    for name, (B, kw) in OTHER_CONFIGS.items():
+        cfg = ViTConfig(**kw)
+        model = convnn_b200.ViT(convnn_b200.make_args(**{f: getattr(cfg, f) for f in cfg.__dataclass_fields__},
+                                                      device=dev)).eval()
+        model.load_state_dict(make_vit_weights(cfg, seed=1), strict=True)
+        model = model.to(dev, torch.bfloat16)
+        if cfg.sampling_type == "random":
+            model.set_candidates(torch.randperm(cfg.seq_len, generator=torch.Generator().manual_seed(17))
+                                 [: cfg.num_samples].to(dev))
+        xs = [torch.randn(B, 3, 224, 224, device=dev).to(torch.bfloat16) for _ in range(2)]
+        static_in = torch.empty_like(xs[0])
+        static_in.copy_(xs[0])
+        graph, _ = graph_model(model, static_in)
+        i = [0]
+
+        def fwd():
+            static_in.copy_(xs[i[0] & 1], non_blocking=True)
+            graph.replay()
+            i[0] += 1
+        sampler = ClockSampler(dev.index or 0)
+        ms, reps = timed_loop(fwd, 10, min_ms)
+        out[name] = {"images_per_s": B / (ms / 1e3), "ms_per_forward": ms, "batch": B, "forwards_timed": reps,
+                     "dtype": "bf16", "clocks": sampler.stop()}
+        del graph, model, xs, static_in
+        torch.cuda.empty_cache()
+    return out
 
 
 # dram__bytes_read + dram__bytes_write of one launch of each stage at the bench shape, from the
@@ -334,11 +524,46 @@ def algorithmic_work(B, T, S, D, H, K, elt=2):
     }
 
 
+class LogitsGather:
+    """All-gather of each step's logits on a side stream, double-buffered, so that the collective of
+    batch i runs under the forward of batch i+1 instead of between the two on the compute stream."""
+
+    def __init__(self, world, n_local, classes, dtype, dev):
+        self.world = world
+        if world > 1:
+            self.side = torch.cuda.Stream(dev)
+            self.local = [torch.empty(n_local, classes, dtype=dtype, device=dev) for _ in range(2)]
+            self.full = [torch.empty(n_local * world, classes, dtype=dtype, device=dev) for _ in range(2)]
+            self.copied = [torch.cuda.Event() for _ in range(2)]
+            self.gathered = [torch.cuda.Event() for _ in range(2)]
+            self.i = 0
+
+    def __call__(self, logits):
+        """Returns the tensor that will hold the gathered logits and the event that says when."""
+        if self.world == 1:
+            return logits, None
+        import torch.distributed as dist
+        s = self.i & 1
+        self.i += 1
+        cur = torch.cuda.current_stream()
+        cur.wait_event(self.gathered[s])            # the gather that last read this slot has finished
+        self.local[s].copy_(logits, non_blocking=True)
+        self.copied[s].record(cur)
+        with torch.cuda.stream(self.side):
+            self.side.wait_event(self.copied[s])
+            dist.all_gather_into_tensor(self.full[s], self.local[s])
+            self.gathered[s].record(self.side)
+        return self.full[s], self.gathered[s]
+
+    def drain(self):
+        if self.world > 1:
+            torch.cuda.current_stream().wait_stream(self.side)
+
+
 def run_ours(args) -> int:
     import torch.distributed as dist
     import convnn_b200
     from convnn_b200 import _capi
-    from convnn_b200.sharded import gather_logits
     from oracle.vit_oracle import ViTConfig, make_vit_weights  # seeded weights only (not on the timed path)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -353,6 +578,7 @@ def run_ours(args) -> int:
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     lib = _capi.lib()
+    inner = args.inner_iters
 
     cfg = ViTConfig(**WORKLOAD)
     margs = convnn_b200.make_args(**WORKLOAD, device=dev)
@@ -360,6 +586,7 @@ def run_ours(args) -> int:
     model.load_state_dict(make_vit_weights(cfg, seed=1), strict=True)
     model = model.to(dev, torch.bfloat16)
     B = BATCH_PER_GPU
+    classes = WORKLOAD["num_classes"]
     g = torch.Generator(device="cpu").manual_seed(100 + rank)
     NBUF = 3   # 3 x 77 MB of distinct resident inputs > 126 MB L2
     host = [torch.randn(B, 3, 224, 224, generator=g).to(torch.bfloat16).pin_memory() for _ in range(NBUF)]
@@ -367,37 +594,18 @@ def run_ours(args) -> int:
     static_in = torch.empty_like(resident[0])
     total = B * world
 
-    def step_eager(x):
-        logits = model(x)
-        return gather_logits(logits, total) if world > 1 else logits
-
     # CUDA graph of the whole forward (ctypes launches on the capturing stream are captured)
-    graph, static_out, graph_note, per_forward = None, None, "eager", 0
     with torch.no_grad():
-        for _ in range(2):
-            static_in.copy_(resident[0])
-            model(static_in)
-        torch.cuda.synchronize()
-        if not args.no_graph:
-            try:
-                n_cap = lib.convnn_b200_launch_count()
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph):
-                    static_out = model(static_in)
-                per_forward = lib.convnn_b200_launch_count() - n_cap
-                graph_note = "cuda_graph"
-            except Exception as e:  # noqa: BLE001
-                graph, graph_note = None, f"eager (graph capture failed: {type(e).__name__})"
-                torch.cuda.synchronize()
+        static_in.copy_(resident[0])
+        n_cap = lib.convnn_b200_launch_count()
+        graph, static_out = graph_model(model, static_in)
+        per_forward = (lib.convnn_b200_launch_count() - n_cap) // 3      # two eager calls + the capture
+    gather = LogitsGather(world, B, classes, torch.bfloat16, dev)
 
-    def step(x):
-        if graph is not None:
-            static_in.copy_(x, non_blocking=True)
-            graph.replay()
-            logits = static_out
-        else:
-            logits = model(x)
-        return gather_logits(logits, total) if world > 1 else logits
+    def batch_step(x):
+        static_in.copy_(x, non_blocking=True)
+        graph.replay()
+        return gather(static_out)
 
     def barrier():
         if world > 1:
@@ -406,59 +614,104 @@ def run_ours(args) -> int:
 
     with torch.no_grad():
         # ---- device-resident timing -------------------------------------------------------
-        for i in range(args.warmup):
-            step(resident[i % NBUF])
+        n = 0
+        for _ in range(args.warmup):
+            for _ in range(inner):
+                batch_step(resident[n % NBUF])
+                n += 1
+        gather.drain()
         barrier()
         sampler = ClockSampler(local) if rank == 0 else None
-        n0 = lib.convnn_b200_launch_count()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for i in range(args.steps):
-            step(resident[i % NBUF])
+        for _ in range(args.steps):
+            for _ in range(inner):
+                batch_step(resident[n % NBUF])
+                n += 1
+        gather.drain()
         e1.record()
         barrier()
         ms = e0.elapsed_time(e1)
-        launches_eager = lib.convnn_b200_launch_count() - n0
         clocks = sampler.stop() if sampler else None
 
         # ---- end to end: pinned host images in, logits out ------------------------------------
         copy_stream = torch.cuda.Stream(dev)
+        d2h_stream = torch.cuda.Stream(dev)
         staging = [torch.empty_like(resident[0]) for _ in range(2)]
-        out_host = torch.empty(total if world > 1 else B, WORKLOAD["num_classes"], dtype=torch.bfloat16).pin_memory()
+        out_host = torch.empty(total, classes, dtype=torch.bfloat16).pin_memory()
         ready = [torch.cuda.Event() for _ in range(2)]
         freed = [torch.cuda.Event() for _ in range(2)]
 
-        def e2e_run(n):
+        def e2e_run(n_batches):
             cur = torch.cuda.current_stream()
             for f in freed:
                 f.record(cur)
-            for i in range(n):
+            for i in range(n_batches):
                 s = i % 2
                 with torch.cuda.stream(copy_stream):
                     copy_stream.wait_event(freed[s])
                     staging[s].copy_(host[i % NBUF], non_blocking=True)
                     ready[s].record(copy_stream)
                 cur.wait_event(ready[s])
-                logits = step(staging[s])
+                logits, done = batch_step(staging[s])
                 freed[s].record(cur)
-                out_host.copy_(logits, non_blocking=True)
+                if done is not None:
+                    # read the gathered logits back on a stream of their own once the side stream has
+                    # them (behind the input copies they would hold up the next batch)
+                    with torch.cuda.stream(d2h_stream):
+                        d2h_stream.wait_event(done)
+                        out_host.copy_(logits, non_blocking=True)
+                else:
+                    out_host.copy_(logits, non_blocking=True)
+            gather.drain()
+            cur.wait_stream(copy_stream)
+            cur.wait_stream(d2h_stream)
 
         e2e_run(max(2, args.warmup))
         barrier()
         f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         f0.record()
-        e2e_run(args.steps)
+        e2e_run(args.steps * inner)
         f1.record()
         barrier()
         ms_e2e = f0.elapsed_time(f1)
 
+        # ---- strong scaling: the 256-image batch of the baseline split over the ranks ----------
+        ms_strong = 0.0
+        if world > 1:
+            Bs = BATCH_PER_GPU // world
+            xs = [r[:Bs].contiguous() for r in resident]
+            s_in = torch.empty_like(xs[0])
+            s_in.copy_(xs[0])
+            s_graph, s_out = graph_model(model, s_in)
+            s_gather = LogitsGather(world, Bs, classes, torch.bfloat16, dev)
+
+            def strong_step(i):
+                s_in.copy_(xs[i % NBUF], non_blocking=True)
+                s_graph.replay()
+                s_gather(s_out)
+            for i in range(10):
+                strong_step(i)
+            s_gather.drain()
+            barrier()
+            n_strong = max(50, args.steps * inner)
+            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            g0.record()
+            for i in range(n_strong):
+                strong_step(i)
+            s_gather.drain()
+            g1.record()
+            barrier()
+            ms_strong = g0.elapsed_time(g1) / n_strong
+            del s_graph
+
         # ---- per-stage device time for the roofline ----------------------------------------
         stage_ms = stage_profile(model, B, cfg, dev)
 
-    t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
+    t = torch.tensor([ms, ms_e2e, ms_strong], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, ms_e2e = float(t[0]), float(t[1])
+    ms, ms_e2e, ms_strong = float(t[0]), float(t[1]), float(t[2])
 
     if rank == 0:
         pk = peaks()
@@ -473,33 +726,46 @@ def run_ours(args) -> int:
         else:
             bound, ach, peak, unit = "hbm", work[dom]["bytes"] / per_launch_ms / 1e6, pk["hbm"], "GB/s"
         stages = {k: {"ms_per_launch": stage_ms[k], "GBps": work[k]["bytes"] / stage_ms[k] / 1e6,
-                      "TFLOPs": work[k]["flops"] / stage_ms[k] / 1e9} for k in stage_ms}
-        cpu_v, cpu_per, cores, cpu_done = (None, None, None, 0)
+                      "TFLOPs": work[k]["flops"] / stage_ms[k] / 1e9,
+                      "frac_of_hbm_peak": work[k]["bytes"] / stage_ms[k] / 1e6 / pk["hbm"]} for k in stage_ms}
         cpu = None
         if world == 1 and not args.no_cpu:
             torch.set_num_threads(max(1, os.cpu_count() or 1))
-            cpu_v, cpu_per, cores, cpu_done = cpu_model_throughput(32, 8, 1, budget_s=20.0)
-            cpu = {"value": cpu_v, "unit": UNIT, "cores": cores, "kind": "port",
-                   "sample": f"{cpu_done} forwards of 32 images (of the 256-image batch), fp32, torch CPU oracle"}
+            cpu_v, cpu_per, cores, cpu_done, kind = cpu_model_throughput(32, 8, 1, budget_s=20.0)
+            cpu = {"value": cpu_v, "unit": UNIT, "cores": cores, "kind": kind,
+                   "sample": f"{cpu_done} forwards of 32 images (of the 256-image batch), fp32, torch CPU, "
+                             + ("the reference's own vit.ViT" if kind == "reference" else "oracle port")}
+        n_batches = args.steps * inner
         h2d = B * 3 * 224 * 224 * 2
         d2h = out_host.numel() * 2
         line = {
-            "metric": METRIC, "value": total * args.steps / (ms / 1e3), "unit": UNIT, "n_gpus": world,
+            "metric": METRIC, "value": total * n_batches / (ms / 1e3), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD_NAME,
-                       "batch_per_gpu": B, "global_batch": total, "parallelism": f"batch-shard x{world}",
-                       "l2": f"{NBUF} distinct resident input batches (231 MB) rotate, larger than L2",
-                       "launch": graph_note, "host_numa_bound": bool(numa_bound)},
-            "e2e": {"value": total * args.steps / (ms_e2e / 1e3), "unit": UNIT, "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / args.steps},
-            "gpu_launches": int(launches_eager) if graph is None else int(per_forward * args.steps),
+            "config": config_record(world, inner),
+            "ms_per_batch": ms / n_batches, "host_numa_bound": bool(numa_bound),
+            "e2e": {"value": total * n_batches / (ms_e2e / 1e3), "unit": UNIT, "h2d_bytes_per_step": h2d * inner,
+                    "d2h_bytes_per_step": d2h * inner, "ms_per_step": ms_e2e / args.steps,
+                    "host_images": "bfloat16, pinned (float32 host images would double the copy)",
+                    "h2d_GBps_per_rank": h2d * n_batches / (ms_e2e / 1e3) / 1e9},
+            "gpu_launches": int(per_forward * n_batches),
             "roofline": {"bound": bound, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak,
                          "traffic": NCU_TRAFFIC_BYTES.get(dom), "kernel": dom, "peak_source": pk["source"],
                          "ms_per_launch": per_launch_ms, "stages": stages},
             "cpu_baseline": cpu,
             "clocks": clocks,
         }
+        if world > 1:
+            line["strong"] = {"global_batch": BATCH_PER_GPU, "batch_per_gpu": BATCH_PER_GPU // world,
+                              "images_per_s": BATCH_PER_GPU / (ms_strong / 1e3), "ms_per_batch": ms_strong,
+                              "note": "the baseline's 256-image batch split over the ranks, device-resident, "
+                                      "max over ranks; `value` stays the weak-scaling figure"}
+        if world == 1 and not args.no_extras:
+            with torch.no_grad():
+                del graph
+                torch.cuda.empty_cache()
+                line["configs"] = other_configs(dev)
+                line["layer_sweep"] = layer_sweep(dev, [4096, 16384])
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -509,10 +775,12 @@ def run_ours(args) -> int:
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--inner-iters", type=int, default=0,
+                    help="batches per step (default: chosen so that the timed region lasts about a second)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the cfg-3 / cfg-4 models and the layer sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--stage", choices=["qkv_proj", "sim_topk", "gather_conv", "out_proj", "out_proj_skip", "mlp0",
                                         "mlp3", "layernorm"],
@@ -528,6 +796,8 @@ def main() -> int:
     if args.layer_sweep:
         return run_layer_sweep(args)
     args.warmup = max(args.warmup, 3)
+    if args.inner_iters <= 0:
+        args.inner_iters = inner_iters_for(args.steps)
     if args.impl == "reference":
         return run_reference_arm(args)
     return run_ours(args)

@@ -35,7 +35,7 @@ SIGNATURES = {
     "convnn_b200_last_error": (ctypes.c_char_p, []),
     "convnn_b200_launch_count": (ctypes.c_uint64, []),
     "convnn_b200_device_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_int)]),
-    "convnn_b200_debug_gemm_trace": (ctypes.c_int, [ctypes.c_int, ctypes.POINTER(ctypes.c_uint64), ctypes.c_int]),
+    "convnn_b200_selftest_wait_timeout": (ctypes.c_int, [ctypes.c_uint32, c_void, c_void, c_void]),
     "convnn_b200_head_channels": (ctypes.c_int, [ctypes.POINTER(ConvnnDesc)]),
     "convnn_b200_workspace_bytes": (c_size, [ctypes.POINTER(ConvnnDesc)]),
     "convnn_b200_stage_scratch_bytes": (c_size, [ctypes.POINTER(ConvnnDesc)]),

@@ -124,6 +124,9 @@ Workspace carve(const Dims& dm, int conv_type, void* base) {
 }
 
 }  // namespace
+
+int check_device_is_sm100() { return check_device(); }
+
 }  // namespace convnn
 
 using namespace convnn;
@@ -164,10 +167,6 @@ int convnn_b200_device_status(int* code) {
     if (!c && (rc = read_dw_stream_status(&c))) return rc;
     *code = a ? a : (b ? b : c);
     return CONVNN_OK;
-}
-
-int convnn_b200_debug_gemm_trace(int enable, uint64_t* host_out, int n) {
-    return gemm_tc_trace(enable, reinterpret_cast<unsigned long long*>(host_out), n);
 }
 
 uint64_t convnn_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }

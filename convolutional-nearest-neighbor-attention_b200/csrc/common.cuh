@@ -99,7 +99,6 @@ int try_launch_gather_conv_dw_stream(const convnn_desc* d, const Dims& dm, const
                                      const float* val, const void* w_conv, void* o, cudaStream_t st);
 int read_dw_stream_status(int* out);
 int read_gemm_tc_status(int* out);
-int gemm_tc_trace(int enable, unsigned long long* host_out, int n);
 // bfloat16 tensor-core GEMM C = A W^T (+bias, +GELU); `parts` outputs share M and split N evenly.
 bool gemm_tc_supported(const void* a, long long lda, const void* w, int Kd, int N, int parts, const void* const* c,
                        long long ldc);

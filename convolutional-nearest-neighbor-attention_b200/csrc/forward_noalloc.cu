@@ -12,7 +12,9 @@
 namespace convnn {
 namespace {
 
-// Every GPU that loads the library holds this array from module load until process exit.
+// The array belongs to this translation unit's CUDA module.  The runtime loads modules lazily by
+// default, so a GPU reserves these bytes when the module is first touched on it -- by the address
+// lookup below -- and keeps them until the process exits.
 constexpr size_t kStaticWorkspaceBytes = 32u << 20;
 static __device__ __align__(256) unsigned char g_static_workspace[kStaticWorkspaceBytes];
 
@@ -43,11 +45,23 @@ int static_workspace(void** out) {
 }
 
 }  // namespace
+
+// capi.cu: the current device must be an sm_100 part (cached per device).
+int check_device_is_sm100();
 }  // namespace convnn
 
 extern "C" {
 
-size_t convnn_b200_noalloc_capacity(void) { return convnn::kStaticWorkspaceBytes; }
+// Also the warm-up: resolving the address here, at start-up, is what makes the GPU reserve the
+// array, so that no later forward has to (see the header).  The capacity is returned whether or
+// not the lookup worked; a failed lookup is reported by the first forward.
+size_t convnn_b200_noalloc_capacity(void) {
+    if (convnn::check_device_is_sm100() == CONVNN_OK) {
+        void* ws = nullptr;
+        (void)convnn::static_workspace(&ws);
+    }
+    return convnn::kStaticWorkspaceBytes;
+}
 
 int convnn_b200_forward_noalloc(const convnn_desc* d, const void* x, int64_t ldx, const void* w_qkv,
                                 const void* w_conv, const void* w_pw, const void* w_o, const int32_t* cand,
@@ -60,7 +74,9 @@ int convnn_b200_forward_noalloc(const convnn_desc* d, const void* x, int64_t ldx
                                  "workspace holds %zu; use convnn_b200_forward with a caller-provided workspace",
                                  need, convnn::kStaticWorkspaceBytes);
     void* ws = nullptr;
-    const int rc = convnn::static_workspace(&ws);
+    int rc = convnn::check_device_is_sm100();         // a foreign GPU is a device error, not a CUDA error
+    if (rc) return rc;
+    rc = convnn::static_workspace(&ws);
     if (rc) return rc;
     return convnn_b200_forward(d, x, ldx, w_qkv, w_conv, w_pw, w_o, cand, residual, ldr, out, ldo, ws,
                                convnn::kStaticWorkspaceBytes, stream);

@@ -29,10 +29,13 @@ namespace convnn {
 
 __device__ int g_gemm_tc_status = 0;   // error latch of this translation unit
 
-// Pipeline trace (diagnostic): when enabled, CTA 0 records SM clock stamps of its producer,
-// MMA and epilogue events; four regions of 512 slots (producer, MMA, epilogue half 0 / 1).
+// Pipeline trace (a development aid, compiled in only with -DCONVNN_B200_GEMM_TRACE): when
+// enabled, CTA 0 records SM clock stamps of its producer, MMA and epilogue events; four regions
+// of 512 slots (producer, MMA, epilogue half 0 / 1).
+#ifdef CONVNN_B200_GEMM_TRACE
 __device__ int g_gemm_trace_on = 0;
 __device__ unsigned long long g_gemm_trace[4 * 512];
+#endif
 
 namespace {
 
@@ -74,9 +77,15 @@ __device__ __forceinline__ void fail_pair(volatile int* abort_flag, uint32_t pee
     fail(abort_flag, code);
 }
 
+#ifdef CONVNN_B200_GEMM_TRACE
+__device__ __forceinline__ bool trace_enabled() { return g_gemm_trace_on != 0; }
 __device__ __forceinline__ void trace(bool on, int region, int& n) {
     if (on && n < 512) g_gemm_trace[region * 512 + n++] = clock64();
 }
+#else
+__device__ __forceinline__ bool trace_enabled() { return false; }
+__device__ __forceinline__ void trace(bool, int, int&) {}
+#endif
 
 // GELU for the bfloat16 epilogue.  nn.GELU()'s default is the erf form; here the tanh form
 // 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))) is evaluated with the hardware tanh unit.
@@ -252,7 +261,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             bool any = false;
             int cur_nt = -1;
             bool ok = true;
-            const bool tr = !PAIR && g_gemm_trace_on && blockIdx.x == 0;
+            const bool tr = !PAIR && trace_enabled() && blockIdx.x == 0;
             int tn = 0;
             trace(tr, 0, tn);
             const uint32_t tx = (a_bytes + (p.wstat ? 0u : b_bytes)) * (PAIR ? 2u : 1u);
@@ -301,7 +310,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             uint32_t s = 0, ph = 0, tile = 0, wloads = 0;
             int cur_nt = -1;
             bool ok = true;
-            const bool tr = !PAIR && g_gemm_trace_on && blockIdx.x == 0;
+            const bool tr = !PAIR && trace_enabled() && blockIdx.x == 0;
             int tn = 0;
             const uint32_t peer_empty0 = PAIR ? map_to_cta(empty0, 1) : 0u;
             const uint32_t peer_tfull0 = PAIR ? map_to_cta(tfull0, 1) : 0u;
@@ -368,7 +377,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         uint32_t tile = half;
         bool ok = true;
-        const bool tr = !PAIR && g_gemm_trace_on && blockIdx.x == 0 && lq == 0 && lane == 0 && chalf == 0;
+        const bool tr = !PAIR && trace_enabled() && blockIdx.x == 0 && lq == 0 && lane == 0 && chalf == 0;
         const uint32_t lead_tempty0 = PAIR ? map_to_cta(smem_u32(tempty), 0) : 0u;
         int tn = 0;
         for (int t = first + half * step; t < last && ok; t += 2 * step, tile += 2) {
@@ -772,7 +781,10 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
     return CONVNN_OK;
 }
 
-int gemm_tc_trace(int enable, unsigned long long* host_out, int n) {
+#ifdef CONVNN_B200_GEMM_TRACE
+// Copies up to 2048 recorded clock stamps to `host_out` (host memory), clears the trace and
+// switches recording on or off.  Synchronises the device.
+extern "C" int convnn_b200_debug_gemm_trace(int enable, unsigned long long* host_out, int n) {
     cudaError_t e = cudaSuccess;
     if (host_out && n > 0) {
         if (n > 4 * 512) n = 4 * 512;
@@ -785,6 +797,7 @@ int gemm_tc_trace(int enable, unsigned long long* host_out, int n) {
     if (e != cudaSuccess) return set_error(CONVNN_E_CUDA, "cudaMemcpyToSymbol: %s", cudaGetErrorString(e));
     return CONVNN_OK;
 }
+#endif
 
 int read_gemm_tc_status(int* out) {
     int v = 0;

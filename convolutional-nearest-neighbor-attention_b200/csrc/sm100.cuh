@@ -42,13 +42,29 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after `limit` polls or as soon as *abort becomes non-zero, and
-// reports failure so the caller can record an error and leave instead of hanging the GPU.
-constexpr uint32_t kWaitLimit = 1u << 24;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
-    for (uint32_t i = 0; i < kWaitLimit; ++i) {
+// Bounded wait: gives up once `budget_ns` of wall time (the GPU's nanosecond timer) have passed
+// or as soon as *abort becomes non-zero, and reports failure so the caller can record an error
+// and leave instead of hanging the GPU.  The timer is read once per 256 polls; an extra poll
+// counter backs it up should the timer not advance.  In normal operation no wait of these
+// kernels lasts longer than the epilogue of one tile (tens of microseconds); the budget only has
+// to exceed that under time slicing or a profiler's replay.
+constexpr unsigned long long kWaitBudgetNs = 250ull * 1000 * 1000;
+constexpr uint32_t kWaitPollLimit = 1u << 28;
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort,
+                                          unsigned long long budget_ns = kWaitBudgetNs) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_timer_ns();
+    for (uint32_t i = 0; i < kWaitPollLimit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 1023u) == 1023u && *abort) return false;
+        if ((i & 255u) == 255u) {
+            if (*abort) return false;
+            if (global_timer_ns() - t0 > budget_ns) return false;
+        }
     }
     return false;
 }
@@ -68,9 +84,13 @@ __device__ __forceinline__ bool mbar_try_wait_a(uint32_t bar, uint32_t parity) {
 }
 __device__ __forceinline__ bool mbar_wait_a(uint32_t bar, uint32_t parity, volatile int* abort) {
     if (mbar_try_wait_a(bar, parity)) return true;          // common case: already complete
-    for (uint32_t i = 0; i < kWaitLimit; ++i) {
+    const unsigned long long t0 = global_timer_ns();
+    for (uint32_t i = 0; i < kWaitPollLimit; ++i) {
         if (mbar_try_wait_a(bar, parity)) return true;
-        if ((i & 1023u) == 1023u && *abort) return false;
+        if ((i & 255u) == 255u) {
+            if (*abort) return false;
+            if (global_timer_ns() - t0 > kWaitBudgetNs) return false;
+        }
     }
     return false;
 }

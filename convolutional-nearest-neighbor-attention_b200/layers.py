@@ -67,13 +67,25 @@ class MultiHeadConvNNAttention(nn.Module):
                 nn.Conv1d(C, dk, kernel_size=1, stride=1, padding=0, bias=False))
         # (any other string leaves the module without a conv, as in the reference)
 
-        self.candidate_override: Optional[torch.Tensor] = None   # fixes the sampled candidate set
+        self._candidate_override: Optional[torch.Tensor] = None
         self.stage_timer = None   # callable(label): records a CUDA event between the stage calls
         self._packed = None
         self._packed_key = None
         self._spatial_cache = {}
 
     # -- host-side helpers --------------------------------------------------------------
+    @property
+    def candidate_override(self) -> Optional[torch.Tensor]:
+        """Fixes the candidate set of the sampled modes (instead of a fresh draw per call)."""
+        return self._candidate_override
+
+    @candidate_override.setter
+    def candidate_override(self, cand: Optional[torch.Tensor]) -> None:
+        if cand is not None:
+            ops.check_candidates(cand)      # negatives here; the upper bound once T is known
+        self._candidate_override = cand
+        self._override_checked_T = None
+
     def _spec(self) -> LayerSpec:
         return LayerSpec(self.d_hidden, self.num_heads, self.K, self.sampling_type, self.magnitude_type,
                          self.convolution_type, self.softmax_topk_val, self.coordinate_encoding,
@@ -98,8 +110,11 @@ class MultiHeadConvNNAttention(nn.Module):
         (layers.py:284, 297) unless ``candidate_override`` is set."""
         if self.sampling_type == 'all':
             return None
-        if self.candidate_override is not None:
-            return self.candidate_override.to(device)
+        if self._candidate_override is not None:
+            if getattr(self, "_override_checked_T", None) != T:
+                ops.check_candidates(self._candidate_override, T)    # once per sequence length
+                self._override_checked_T = T
+            return self._candidate_override.to(device)
         if self.sampling_type == 'random':
             return torch.randperm(T, device=device)[:self.num_samples]
         if self.sampling_type == 'spatial':

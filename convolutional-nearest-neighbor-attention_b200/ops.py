@@ -92,11 +92,28 @@ def pack_weights(spec: LayerSpec, w_q, w_k, w_v, w_o, conv_weights, dtype, devic
     return w_qkv, w_conv, w_pw, cvt(w_o)
 
 
+def check_candidates(cand: torch.Tensor, T: Optional[int] = None) -> torch.Tensor:
+    """Range check of caller-supplied candidate token indices: the kernels use them as row
+    numbers without looking, so a value outside [0, T) must be stopped on the host.  Raises
+    IndexError as the reference's ``x[:, rand_idx, :]`` (layers.py:285) does.  Reads the
+    tensor (a device tensor is synchronised), so it runs where a candidate set is fixed, not
+    on every forward."""
+    if cand.numel() == 0:
+        raise IndexError("the candidate set is empty")
+    lo, hi = int(cand.min()), int(cand.max())
+    if lo < 0 or (T is not None and hi >= T):
+        bad = lo if lo < 0 else hi
+        raise IndexError(f"index {bad} is out of bounds for dimension 1 with size {T}")
+    return cand
+
+
 def _cand_arg(spec: LayerSpec, cand: Optional[torch.Tensor], T: int, device) -> Tuple[Optional[torch.Tensor], int]:
     if spec.sampling_type == "all":
         return None, T
     if cand is None:
         raise ValueError("sampled modes need candidate indices")
+    if not cand.is_cuda:
+        check_candidates(cand, T)          # host tensors are cheap to check on every call
     cand = cand.to(device=device, dtype=torch.int32).contiguous()
     return cand, int(cand.numel())
 

@@ -2,9 +2,12 @@
 
 Mirrors the reference model's module tree and ``state_dict`` keys (reference vit.py:22-270)
 so that a reference checkpoint loads with ``strict=True`` and whole-model throughput can be
-measured without the reference checkout.  Only the attention block runs in libconvnn_b200;
-patch embedding, LayerNorm, MLP and the classifier head are plain torch modules (they are
-the callers of the hot path, not part of it).
+measured without the reference checkout.  The ``nn.Module``s here only hold the parameters:
+on CUDA, in float32 or bfloat16 and without autograd, every operation of the forward (patch
+unfold and projection, LayerNorm, the attention block, both MLP layers with GELU and the skip
+connections, the classifier) runs in libconvnn_b200.  Any other call (CPU tensors, autograd,
+dropout in training mode) takes the modules' ordinary torch forward for the encoder shell and
+is refused by the ConvNN layers themselves.
 """
 from __future__ import annotations
 

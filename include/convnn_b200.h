@@ -7,10 +7,18 @@
  *
  * Conventions
  *   - Every pointer is a DEVICE pointer owned by the caller.  The library allocates
- *     nothing, frees nothing and keeps no pointer after the call returns.
+ *     nothing, frees nothing and keeps no caller pointer after the call returns.
  *   - All work is enqueued on `stream` (a cudaStream_t passed as void*); no call
- *     synchronises the host.  Calls are re-entrant; the only process-wide state is a
- *     launch counter.
+ *     synchronises the host, except convnn_b200_device_status().  The stage calls, the
+ *     workspace forward and the encoder ops are re-entrant: host threads may call them
+ *     at the same time on different streams with different buffers.
+ *   - Process-wide state, all of it: a launch counter; per-device flags remembering that
+ *     a device was checked to be sm_100; one device-side error latch per tensor-core
+ *     kernel family (read by convnn_b200_device_status(), never cleared, first code
+ *     wins); and, for convnn_b200_forward_noalloc() only, one fixed device array per GPU
+ *     with its cached address (those calls are NOT re-entrant on one device: see there).
+ *     cudaDeviceReset() invalidates the cached address and the latches' device copies;
+ *     a process that resets a device must not call the library on it afterwards.
  *   - Return value: CONVNN_OK or a negative convnn_status; a human-readable reason for
  *     the last failure on the calling thread is in convnn_b200_last_error().
  *   - `dtype` is the storage type of activations and weights (float32 or bfloat16);
@@ -95,15 +103,19 @@ uint64_t convnn_b200_launch_count(void);
 
 /* No reference counterpart: reads the device-side error latch (synchronises the device).
  * 0 = no kernel gave up; otherwise the code of the first bounded wait that expired inside
- * a tensor-core kernel (similarity: 1 producer, 2/3 MMA issuer, 4 epilogue; GEMM: 11-14).  Results of a call that
- * latched a code are undefined. */
+ * a tensor-core kernel (similarity: 1 producer, 2/3 MMA issuer, 4 epilogue; GEMM: 11-16; pair
+ * similarity: 21-26; streaming depthwise conv: 31).  A wait gives up after 250 ms.  Results of
+ * a call that latched a code are undefined. */
 int convnn_b200_device_status(int* code);
 
-/* No reference counterpart: pipeline trace of the tensor-core GEMM (diagnostic).  Copies up
- * to 2048 recorded SM clock stamps of CTA 0 to `host_out` (HOST memory; four regions of 512:
- * producer, MMA issuer, epilogue halves), clears the trace and sets recording on or off.
- * Synchronises the device. */
-int convnn_b200_debug_gemm_trace(int enable, uint64_t* host_out, int n);
+/* No reference counterpart: exercises the bounded wait every tensor-core kernel of this
+ * library uses, without any copy or MMA in flight.  One thread of a one-CTA kernel waits on a
+ * barrier that nothing ever completes, for at most `budget_us` microseconds (1 .. 100000),
+ * then writes 41 to *status_dev (0 if the wait had, impossibly, succeeded) and the time it
+ * waited, in nanoseconds, to *waited_ns_dev (both DEVICE pointers), and returns.  The kernel
+ * neither traps nor touches the error latch; the context stays usable. */
+int convnn_b200_selftest_wait_timeout(uint32_t budget_us, int* status_dev, uint64_t* waited_ns_dev,
+                                      void* stream);
 
 /* Channels per head as stored in q/k/v (Cp above). Negative status on a bad descriptor. */
 int convnn_b200_head_channels(const convnn_desc* d);
@@ -164,17 +176,24 @@ int convnn_b200_forward(const convnn_desc* d, const void* x, int64_t ldx, const 
  * The same forward as convnn_b200_forward for callers that cannot provide a workspace because
  * they must not allocate device memory where they call from: a serving loop in which
  * cudaMalloc would stall the device, a plugin whose host application owns the allocator, or
- * a GPU whose memory was handed out in full beforehand.  The intermediates
+ * a GPU whose memory is handed out in full once start-up is over.  The intermediates
  * live in a fixed array inside the library's device image: convnn_b200_noalloc_capacity()
- * bytes (32 MiB), held by every GPU that loads the library until the process exits.  The
- * call allocates and frees nothing.  A descriptor whose convnn_b200_workspace_bytes()
- * exceeds the capacity is refused with CONVNN_E_WORKSPACE.
- *   - The first call on each device looks the array's device address up (with that device
- *     current); make that first call outside any stream capture.
+ * bytes (32 MiB) per GPU.  A descriptor whose convnn_b200_workspace_bytes() exceeds the
+ * capacity is refused with CONVNN_E_WORKSPACE.
+ *   - The array is part of a CUDA module, and the CUDA runtime loads modules lazily by
+ *     default (CUDA_MODULE_LOADING=LAZY): the GPU reserves the 32 MiB when the module is
+ *     first touched, not when the shared library is loaded.  convnn_b200_noalloc_capacity()
+ *     touches it: it resolves (and caches) the array's device address for the CURRENT
+ *     device.  Call it once per device at start-up, with that device current, before
+ *     memory is handed out and outside any stream capture; from then on
+ *     convnn_b200_forward_noalloc() neither allocates nor frees anything and makes no
+ *     address lookup.  Without that warm-up the first forward on a device does the lookup
+ *     itself: it may then fail with CONVNN_E_CUDA on a GPU with no memory left, and must not
+ *     run inside a capture.  The array is held until the process exits.
  *   - All calls on a device share the one array and it keeps the previous call's contents.
  *     Every intermediate is written before it is read, so nothing has to be cleared, but two
- *     calls that overlap on the GPU (different streams, or graph branches) race on it: keep
- *     calls on one device stream-ordered. */
+ *     calls that overlap on the GPU (different streams, graph branches, host threads) race
+ *     on it: keep calls on one device stream-ordered. */
 size_t convnn_b200_noalloc_capacity(void);
 int convnn_b200_forward_noalloc(const convnn_desc* d, const void* x, int64_t ldx, const void* w_qkv,
                                 const void* w_conv, const void* w_pw, const void* w_o,

@@ -283,6 +283,22 @@ def near_tie_rows(sim: torch.Tensor, cfg: ConvNNConfig, sampled: bool, tol: floa
     return (gaps < tol * scale).any(dim=-1)
 
 
+def swap_possible_rows(sim: torch.Tensor, cfg: ConvNNConfig, sampled: bool, delta: torch.Tensor) -> torch.Tensor:
+    """Boolean (B, H, T): rows in which a perturbation of every similarity by at most
+    ``delta`` (per row, shape (B, H, T), absolute) can change the ordered top-n list.  If two
+    similarity matrices differ by at most delta on a row and their exact selections differ,
+    two columns have swapped order, so some adjacent gap among the top-(n+1) sorted values
+    of either matrix is at most 2*delta.  Used to check that every row on which a bfloat16
+    run and the oracle disagree is explained by the measured difference of their q / k."""
+    n = cfg.K - 1 if sampled else cfg.K
+    m = min(n + 1, sim.shape[-1])
+    if m < 2:
+        return torch.zeros(sim.shape[:-1], dtype=torch.bool)
+    top, _ = torch.topk(sim.double(), k=m, dim=-1, largest=cfg.maximum)
+    gaps = (top[..., 1:] - top[..., :-1]).abs()
+    return (gaps <= 2.0 * delta.double().unsqueeze(-1)).any(dim=-1)
+
+
 # --------------------------------------------------------------------------------------
 # Branching wrappers (ConvNN branch is the hot path; the other halves are plain torch)
 # --------------------------------------------------------------------------------------

@@ -157,3 +157,25 @@ def test_dropin_install_rebinds_reference_names():
         assert fake_vit.MultiHeadConvNNAttention is object
     finally:
         del sys.modules["layers"], sys.modules["vit"]
+
+
+def test_candidate_indices_are_range_checked_on_the_host():
+    """A candidate index outside [0, T) would become an out-of-bounds row number inside the
+    kernels; the reference raises IndexError on `x[:, rand_idx, :]` (layers.py:285), and so do
+    the places where a caller fixes the candidate set."""
+    from convnn_b200 import ops
+    ops.check_candidates(torch.tensor([0, 5, 64]), 65)
+    with pytest.raises(IndexError, match="out of bounds"):
+        ops.check_candidates(torch.tensor([0, 5, 65]), 65)
+    with pytest.raises(IndexError, match="out of bounds"):
+        ops.check_candidates(torch.tensor([-1, 5]), 65)
+    m = convnn_b200.MultiHeadConvNNAttention(48, 1, 0.0, 5, "random", 16, 0, "cosine")
+    with pytest.raises(IndexError):
+        m.candidate_override = torch.tensor([3, -2, 7])
+    m.candidate_override = torch.tensor([3, 70, 7])              # upper bound needs T
+    with pytest.raises(IndexError):
+        m.candidates(65, torch.device("cpu"))
+    assert torch.equal(m.candidates(71, torch.device("cpu")), torch.tensor([3, 70, 7]))
+    spec = ops.LayerSpec(48, 1, 5, "random")
+    with pytest.raises(IndexError):
+        ops._cand_arg(spec, torch.tensor([1, 99]), 65, torch.device("cpu"))

@@ -51,3 +51,28 @@ def test_reference_vit_constructs_our_layers_and_shares_checkpoints(reference_mo
     mirror.load_state_dict(stock.state_dict(), strict=True)          # our ViT mirror takes it too
     with torch.no_grad(), pytest.raises(RuntimeError, match="no CPU path"):
         ours(torch.randn(1, 3, 224, 224))
+
+
+@pytest.mark.gpu
+def test_reference_vit_runs_our_layers_on_the_gpu(reference_modules):
+    """install() + the reference's own vit.ViT, built and run on CUDA exactly as main.py builds
+    it (vit.py:189-197 constructs the layer, vit.py:263 calls it): the logits must equal the
+    stored outputs of the unmodified reference."""
+    import types
+    from golden_util import vit_case
+    ref_layers, ref_vit = reference_modules
+    cfg, sd, img, want = vit_case("vit_tiny_cifar_convnn")
+    args = {f: getattr(cfg, f) for f in cfg.__dataclass_fields__}
+    args.update(device="cuda", img_size=tuple(cfg.img_size))
+    convnn_b200.install(ref_layers, ref_vit)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    model = ref_vit.ViT(types.SimpleNamespace(**args)).eval()
+    assert type(model.transformer_encoder[0].attention).__module__.startswith(
+        "convolutional-nearest-neighbor-attention_b200")
+    model.load_state_dict(sd, strict=True)
+    with torch.no_grad():
+        got = model(img.to("cuda")).float().cpu()
+    err = float((got.double() - want.double()).norm() / want.double().norm())
+    assert err < 2e-3, err
+    assert torch.equal(got.argmax(-1), want.argmax(-1))

@@ -12,7 +12,7 @@ import torch
 from convnn_b200 import ops
 from oracle.convnn_oracle import (ConvNNConfig, bf16_round, convnn_attention, from_neighbours, make_input,
                                   make_layer_weights, near_tie_rows, neighbour_conv, neighbour_weights,
-                                  select_neighbours, similarity)
+                                  select_neighbours, similarity, swap_possible_rows)
 from golden_util import LAYER_NAMES, layer_case
 from gpu_util import DEV, heads_to_oracle, module_of, pack, rel_err, spec_of
 
@@ -94,6 +94,11 @@ BASELINE_SHAPES = {
                               convolution_type="depthwise-separable")),
     "d768_cosine_short": (2, 197, dict(d_hidden=768, num_heads=1, K=9, magnitude_type="cosine")),
     "long_pair": (1, 1536, dict(d_hidden=128, num_heads=1, K=9, magnitude_type="cosine", seq_length=1536)),
+    # the long-sequence sweep's own shape: 4096 tokens of 768 channels through all four stages (the
+    # CTA-pair similarity kernel with 12 channel chunks per tile over a 5-stage ring)
+    "cfg5_n4096_all": (1, 4096, dict(d_hidden=768, num_heads=1, K=9, magnitude_type="cosine", seq_length=4096)),
+    "cfg5_n4096_spatial_k25": (1, 4096, dict(d_hidden=768, num_heads=1, K=25, magnitude_type="cosine",
+                                             sampling_type="spatial", num_samples=1024, seq_length=4096)),
 }
 
 
@@ -106,6 +111,28 @@ def _named_case(name):
             cand = torch.randperm(T, generator=torch.Generator().manual_seed(17))[: cfg.num_samples]
         return cfg, make_layer_weights(cfg, seed=7), make_input(B, T, cfg.d_hidden, seed=11), None, cand
     return layer_case(name)
+
+
+def rows_explained_by_rounding(sim_kernel, sim_oracle, idx_kernel, cfg, cand):
+    """Rows (B, H, T) on which the kernel's exact selection over ITS similarities may differ from
+    the oracle's exact selection over the oracle's.  Both lists are the best of the column set
+    U = (oracle's top n+1) + (kernel's picks); if they differ, two columns of U have swapped
+    order although their similarities moved by at most delta = max over U of |sim_kernel -
+    sim_oracle|, so an adjacent gap of the oracle's top-(n+1) values is at most 2 delta.
+    Returns (mask, delta)."""
+    sampled = cand is not None
+    n = cfg.K - 1 if sampled else cfg.K
+    m = min(n + 1, sim_oracle.shape[-1])
+    top_cols = torch.topk(sim_oracle, k=m, dim=-1, largest=cfg.maximum).indices
+    if sampled:
+        inv = torch.full((sim_oracle.shape[-2],), 0, dtype=torch.long)
+        inv[cand] = torch.arange(cand.numel())
+        picked = inv[idx_kernel[..., 1:]]
+    else:
+        picked = idx_kernel
+    cols = torch.cat([top_cols, picked], dim=-1)
+    delta = (sim_kernel - sim_oracle).abs().gather(-1, cols).amax(-1) + 1e-6
+    return swap_possible_rows(sim_oracle, cfg, sampled, delta), delta
 
 
 @pytest.mark.parametrize("name", LAYER_NAMES + sorted(BASELINE_SHAPES))
@@ -135,10 +162,21 @@ def test_bf16_stages_against_oracle(name):
     p = neighbour_weights(val.cpu(), cfg)
     assert rel_err(o, neighbour_conv(vo, idx.cpu().long(), p, w, cfg)) < BF16_OUT
     assert rel_err(out, from_neighbours(vo, idx.cpu(), val.cpu(), w, cfg)) < BF16_OUT
-    # end to end against the oracle with the same rounding policy, on rows that chose the
-    # same neighbours (a one-step rounding difference in q or k can flip a close call)
+    # End to end against the oracle with the same rounding policy.  q and k of the two runs differ
+    # where an fp32 sum rounded the other way (one bfloat16 step, checked above), which moves the
+    # similarities a row's decision depends on by at most delta; every row whose ordered list
+    # differs from the oracle's must be explained by that (see rows_explained_by_rounding).
     agree = (idx.cpu().long() == tr.idx).all(-1)
-    assert float(agree.float().mean()) > 0.85
+    explained, delta = rows_explained_by_rounding(sim, tr.sim, idx.cpu().long(), cfg, tr.cand)
+    assert bool((agree | explained).all()), \
+        f"{int((~(agree | explained)).sum())} rows differ from the oracle beyond what the q/k rounding explains"
+    print(f"[{name}] rows agreeing with the bf16-policy oracle: {float(agree.float().mean()):.4f}; "
+          f"delta median {float(delta.median()):.2e} max {float(delta.max()):.2e}")
+    # (with thousands of candidates per row the top values crowd together and more rows sit within
+    # 2 delta of a swap; the fraction is reported, the bound above is what must hold)
+    assert float(agree.float().mean()) > (0.85 if x.shape[1] <= 2048 else 0.2)
+    # per-head conv output on the agreeing rows (valid for every H: the head merge mixes rows)
+    assert rel_err(o.float().cpu()[agree], tr.o[agree]) < BF16_OUT
     if cfg.num_heads == 1:
         rows = agree[:, 0]
         assert rel_err(out.float().cpu()[rows], tr.out[rows]) < BF16_OUT

@@ -29,6 +29,11 @@ CASES = [
     (1, 1100, 1100, 64, 1, 25, "cosine", "all"),      # long lists on short sequences stay on the single-CTA kernel
     (1, 8200, 4100, 64, 1, 25, "cosine", "spatial"),  # ... and move to the pair kernel on long ones
     (1, 8192, 4096, 64, 1, 32, "euclidean", "random"),
+    # the pair kernel at the channel count of the long-sequence sweep: d_k = 768 is 12 chunks per
+    # tile wrapping around the 5-stage (4-stage for lists longer than 24) shared-memory ring
+    (1, 2048, 2048, 768, 1, 9, "cosine", "all"),
+    (1, 4096, 1024, 768, 1, 9, "cosine", "spatial"),
+    (1, 8192, 4096, 768, 1, 25, "cosine", "spatial"),
 ]
 
 
@@ -58,9 +63,57 @@ def test_tensor_core_topk_matches_oracle(B, T, S, D, H, K, metric, sampling):
     ties = near_tie_rows(sim, cfg, cand is not None, 2e-6)
     same = (idx.cpu().long() == idx_want).all(-1)
     assert bool((same | ties).all()), f"{int((~(same | ties)).sum())} rows differ without a near-tie"
-    assert float(ties.float().mean()) < 0.05
+    assert float(ties.float().mean()) < 0.08    # (25 gaps per row among thousands of candidates: ~5 % at 2e-6)
     dv = (val.cpu().double() - val_want).abs() / val_want.abs().clamp_min(1.0)
     assert float(dv[same].max()) < 1e-5
+
+
+@pytest.mark.parametrize("S,K,sampling", [(16384, 9, "all"), (4096, 25, "spatial")])
+def test_pair_kernel_at_16384_tokens_against_float64_rows(S, K, sampling):
+    """The largest shape of the long-sequence sweep (16384 tokens of 768 channels): the whole
+    launch runs, and a seeded sample of 256 key rows is compared with a float64 similarity over
+    all candidates (the full 16384 x 16384 matrix is never formed, here or in the kernel)."""
+    T, D, n_rows = 16384, 768, 256
+    g = torch.Generator().manual_seed(S + K)
+    q = torch.randn(1, S, 1, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(1, T, 1, D, generator=g).to(torch.bfloat16)
+    cand = None if sampling == "all" else torch.linspace(0, T - 1, S).long()
+    cfg = ConvNNConfig(d_hidden=D, num_heads=1, K=K, sampling_type=sampling, num_samples=S, magnitude_type="cosine",
+                       seq_length=T)
+    qo, ko = q.float().permute(0, 2, 1, 3), k.float().permute(0, 2, 1, 3)
+    qstat, kstat = 1.0 / qo.norm(dim=-1).clamp_min(1e-12), 1.0 / ko.norm(dim=-1).clamp_min(1e-12)
+    idx, val = ops.sim_topk(spec_of(cfg), q.to(DEV), k.to(DEV), qstat.contiguous().to(DEV), kstat.contiguous().to(DEV),
+                            None if cand is None else cand.to(DEV))
+    torch.cuda.synchronize()
+    assert _capi.device_status() == 0
+    idx, val = idx.cpu().long(), val.cpu().double()
+    # properties of every row
+    n = K if cand is None else K - 1
+    own = 0 if cand is None else 1
+    assert int(idx.min()) >= 0 and int(idx.max()) < T
+    assert bool((val[..., own:-1] >= val[..., own + 1:]).all()), "values not sorted best first"
+    srt = idx[..., own:].sort(-1).values
+    assert bool((srt[..., 1:] != srt[..., :-1]).all()), "duplicate neighbour in a row"
+    # float64 check of the sampled rows
+    rows = torch.randperm(T, generator=g)[:n_rows].sort().values
+    kd = ko[0, 0, rows].double()
+    qd = qo[0, 0].double()
+    sim = (kd / kd.norm(dim=-1, keepdim=True)) @ (qd / qd.norm(dim=-1, keepdim=True)).t()     # (n_rows, S)
+    if cand is not None:
+        own_col = (cand.view(1, -1) == rows.view(-1, 1))
+        sim = torch.where(own_col, torch.full_like(sim, -0.1), sim)
+    top, cols = torch.topk(sim, n + 1, dim=-1)
+    want = cols[:, :n] if cand is None else cand[cols[:, :n]]
+    gaps = (top[:, :-1] - top[:, 1:]).abs()
+    ties = (gaps < 2e-6).any(-1)
+    got = idx[0, 0, rows][:, own:]
+    same = (got == want).all(-1)
+    assert bool((same | ties).all()), f"{int((~(same | ties)).sum())} of {n_rows} rows differ without a near-tie"
+    assert float(ties.float().mean()) < 0.1
+    dv = (val[0, 0, rows][:, own:] - top[:, :n]).abs()
+    assert float(dv[same].max()) < 1e-5
+    if cand is not None:
+        assert bool((idx[0, 0, :, 0] == torch.arange(T)).all()) and bool((val[0, 0, :, 0] == 1.0).all())
 
 
 def test_tensor_core_and_simt_kernels_agree_bitwise_on_indices():

@@ -45,6 +45,33 @@ def test_noalloc_forward_matches_workspace_forward_twice(dtype):
     assert _capi.device_status() == 0
 
 
+def test_noalloc_forward_takes_no_device_memory_after_warm_up():
+    """The built-in array is reserved when its CUDA module is first touched on a device, which
+    convnn_b200_noalloc_capacity() does (the start-up warm-up the header asks for).  After that
+    a forward must leave the device's free memory exactly as it found it."""
+    L = _capi.lib()
+    assert L.convnn_b200_noalloc_capacity() == 32 << 20           # warm-up: resolves the address
+    cfg = ConvNNConfig(d_hidden=192, num_heads=1, K=9, magnitude_type="cosine")
+    spec, packed = spec_of(cfg), pack(cfg, make_layer_weights(cfg, seed=5), torch.bfloat16)
+    w_qkv, w_conv, w_pw, w_o = packed
+    x = make_input(8, 197, 192, seed=1).to(DEV, torch.bfloat16)
+    out = torch.empty_like(x)
+    d = ops.descriptor(spec, 8, 197, 197, x.dtype)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def call():
+        return L.convnn_b200_forward_noalloc(d, x.data_ptr(), 192, w_qkv.data_ptr(), w_conv.data_ptr(), None,
+                                             w_o.data_ptr(), None, None, 0, out.data_ptr(), 192, stream)
+    _capi.check(call())                                           # kernels loaded, attributes set
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    _capi.check(call())
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    assert torch.equal(out, ops.forward(spec, x, packed))
+
+
 def test_noalloc_forward_sampled_mode_and_heads():
     cfg = ConvNNConfig(d_hidden=96, num_heads=3, K=9, magnitude_type="euclidean", sampling_type="spatial",
                        num_samples=49, convolution_type="depthwise-separable")
