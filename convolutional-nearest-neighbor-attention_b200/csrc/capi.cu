@@ -165,6 +165,7 @@ int convnn_b200_device_status(int* code) {
     if ((rc = read_gemm_tc_status(&b))) return rc;
     if ((rc = read_sim_topk2_status(&c))) return rc;
     if (!c && (rc = read_dw_stream_status(&c))) return rc;
+    if (!c && (rc = read_attention_status(&c))) return rc;
     *code = a ? a : (b ? b : c);
     return CONVNN_OK;
 }
@@ -399,6 +400,84 @@ int convnn_b200_linear(int dtype, const void* a, int64_t lda, const void* w, con
     p.a_mode = A_ROWS; p.c_mode = C_ROWS; p.rows_per_batch = 1; p.T = 1; p.H = 1; p.dk = N; p.Cp = N;
     p.gelu = gelu; p.residual = residual; p.ldr = ldr;
     return launch_gemm_simt(dtype, p, st);
+}
+
+// ---- the other halves of the branching wrappers ------------------------------------------------
+
+static int branch_args_ok(const char* who, int dtype, int32_t B, int32_t T, int32_t D, int32_t H, int64_t ldx, int64_t ldo) {
+    if (dtype != CONVNN_F32 && dtype != CONVNN_BF16) return set_error(CONVNN_E_INVALID, "%s: unknown dtype %d", who, dtype);
+    if (B < 1 || T < 1 || D < 1 || H < 1 || D % H != 0)
+        return set_error(CONVNN_E_INVALID, "%s: bad shape (B=%d T=%d D=%d H=%d)", who, B, T, D, H);
+    if (ldx < D || ldo < D) return set_error(CONVNN_E_INVALID, "%s: a leading dimension is smaller than D=%d", who, D);
+    if ((long long)B * T * D >= (1ll << 31)) return set_error(CONVNN_E_UNSUPPORTED, "%s: tensor exceeds 2^31 elements", who);
+    return CONVNN_OK;
+}
+
+size_t convnn_b200_attention_workspace_bytes(int dtype, int32_t B, int32_t T, int32_t D) {
+    if ((dtype != CONVNN_F32 && dtype != CONVNN_BF16) || B < 1 || T < 1 || D < 1) return 0;
+    return 4 * up256((size_t)B * T * D * (dtype == CONVNN_F32 ? 4 : 2));
+}
+
+int convnn_b200_softmax_attention(int dtype, const void* x, int64_t ldx, const void* w_qkv, const void* w_o, void* out,
+                                  int64_t ldo, int32_t B, int32_t T, int32_t D, int32_t H, void* workspace,
+                                  size_t workspace_bytes, void* stream) {
+    int rc = branch_args_ok("softmax_attention", dtype, B, T, D, H, ldx, ldo);
+    if (rc) return rc;
+    REQUIRE_PTR(x); REQUIRE_PTR(w_qkv); REQUIRE_PTR(w_o); REQUIRE_PTR(out); REQUIRE_PTR(workspace);
+    if (!aligned16(workspace)) return set_error(CONVNN_E_ALIGN, "workspace must be 16-byte aligned");
+    const size_t need = convnn_b200_attention_workspace_bytes(dtype, B, T, D);
+    if (workspace_bytes < need)
+        return set_error(CONVNN_E_WORKSPACE, "workspace has %zu bytes, %zu needed", workspace_bytes, need);
+    if ((rc = check_device())) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t elt = dtype == CONVNN_F32 ? 4 : 2, part = up256((size_t)B * T * D * elt);
+    char* ws = static_cast<char*>(workspace);
+    void* qkv[3] = {ws, ws + part, ws + 2 * part};
+    void* o = ws + 3 * part;
+    const long long M = (long long)B * T;
+    // q, k, v: one launch over the packed weight where the tensor-core GEMM takes the shape
+    if (dtype == CONVNN_BF16 && !force_simt() && gemm_tc_supported(x, ldx, w_qkv, D, 3 * D, 3, qkv, D)) {
+        GemmTcOpts go;
+        if ((rc = launch_gemm_tc(x, ldx, w_qkv, (int)M, 3 * D, D, 3, qkv, D, go, st))) return rc;
+    } else {
+        for (int i = 0; i < 3; ++i)
+            if ((rc = convnn_b200_linear(dtype, x, ldx, static_cast<const char*>(w_qkv) + (size_t)i * D * D * elt, nullptr,
+                                         nullptr, 0, qkv[i], D, M, D, D, 0, stream)))
+                return rc;
+    }
+    if ((rc = launch_attention(dtype, qkv[0], qkv[1], qkv[2], o, B, T, D, H, st))) return rc;
+    return convnn_b200_linear(dtype, o, D, w_o, nullptr, nullptr, 0, out, ldo, M, D, D, 0, stream);
+}
+
+size_t convnn_b200_conv1d_attention_workspace_bytes(int dtype, int32_t B, int32_t T, int32_t D, int32_t kernel_size) {
+    if ((dtype != CONVNN_F32 && dtype != CONVNN_BF16) || B < 1 || T < 1 || D < 1 || kernel_size < 1) return 0;
+    const size_t elt = dtype == CONVNN_F32 ? 4 : 2, part = up256((size_t)B * T * D * elt);
+    return 3 * part + up256((size_t)B * T * D * kernel_size * elt);
+}
+
+int convnn_b200_conv1d_attention(int dtype, const void* x, int64_t ldx, const void* w_x, const void* b_x,
+                                 const void* w_conv, const void* b_conv, const void* w_o, const void* b_o, void* out,
+                                 int64_t ldo, int32_t B, int32_t T, int32_t D, int32_t H, int32_t kernel_size,
+                                 void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = branch_args_ok("conv1d_attention", dtype, B, T, D, H, ldx, ldo);
+    if (rc) return rc;
+    if (kernel_size < 1) return set_error(CONVNN_E_INVALID, "conv1d_attention: kernel_size must be positive");
+    REQUIRE_PTR(x); REQUIRE_PTR(w_x); REQUIRE_PTR(w_conv); REQUIRE_PTR(w_o); REQUIRE_PTR(out); REQUIRE_PTR(workspace);
+    if (!aligned16(workspace)) return set_error(CONVNN_E_ALIGN, "workspace must be 16-byte aligned");
+    const size_t need = convnn_b200_conv1d_attention_workspace_bytes(dtype, B, T, D, kernel_size);
+    if (workspace_bytes < need)
+        return set_error(CONVNN_E_WORKSPACE, "workspace has %zu bytes, %zu needed", workspace_bytes, need);
+    if ((rc = check_device())) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t elt = dtype == CONVNN_F32 ? 4 : 2, part = up256((size_t)B * T * D * elt);
+    char* ws = static_cast<char*>(workspace);
+    void *y = ws, *o = ws + part, *merged = ws + 2 * part, *unfold = ws + 3 * part;
+    const long long M = (long long)B * T;
+    if ((rc = convnn_b200_linear(dtype, x, ldx, w_x, b_x, nullptr, 0, y, D, M, D, D, 0, stream))) return rc;
+    if ((rc = launch_conv1d_heads(dtype, y, w_conv, b_conv, o, unfold, B, T, H, D / H, kernel_size, st))) return rc;
+    // the reference reads the per-head (T, d_k) block back as (d_k, T) for every H (layers.py:487-489, 499)
+    if ((rc = launch_merge_heads(dtype, o, merged, B, T, H, D / H, st))) return rc;
+    return convnn_b200_linear(dtype, merged, D, w_o, b_o, nullptr, 0, out, ldo, M, D, D, 0, stream);
 }
 
 }  // extern "C"

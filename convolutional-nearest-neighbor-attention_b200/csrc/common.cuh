@@ -126,6 +126,11 @@ int launch_patchify(int dtype, const void* img, void* out, int B, int C, int Hh,
 int launch_gather_rows(int dtype, const void* x, long long ldx, const int32_t* cand, void* xq, int B, int Tn, int S,
                        int D, cudaStream_t st);
 int launch_merge_heads(int dtype, const void* o, void* y, int B, int Tn, int H, int dk, cudaStream_t st);
+int launch_attention(int dtype, const void* q, const void* k, const void* v, void* o, int B, int Tn, int D, int H,
+                     cudaStream_t st);
+int read_attention_status(int* out);
+int launch_conv1d_heads(int dtype, const void* y, const void* w, const void* bias, void* o, void* unfold, int B,
+                        int Tn, int H, int dk, int ks, cudaStream_t st);
 bool force_simt();   // debugging switch: environment variable CONVNN_B200_FORCE_SIMT=1
 int launch_gather_conv_simt(const convnn_desc* d, const Dims& dm, const void* v, const int32_t* idx,
                             const float* val, const void* w_conv, const void* w_pw, void* o, void* scratch,

@@ -5,18 +5,16 @@ Same constructor arguments, ``state_dict`` keys and ``forward(x)`` signature as
 (layers.py:580-652) and ``MultiHeadBranchingConv`` (layers.py:502-578), so a reference
 checkpoint loads with ``strict=True`` and the reference's ``vit.py`` can construct them
 in place of its own.  The ConvNN path runs in libconvnn_b200 (CUDA, sm_100a); it is
-forward-only (inference) and has no CPU implementation.  The non-ConvNN halves of the
-branching wrappers (softmax attention, Conv1d attention) and ``pointwise_linear`` are
-ordinary torch modules with the reference's parameter names.
+forward-only (inference) and has no CPU implementation.  The other halves of the branching
+wrappers (softmax attention, Conv1d attention) and ``pointwise_linear`` run in the same
+library; their modules only hold the parameters under the reference's names.
 """
 from __future__ import annotations
 
-import math
 from typing import Optional
 
 import torch
 import torch.nn as nn
-import torch.nn.functional as F
 
 from . import ops
 from .ops import LayerSpec
@@ -165,9 +163,32 @@ class MultiHeadConvNNAttention(nn.Module):
         return y
 
 
+def _library_call(x: torch.Tensor, what: str) -> None:
+    if not x.is_cuda:
+        raise RuntimeError(f"convnn_b200.{what} runs on CUDA (sm_100a) only; there is no CPU path")
+    if torch.is_grad_enabled() and x.requires_grad:
+        raise RuntimeError("convnn_b200 is forward-only: call it under torch.no_grad() "
+                           "(training / backward is outside this library)")
+
+
+class _PackedParams:
+    """Kernel-side copies of a module's parameters, rebuilt when a parameter changes."""
+
+    def __init__(self):
+        self._key, self._val = None, None
+
+    def get(self, params, dtype, device, build):
+        key = (dtype, device) + tuple((p.data_ptr(), p._version) for p in params)
+        if key != self._key:
+            self._val, self._key = build(), key
+        return self._val
+
+
 class MultiHeadAttention(nn.Module):
     """Softmax attention half of MultiHeadBranchingAttention (reference layers.py:90-130):
-    bias-free W_q/W_k/W_v/W_o, softmax(QK^T / sqrt(d_k)) V.  Host-side torch module."""
+    bias-free W_q/W_k/W_v/W_o, softmax(QK^T / sqrt(d_k)) V.  The modules hold the parameters (same
+    ``state_dict`` keys as the reference); the forward runs in libconvnn_b200: one packed
+    three-output projection, the softmax-attention kernel, the output projection."""
 
     def __init__(self, d_hidden, num_heads, attention_dropout):
         super().__init__()
@@ -178,28 +199,25 @@ class MultiHeadAttention(nn.Module):
         self.W_k = nn.Linear(d_hidden, d_hidden, bias=False)
         self.W_v = nn.Linear(d_hidden, d_hidden, bias=False)
         self.W_o = nn.Linear(d_hidden, d_hidden, bias=False)
+        self._packed = _PackedParams()
 
-    def forward(self, x, mask=None):
-        B, T, _ = x.shape
-        H, dk = self.num_heads, self.d_k
-        q = self.W_q(x).view(B, T, H, dk).transpose(1, 2)
-        k = self.W_k(x).view(B, T, H, dk).transpose(1, 2)
-        v = self.W_v(x).view(B, T, H, dk).transpose(1, 2)
-        if mask is None and x.is_cuda and not (self.training and self.dropout.p > 0):
-            # same softmax(QK^T / sqrt(d_k)) V, through torch's fused attention kernels
-            o = F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(B, T, self.d_hidden)
-            return self.W_o(o)
-        s = torch.matmul(q, k.transpose(-2, -1)) / math.sqrt(dk)
+    def forward(self, x, mask=None, out: Optional[torch.Tensor] = None):
+        _library_call(x, "MultiHeadAttention")
         if mask is not None:
-            s = s.masked_fill(mask == 0, -1e9)
-        a = self.dropout(torch.softmax(s, dim=-1))
-        o = torch.matmul(a, v).transpose(1, 2).reshape(B, T, self.d_hidden)
-        return self.W_o(o)
+            raise RuntimeError("convnn_b200.MultiHeadAttention takes no mask (the reference's ViT never passes one)")
+        if self.training and self.dropout.p > 0:
+            raise RuntimeError("convnn_b200 is forward-only: dropout > 0 needs module.eval()")
+        params = (self.W_q.weight, self.W_k.weight, self.W_v.weight, self.W_o.weight)
+        w_qkv, w_o = self._packed.get(params, x.dtype, x.device, lambda: (
+            torch.stack([p.detach().to(x.device, x.dtype) for p in params[:3]]).contiguous(),
+            self.W_o.weight.detach().to(x.device, x.dtype).contiguous()))
+        return ops.softmax_attention(x, w_qkv, w_o, self.num_heads, out=out)
 
 
 class MultiHeadConv1dAttention(nn.Module):
-    """Conv1d half of MultiHeadBranchingConv (reference layers.py:452-500), including its
-    flat head reinterpretation.  Host-side torch module."""
+    """Conv1d half of MultiHeadBranchingConv (reference layers.py:452-500): Linear, per-head
+    Conv1d(d_k, d_k, kernel_size, padding='same'), the reference's flat head reinterpretation,
+    Linear.  Parameters as in the reference; the forward runs in libconvnn_b200."""
 
     def __init__(self, d_hidden, num_heads, kernel_size):
         super().__init__()
@@ -210,15 +228,19 @@ class MultiHeadConv1dAttention(nn.Module):
         self.W_o = nn.Linear(d_hidden, d_hidden)
         self.in_channels = self.out_channels = self.d_k
         self.conv = nn.Conv1d(self.d_k, self.d_k, kernel_size=kernel_size, stride=1, padding="same")
+        self._packed = _PackedParams()
 
-    def forward(self, x):
-        B, T, D = x.shape
-        H, dk = self.num_heads, self.d_k
-        y = self.W_x(x).view(B, T, H, dk).permute(0, 2, 3, 1).reshape(B * H, dk, T)
-        z = self.conv(y)                                       # (B*H, dk, T)
-        o = z.permute(0, 2, 1).reshape(B, H, T * dk)           # token-major per head, flat
-        y = o.view(B, H, dk, T).permute(0, 3, 1, 2).reshape(B, T, D)
-        return self.W_o(y)
+    def forward(self, x, out: Optional[torch.Tensor] = None):
+        _library_call(x, "MultiHeadConv1dAttention")
+        params = (self.W_x.weight, self.W_x.bias, self.conv.weight, self.conv.bias, self.W_o.weight, self.W_o.bias)
+
+        def build():
+            cvt = lambda t: t.detach().to(x.device, x.dtype).contiguous()
+            # (d_k out, d_k in, kernel_size) -> (d_k out, kernel_size, d_k in): a (d_k, kernel_size * d_k) matrix
+            return (cvt(self.W_x.weight), cvt(self.W_x.bias), cvt(self.conv.weight.permute(0, 2, 1)),
+                    cvt(self.conv.bias), cvt(self.W_o.weight), cvt(self.W_o.bias))
+        w_x, b_x, w_c, b_c, w_o, b_o = self._packed.get(params, x.dtype, x.device, build)
+        return ops.conv1d_attention(x, w_x, b_x, w_c, b_c, w_o, b_o, self.num_heads, self.kernel_size, out=out)
 
 
 class _Branching(nn.Module):
@@ -244,15 +266,17 @@ class _Branching(nn.Module):
                 magnitude_type=magnitude_type, seq_length=seq_length, coordinate_encoding=coordinate_encoding,
                 convolution_type=convolution_type, softmax_topk_val=softmax_topk_val)
 
-    def _two_branches(self, x, other):
-        """ConvNN on x[..., :d_convnn] written straight into the concat buffer (no slice
-        copy in, no cat copy out), the other branch on the rest, then pointwise_linear
-        (reference layers.py:574-577, 648-651)."""
+    def _two_branches(self, x, other, residual=None):
+        """Both branches read their channel slice of x in place and write their slice of the
+        concat buffer in place (no slice copy in, no cat copy out); then pointwise_linear with
+        its bias, and the caller's skip connection if given, folded into one GEMM epilogue
+        (reference layers.py:574-577, 648-651; vit.py:264)."""
         dc = self.d_hidden_convnn
         cat = torch.empty(x.shape, dtype=x.dtype, device=x.device)
         self.convnn(x[:, :, :dc], out=cat[:, :, :dc])
-        cat[:, :, dc:] = other(x[:, :, dc:])
-        return self.pointwise_linear(cat)
+        other(x[:, :, dc:], out=cat[:, :, dc:])
+        pw = self.pointwise_linear
+        return ops.linear(cat, pw.weight, pw.bias, residual=residual)
 
 
 class MultiHeadBranchingAttention(_Branching):
@@ -268,14 +292,16 @@ class MultiHeadBranchingAttention(_Branching):
             self.attention = MultiHeadAttention(self.d_hidden_attention, num_heads, attention_dropout)
         self.pointwise_linear = nn.Linear(d_hidden, d_hidden)
 
-    def forward(self, x):
+    def forward(self, x, residual: Optional[torch.Tensor] = None):
         # The reference swaps the degenerate cases (ratio 0 calls the ConvNN branch that was
         # not built and vice versa, layers.py:643-646) and fails with AttributeError; so do we.
         if self.branch_ratio == 0:
-            return self.convnn(x)
-        if self.branch_ratio == 1:
-            return self.attention(x)
-        return self._two_branches(x, self.attention)
+            y = self.convnn(x)
+        elif self.branch_ratio == 1:
+            y = self.attention(x)
+        else:
+            return self._two_branches(x, self.attention, residual)
+        return y if residual is None else residual + y
 
 
 class MultiHeadBranchingConv(_Branching):
@@ -292,9 +318,11 @@ class MultiHeadBranchingConv(_Branching):
             self.conv1d = MultiHeadConv1dAttention(self.d_hidden_conv1d, num_heads, kernel_size)
         self.pointwise_linear = nn.Linear(d_hidden, d_hidden)
 
-    def forward(self, x):
+    def forward(self, x, residual: Optional[torch.Tensor] = None):
         if self.branch_ratio == 0:
-            return self.conv1d(x)
-        if self.branch_ratio == 1:
-            return self.convnn(x)
-        return self._two_branches(x, self.conv1d)
+            y = self.conv1d(x)
+        elif self.branch_ratio == 1:
+            y = self.convnn(x)
+        else:
+            return self._two_branches(x, self.conv1d, residual)
+        return y if residual is None else residual + y

@@ -235,6 +235,52 @@ def forward(spec: LayerSpec, x: torch.Tensor, packed, cand: Optional[torch.Tenso
     return out
 
 
+# ---- the other halves of the branching wrappers ------------------------------------------------
+
+def _out_slice(out: Optional[torch.Tensor], like: torch.Tensor) -> Tuple[torch.Tensor, int]:
+    B, T, D = like.shape
+    if out is None:
+        out = torch.empty(B, T, D, dtype=like.dtype, device=like.device)
+    view, ldo = _rows_view(out)
+    if view is not out:
+        raise ValueError("out must have unit channel stride and evenly strided rows")
+    return out, ldo
+
+
+def softmax_attention(x: torch.Tensor, w_qkv: torch.Tensor, w_o: torch.Tensor, num_heads: int,
+                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """MultiHeadAttention.forward (reference layers.py:105-130) through
+    ``convnn_b200_softmax_attention``; ``w_qkv`` = (3, D, D) [W_q; W_k; W_v]."""
+    _require_cuda(x, w_qkv, w_o)
+    L = _capi.lib()
+    x, ldx = _rows_view(x)
+    B, T, D = x.shape
+    out, ldo = _out_slice(out, x)
+    dt = _dtype_code(x.dtype)
+    ws = torch.empty(L.convnn_b200_attention_workspace_bytes(dt, B, T, D), dtype=torch.uint8, device=x.device)
+    _capi.check(L.convnn_b200_softmax_attention(dt, x.data_ptr(), ldx, w_qkv.data_ptr(), w_o.data_ptr(), out.data_ptr(),
+                                                ldo, B, T, D, num_heads, ws.data_ptr(), ws.numel(), _stream(x)))
+    return out
+
+
+def conv1d_attention(x: torch.Tensor, w_x, b_x, w_conv, b_conv, w_o, b_o, num_heads: int, kernel_size: int,
+                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """MultiHeadConv1dAttention.forward (reference layers.py:477-500) through
+    ``convnn_b200_conv1d_attention``; ``w_conv`` packed (d_k, kernel_size, d_k)."""
+    _require_cuda(x, w_x, w_conv, w_o)
+    L = _capi.lib()
+    x, ldx = _rows_view(x)
+    B, T, D = x.shape
+    out, ldo = _out_slice(out, x)
+    dt = _dtype_code(x.dtype)
+    ws = torch.empty(L.convnn_b200_conv1d_attention_workspace_bytes(dt, B, T, D, kernel_size), dtype=torch.uint8,
+                     device=x.device)
+    _capi.check(L.convnn_b200_conv1d_attention(dt, x.data_ptr(), ldx, w_x.data_ptr(), _capi.ptr(b_x), w_conv.data_ptr(),
+                                               _capi.ptr(b_conv), w_o.data_ptr(), _capi.ptr(b_o), out.data_ptr(), ldo,
+                                               B, T, D, num_heads, kernel_size, ws.data_ptr(), ws.numel(), _stream(x)))
+    return out
+
+
 # ---- the encoder ops around the layer ---------------------------------------------------
 
 def _flat_rows(t: torch.Tensor) -> Tuple[torch.Tensor, int, int]:

@@ -102,10 +102,7 @@ class TransformerEncoder(nn.Module):
         folded into their stores) and the attention output projection (+ skip) in libconvnn_b200."""
         n1, n2, fc1, fc2 = self.norm1, self.norm2, self.mlp[0], self.mlp[3]
         xn = ops.layernorm(x, n1.weight, n1.bias, n1.eps)
-        if isinstance(self.attention, MultiHeadConvNNAttention):
-            x = self.attention(xn, residual=x)
-        else:
-            x = x + self.attention(xn)
+        x = self.attention(xn, residual=x)       # skip connection folded into the layer's last store
         xn = ops.layernorm(x, n2.weight, n2.bias, n2.eps)
         h = ops.linear(xn, fc1.weight, fc1.bias, gelu=True)
         return ops.linear(h, fc2.weight, fc2.bias, residual=x)

@@ -228,6 +228,28 @@ int convnn_b200_embed_tokens(int dtype, const void* proj, const void* gamma, con
                              const void* cls, const void* pe, void* out, int32_t B, int32_t Np,
                              int32_t D, void* stream);
 
+/* ---- the other halves of the reference's branching wrappers (layers.py:574-577, 648-651) ---- */
+
+/* MultiHeadAttention.forward (layers.py:105-130), eval mode, no mask: q, k, v projections with the
+ * packed bias-free weight w_qkv = (3, D, D) [W_q; W_k; W_v], softmax(q k^T / sqrt(d_k)) v per head,
+ * then the bias-free W_o.  x (B, T, D) row stride ldx (a channel slice of a wider tensor goes in
+ * as it is, layers.py:649), out (B, T, D) row stride ldo (written straight into the concat buffer).
+ * workspace: convnn_b200_attention_workspace_bytes() bytes for q, k, v and the per-head output. */
+size_t convnn_b200_attention_workspace_bytes(int dtype, int32_t B, int32_t T, int32_t D);
+int convnn_b200_softmax_attention(int dtype, const void* x, int64_t ldx, const void* w_qkv, const void* w_o,
+                                  void* out, int64_t ldo, int32_t B, int32_t T, int32_t D, int32_t H,
+                                  void* workspace, size_t workspace_bytes, void* stream);
+
+/* MultiHeadConv1dAttention.forward (layers.py:477-500): y = x W_x^T + b_x, per-head
+ * Conv1d(d_k, d_k, kernel_size, padding='same') with bias over the tokens, the reference's flat
+ * head reinterpretation (applied for every H, with seq_length = T), then W_o with bias.
+ * w_conv is packed (d_k out, kernel_size, d_k in) from the module's (d_k, d_k, kernel_size). */
+size_t convnn_b200_conv1d_attention_workspace_bytes(int dtype, int32_t B, int32_t T, int32_t D, int32_t kernel_size);
+int convnn_b200_conv1d_attention(int dtype, const void* x, int64_t ldx, const void* w_x, const void* b_x,
+                                 const void* w_conv, const void* b_conv, const void* w_o, const void* b_o,
+                                 void* out, int64_t ldo, int32_t B, int32_t T, int32_t D, int32_t H,
+                                 int32_t kernel_size, void* workspace, size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

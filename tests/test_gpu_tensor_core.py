@@ -22,6 +22,12 @@ CASES = [
     (1, 130, 130, 48, 1, 32, "euclidean", "all"),
     (1, 1030, 1030, 64, 1, 4, "cosine", "all"),
     (2, 50, 17, 32, 1, 16, "matmul", "random"),
+    # short candidate lists: full 256-candidate set, tiny candidate sets, several row tiles, one pick
+    (1, 256, 256, 64, 2, 12, "euclidean", "all"),
+    (2, 300, 40, 64, 1, 9, "cosine", "random"),
+    (1, 20, 20, 32, 1, 16, "matmul", "all"),
+    (3, 700, 33, 160, 5, 2, "cosine", "spatial"),
+    (2, 197, 197, 96, 3, 1, "matmul", "all"),
     # long key and candidate lists: the CTA-pair kernel (256-row units, 256-column tiles, ragged ends)
     (2, 1536, 1200, 128, 2, 9, "euclidean", "random"),
     (1, 2048, 2048, 192, 1, 16, "matmul", "all"),
@@ -128,6 +134,39 @@ def test_tensor_core_and_simt_kernels_agree_bitwise_on_indices():
     same = (i16 == i32).all(-1)
     assert float(same.float().mean()) > 0.999
     assert float((v16 - v32).abs().max()) < 1e-4
+
+
+def test_short_sequence_exact_ties_keep_the_lower_column():
+    """The ViT shapes on the tensor-core kernel: identical candidate rows in the same and in
+    different column tiles, a key row of zeros (every similarity ties) and a row with ties exactly
+    at the K-th place.  Expected order: by value, equal values by ascending column."""
+    g = torch.Generator().manual_seed(21)
+    T = S = 197
+    q = torch.randn(2, S, 1, 64, generator=g).to(torch.bfloat16)
+    k = torch.randn(2, T, 1, 64, generator=g).to(torch.bfloat16)
+    q[0, 150] = q[0, 20]           # lower and upper column range
+    q[0, 30] = q[0, 21]            # both in the lower range
+    k[0, 5] = q[0, 20]
+    k[0, 100] = q[0, 21]
+    k[0, 7] = 0                    # all 197 similarities are exactly 0
+    q[1, 40:60] = q[1, 40]         # twenty equal candidates: ties at and around the K-th place
+    k[1, 3] = q[1, 40]
+    cfg = ConvNNConfig(d_hidden=64, num_heads=1, K=9, magnitude_type="matmul", seq_length=T)
+    idx, val = ops.sim_topk(spec_of(cfg), q.to(DEV), k.to(DEV), None, None)
+    torch.cuda.synchronize()
+    assert _capi.device_status() == 0
+    sim = (k[:, :, 0].double() @ q[:, :, 0].double().transpose(1, 2)) / 8.0          # exact in float64
+    order = torch.sort(sim, dim=-1, descending=True, stable=True).indices[..., :9]
+    top = sim.gather(-1, order)
+    nxt = torch.sort(sim, dim=-1, descending=True, stable=True).values[..., :10]
+    gaps = (nxt[..., :-1] - nxt[..., 1:])
+    loose = ((gaps > 0) & (gaps < 2e-6)).any(-1)      # near-ties (not exact ties) may go either way
+    same = (idx[:, 0].cpu().long() == order).all(-1)
+    assert bool((same | loose).all()), f"{int((~(same | loose)).sum())} rows break the tie rule"
+    assert idx[0, 0, 5, :2].tolist() == [20, 150] and idx[0, 0, 100, :2].tolist() == [21, 30]
+    assert idx[0, 0, 7].tolist() == list(range(9)) and bool((val[0, 0, 7] == 0).all())
+    assert idx[1, 0, 3].tolist() == list(range(40, 49))
+    assert float((val[:, 0].cpu().double() - top)[same].abs().max()) < 1e-5
 
 
 def test_pair_kernel_orders_exact_ties_by_column():
