@@ -289,7 +289,7 @@ def stage_profile(model, B, cfg, dev, sets=4, reps=5):
         "qkv_proj": lambda d: ops.qkv_proj(spec, d["x"], w_qkv),
         "sim_topk": lambda d: ops.sim_topk(spec, d["q"], d["k"], d["qs"], d["ks"]),
         "gather_conv": lambda d: ops.gather_conv(spec, d["v"], d["idx"], d["val"], w_conv, w_pw),
-        "out_proj": lambda d: ops.out_proj(spec, d["o"], w_o),
+        "out_proj": lambda d: ops.out_proj(spec, d["o"], w_o, residual=d["x"]),
     }
     out = {}
     torch.cuda.synchronize()
@@ -520,44 +520,9 @@ def algorithmic_work(B, T, S, D, H, K, elt=2):
                          flops=2 * B * (2 * T + S) * D * D),
         "sim_topk": dict(bytes=elt * (B * T * D + B * S * D) + idxval + 4 * B * H * (T + S), flops=2 * B * T * S * D),
         "gather_conv": dict(bytes=elt * (2 * B * T * D + K * D) + idxval, flops=2 * B * T * D * K),
-        "out_proj": dict(bytes=elt * (2 * B * T * D + D * D), flops=2 * B * T * D * D),
+        # (with the skip connection read: one more activation-sized tensor)
+        "out_proj": dict(bytes=elt * (3 * B * T * D + D * D), flops=2 * B * T * D * D),
     }
-
-
-class LogitsGather:
-    """All-gather of each step's logits on a side stream, double-buffered, so that the collective of
-    batch i runs under the forward of batch i+1 instead of between the two on the compute stream."""
-
-    def __init__(self, world, n_local, classes, dtype, dev):
-        self.world = world
-        if world > 1:
-            self.side = torch.cuda.Stream(dev)
-            self.local = [torch.empty(n_local, classes, dtype=dtype, device=dev) for _ in range(2)]
-            self.full = [torch.empty(n_local * world, classes, dtype=dtype, device=dev) for _ in range(2)]
-            self.copied = [torch.cuda.Event() for _ in range(2)]
-            self.gathered = [torch.cuda.Event() for _ in range(2)]
-            self.i = 0
-
-    def __call__(self, logits):
-        """Returns the tensor that will hold the gathered logits and the event that says when."""
-        if self.world == 1:
-            return logits, None
-        import torch.distributed as dist
-        s = self.i & 1
-        self.i += 1
-        cur = torch.cuda.current_stream()
-        cur.wait_event(self.gathered[s])            # the gather that last read this slot has finished
-        self.local[s].copy_(logits, non_blocking=True)
-        self.copied[s].record(cur)
-        with torch.cuda.stream(self.side):
-            self.side.wait_event(self.copied[s])
-            dist.all_gather_into_tensor(self.full[s], self.local[s])
-            self.gathered[s].record(self.side)
-        return self.full[s], self.gathered[s]
-
-    def drain(self):
-        if self.world > 1:
-            torch.cuda.current_stream().wait_stream(self.side)
 
 
 def run_ours(args) -> int:
@@ -600,6 +565,7 @@ def run_ours(args) -> int:
         n_cap = lib.convnn_b200_launch_count()
         graph, static_out = graph_model(model, static_in)
         per_forward = (lib.convnn_b200_launch_count() - n_cap) // 3      # two eager calls + the capture
+    from convnn_b200.sharded import LogitsGather
     gather = LogitsGather(world, B, classes, torch.bfloat16, dev)
 
     def batch_step(x):
@@ -782,8 +748,8 @@ def main() -> int:
                     help="batches per step (default: chosen so that the timed region lasts about a second)")
     ap.add_argument("--no-extras", action="store_true", help="skip the cfg-3 / cfg-4 models and the layer sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--stage", choices=["qkv_proj", "sim_topk", "gather_conv", "out_proj", "out_proj_skip", "mlp0",
-                                        "mlp3", "layernorm"],
+    ap.add_argument("--stage", choices=["qkv_proj", "sim_topk", "gather_conv", "out_proj",
+                                        "out_proj_skip", "mlp0", "mlp3", "layernorm"],
                     help="run only this stage of one layer (profiling aid)")
     ap.add_argument("--layer-sweep", action="store_true",
                     help="standalone layer on long sequences (8 x N x 768), per-stage time and roofline")

@@ -47,6 +47,41 @@ def gather_logits(local: torch.Tensor, total: int, group=None) -> torch.Tensor:
     return torch.cat([out[r * nmax: r * nmax + (hi - lo)] for r, (lo, hi) in enumerate(sizes)], dim=0)
 
 
+class LogitsGather:
+    """All-gather of each step's logits on a side stream, double-buffered, so that the collective of
+    batch i runs under the forward of batch i+1 instead of between the two on the compute stream."""
+
+    def __init__(self, world, n_local, classes, dtype, dev):
+        self.world = world
+        if world > 1:
+            self.side = torch.cuda.Stream(dev)
+            self.local = [torch.empty(n_local, classes, dtype=dtype, device=dev) for _ in range(2)]
+            self.full = [torch.empty(n_local * world, classes, dtype=dtype, device=dev) for _ in range(2)]
+            self.copied = [torch.cuda.Event() for _ in range(2)]
+            self.gathered = [torch.cuda.Event() for _ in range(2)]
+            self.i = 0
+
+    def __call__(self, logits):
+        """Returns the tensor that will hold the gathered logits and the event that says when."""
+        if self.world == 1:
+            return logits, None
+        s = self.i & 1
+        self.i += 1
+        cur = torch.cuda.current_stream()
+        cur.wait_event(self.gathered[s])            # the gather that last read this slot has finished
+        self.local[s].copy_(logits, non_blocking=True)
+        self.copied[s].record(cur)
+        with torch.cuda.stream(self.side):
+            self.side.wait_event(self.copied[s])
+            dist.all_gather_into_tensor(self.full[s], self.local[s])
+            self.gathered[s].record(self.side)
+        return self.full[s], self.gathered[s]
+
+    def drain(self):
+        if self.world > 1:
+            torch.cuda.current_stream().wait_stream(self.side)
+
+
 @torch.no_grad()
 def sharded_forward(model, images: torch.Tensor, group=None, gather: bool = True) -> torch.Tensor:
     """Run ``model`` on this rank's slice of ``images`` (the full batch, same on every rank)
