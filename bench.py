@@ -121,7 +121,10 @@ def config_record(world: int, inner: int) -> dict:
             "inner_iters": inner, "images_per_step": BATCH_PER_GPU * world * inner,
             "parallelism": f"batch-shard x{world}",
             "l2": "3 distinct resident input batches (231 MB) rotate, larger than L2",
-            "launch": "cuda_graph"}
+            "launch": "cuda_graph",
+            "collective": "none (one rank)" if world == 1 else
+                          "one NCCL all_gather_into_tensor of the logits per group of batches (default: per step), "
+                          "on a side stream under the following forwards"}
 
 
 def run_reference_arm(args) -> int:
@@ -310,6 +313,41 @@ def stage_profile(model, B, cfg, dev, sets=4, reps=5):
     return out
 
 
+def run_forward_of(args) -> int:
+    """One eager forward (after a warm-up forward) of a whole model of the baseline's configurations,
+    for launch lists: python bench.py --forward-of cfg-4 [--stage-batch 32].  Prints the number of
+    library kernels the forward launched."""
+    import convnn_b200
+    from convnn_b200 import _capi
+    from oracle.vit_oracle import ViTConfig, make_vit_weights
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    table = {"cfg-2": (BATCH_PER_GPU, WORKLOAD)}
+    for name, (B, kw) in OTHER_CONFIGS.items():
+        table[name.split()[0]] = (B, kw)
+    B, kw = table[args.forward_of]
+    B = args.stage_batch if args.stage_batch != BATCH_PER_GPU else B
+    cfg = ViTConfig(**kw)
+    model = convnn_b200.ViT(convnn_b200.make_args(**{f: getattr(cfg, f) for f in cfg.__dataclass_fields__},
+                                                  device=dev)).eval()
+    model.load_state_dict(make_vit_weights(cfg, seed=1), strict=True)
+    model = model.to(dev, torch.bfloat16)
+    if cfg.sampling_type == "random":
+        model.set_candidates(torch.randperm(cfg.seq_len, generator=torch.Generator().manual_seed(17))
+                             [: cfg.num_samples].to(dev))
+    x = torch.randn(B, 3, 224, 224, device=dev).to(torch.bfloat16)
+    lib = _capi.lib()
+    with torch.no_grad():
+        model(x)
+        torch.cuda.synchronize()
+        n0 = lib.convnn_b200_launch_count()
+        model(x)
+        torch.cuda.synchronize()
+    print(json.dumps({"forward_of": args.forward_of, "batch": B, "library_launches_per_forward":
+                      int(lib.convnn_b200_launch_count() - n0), "device_status": _capi.device_status()}))
+    return 0
+
+
 def run_single_stage(args) -> int:
     """Launch one stage of the layer a few times at the bench shape (for ncu captures and
     quick timing): python bench.py --stage sim_topk [--stage-batch 64] [--stage-iters 3]."""
@@ -343,6 +381,17 @@ def run_single_stage(args) -> int:
            "mlp0": lambda: ops.linear(x, W1, b1, gelu=True),
            "mlp3": lambda: ops.linear(h, W2, b2, residual=x),
            "layernorm": lambda: ops.layernorm(x, gam, bet)}
+    if args.stage in ("attention", "conv1d_attention"):
+        # the other halves of the ViT-Base branching wrappers (cfg-4): 384 channels, 12 heads
+        Dh, Hh = 384, 12
+        xa = torch.randn(B, T, 2 * Dh, device=dev).to(torch.bfloat16)[:, :, Dh:]
+        if args.stage == "attention":
+            m = convnn_b200.MultiHeadAttention(Dh, Hh, 0.0).eval().to(dev, torch.bfloat16)
+        else:
+            m = convnn_b200.MultiHeadConv1dAttention(Dh, Hh, 9).eval().to(dev, torch.bfloat16)
+        with torch.no_grad():
+            m(xa)
+        fns[args.stage] = lambda: m(xa)
     fn = fns[args.stage]
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -566,12 +615,13 @@ def run_ours(args) -> int:
         graph, static_out = graph_model(model, static_in)
         per_forward = (lib.convnn_b200_launch_count() - n_cap) // 3      # two eager calls + the capture
     from convnn_b200.sharded import LogitsGather
-    gather = LogitsGather(world, B, classes, torch.bfloat16, dev)
+    per_flush = args.gather_every if args.gather_every > 0 else inner
+    gather = LogitsGather(world, per_flush, B, classes, torch.bfloat16, dev)    # default: one collective per step
 
     def batch_step(x):
         static_in.copy_(x, non_blocking=True)
         graph.replay()
-        return gather(static_out)
+        return gather.add(static_out)
 
     def barrier():
         if world > 1:
@@ -604,7 +654,7 @@ def run_ours(args) -> int:
         copy_stream = torch.cuda.Stream(dev)
         d2h_stream = torch.cuda.Stream(dev)
         staging = [torch.empty_like(resident[0]) for _ in range(2)]
-        out_host = torch.empty(total, classes, dtype=torch.bfloat16).pin_memory()
+        out_host = torch.empty(world * inner * B, classes, dtype=torch.bfloat16).pin_memory()   # one step's logits
         ready = [torch.cuda.Event() for _ in range(2)]
         freed = [torch.cuda.Event() for _ in range(2)]
 
@@ -619,16 +669,15 @@ def run_ours(args) -> int:
                     staging[s].copy_(host[i % NBUF], non_blocking=True)
                     ready[s].record(copy_stream)
                 cur.wait_event(ready[s])
-                logits, done = batch_step(staging[s])
+                group = batch_step(staging[s])
                 freed[s].record(cur)
-                if done is not None:
-                    # read the gathered logits back on a stream of their own once the side stream has
-                    # them (behind the input copies they would hold up the next batch)
+                if group is not None:
+                    # a step's logits are complete (and gathered): read them back on a stream of their
+                    # own (behind the input copies they would hold up the next batch)
+                    logits, done = group
                     with torch.cuda.stream(d2h_stream):
                         d2h_stream.wait_event(done)
-                        out_host.copy_(logits, non_blocking=True)
-                else:
-                    out_host.copy_(logits, non_blocking=True)
+                        out_host[: logits.numel() // classes].view(logits.shape).copy_(logits, non_blocking=True)
             gather.drain()
             cur.wait_stream(copy_stream)
             cur.wait_stream(d2h_stream)
@@ -650,12 +699,12 @@ def run_ours(args) -> int:
             s_in = torch.empty_like(xs[0])
             s_in.copy_(xs[0])
             s_graph, s_out = graph_model(model, s_in)
-            s_gather = LogitsGather(world, Bs, classes, torch.bfloat16, dev)
+            s_gather = LogitsGather(world, per_flush, Bs, classes, torch.bfloat16, dev)
 
             def strong_step(i):
                 s_in.copy_(xs[i % NBUF], non_blocking=True)
                 s_graph.replay()
-                s_gather(s_out)
+                s_gather.add(s_out)
             for i in range(10):
                 strong_step(i)
             s_gather.drain()
@@ -675,7 +724,11 @@ def run_ours(args) -> int:
         stage_ms = stage_profile(model, B, cfg, dev)
 
     t = torch.tensor([ms, ms_e2e, ms_strong], dtype=torch.float64, device=dev)
+    per_rank = [[float(v) for v in t]]
     if world > 1:
+        every = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(every, t)
+        per_rank = [[float(v) for v in r] for r in every]
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, ms_e2e, ms_strong = float(t[0]), float(t[1]), float(t[2])
 
@@ -703,13 +756,15 @@ def run_ours(args) -> int:
                              + ("the reference's own vit.ViT" if kind == "reference" else "oracle port")}
         n_batches = args.steps * inner
         h2d = B * 3 * 224 * 224 * 2
-        d2h = out_host.numel() * 2
+        d2h = world * B * classes * 2            # per batch: the gathered logits of every rank
         line = {
             "metric": METRIC, "value": total * n_batches / (ms / 1e3), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": config_record(world, inner),
             "ms_per_batch": ms / n_batches, "host_numa_bound": bool(numa_bound),
+            "per_rank_ms_per_batch": {"device_resident": [r[0] / n_batches for r in per_rank],
+                                      "e2e": [r[1] / n_batches for r in per_rank]},
             "e2e": {"value": total * n_batches / (ms_e2e / 1e3), "unit": UNIT, "h2d_bytes_per_step": h2d * inner,
                     "d2h_bytes_per_step": d2h * inner, "ms_per_step": ms_e2e / args.steps,
                     "host_images": "bfloat16, pinned (float32 host images would double the copy)",
@@ -726,6 +781,7 @@ def run_ours(args) -> int:
                               "images_per_s": BATCH_PER_GPU / (ms_strong / 1e3), "ms_per_batch": ms_strong,
                               "note": "the baseline's 256-image batch split over the ranks, device-resident, "
                                       "max over ranks; `value` stays the weak-scaling figure"}
+
         if world == 1 and not args.no_extras:
             with torch.no_grad():
                 del graph
@@ -746,19 +802,26 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--inner-iters", type=int, default=0,
                     help="batches per step (default: chosen so that the timed region lasts about a second)")
+    ap.add_argument("--gather-every", type=int, default=0,
+                    help="batches per logits all-gather at N > 1 (default: one collective per step)")
     ap.add_argument("--no-extras", action="store_true", help="skip the cfg-3 / cfg-4 models and the layer sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--stage", choices=["qkv_proj", "sim_topk", "gather_conv", "out_proj",
                                         "out_proj_skip", "mlp0", "mlp3", "layernorm"],
                     help="run only this stage of one layer (profiling aid)")
+    ap.add_argument("--forward-of", choices=["cfg-2", "cfg-3", "cfg-4"],
+                    help="one eager forward of that configuration's whole model (for launch lists)")
     ap.add_argument("--layer-sweep", action="store_true",
                     help="standalone layer on long sequences (8 x N x 768), per-stage time and roofline")
     ap.add_argument("--sweep-n", type=int, nargs="+", default=[1024, 4096, 16384])
     ap.add_argument("--stage-batch", type=int, default=BATCH_PER_GPU)
     ap.add_argument("--stage-iters", type=int, default=3)
     args = ap.parse_args()
+    if args.forward_of:
+        return run_forward_of(args)
     if args.stage:
-        return run_single_stage(args)
+        with torch.no_grad():
+            return run_single_stage(args)
     if args.layer_sweep:
         return run_layer_sweep(args)
     args.warmup = max(args.warmup, 3)
