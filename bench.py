@@ -806,8 +806,8 @@ def main() -> int:
                     help="batches per logits all-gather at N > 1 (default: one collective per step)")
     ap.add_argument("--no-extras", action="store_true", help="skip the cfg-3 / cfg-4 models and the layer sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--stage", choices=["qkv_proj", "sim_topk", "gather_conv", "out_proj",
-                                        "out_proj_skip", "mlp0", "mlp3", "layernorm"],
+    ap.add_argument("--stage", choices=["qkv_proj", "sim_topk", "gather_conv", "out_proj", "out_proj_skip", "mlp0",
+                                        "mlp3", "layernorm", "attention", "conv1d_attention"],
                     help="run only this stage of one layer (profiling aid)")
     ap.add_argument("--forward-of", choices=["cfg-2", "cfg-3", "cfg-4"],
                     help="one eager forward of that configuration's whole model (for launch lists)")

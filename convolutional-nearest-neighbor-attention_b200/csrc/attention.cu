@@ -24,6 +24,7 @@
 
 #include "common.cuh"
 #include "sm100.cuh"
+#include "f32x2.cuh"
 
 namespace convnn {
 
@@ -185,20 +186,27 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) { if (lane == 0) fail(abort_flag, 66); break; }
             {
-                const int nseg = p.BN / 8, items = p.dk * nseg;
+                // item i = (segment of 8 tokens sg, channel c), i = sg * dk + c, visited with stride 128:
+                // (sg, c) advance by (128 / dk, 128 % dk) with a carry, no division in the loop
+                const int nseg = p.BN / 8;
+                const int dsg = 128 / p.dk, dc = 128 - dsg * p.dk;
+                int sg = st / p.dk, c = st - sg * p.dk;
                 const unsigned short* v16 = reinterpret_cast<const unsigned short*>(sV);
-                for (int i = st; i < items; i += 128) {
-                    const int sg = i / p.dk, c = i - sg * p.dk;
+                while (sg < nseg) {
                     const int t0 = sg * 8;
+                    const unsigned short* src = v16 + t0 * p.dk + c;
                     uint32_t w[4];
 #pragma unroll
                     for (int e2 = 0; e2 < 4; ++e2) {
-                        const uint32_t lo = v16[(t0 + 2 * e2) * p.dk + c], hi = v16[(t0 + 2 * e2 + 1) * p.dk + c];
+                        const uint32_t lo = src[(2 * e2) * p.dk], hi = src[(2 * e2 + 1) * p.dk];
                         w[e2] = lo | (hi << 16);
                     }
                     const int kc2 = t0 >> 6, seg = (t0 & 63) >> 3;
                     uint8_t* dst = sVt + kc2 * vt_chunk + c * 128 + ((seg ^ (c & 7)) << 4);
                     *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+                    sg += dsg;
+                    c += dc;
+                    if (c >= p.dk) { c -= p.dk; ++sg; }
                 }
             }
             fence_proxy_async();                 // the transposed tile is read by the MMA (async proxy)
@@ -209,30 +217,45 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) { if (lane == 0) fail(abort_flag, 67); break; }
             tc_fence_after_sync();
+            // row maximum; only the last chunk can hold columns past the sequence
             float m = -CUDART_INF_F;
 #pragma unroll 1
             for (int c = 0; c < p.BN; c += CW) {
                 uint32_t acc[CW];
                 tmem_ld_x16(taddr + c, acc);
                 tmem_ld_wait_on(acc);
+                if (c + CW > p.T) {
 #pragma unroll
-                for (int j = 0; j < CW; ++j)
-                    if (c + j < p.T) m = fmaxf(m, __uint_as_float(acc[j]));
+                    for (int j = 0; j < CW; ++j)
+                        if (c + j >= p.T) acc[j] = 0xff800000u;          // -inf
+                }
+                float m4[4];
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4)
+                    m4[q4] = fmaxf(fmaxf(__uint_as_float(acc[4 * q4]), __uint_as_float(acc[4 * q4 + 1])),
+                                   fmaxf(__uint_as_float(acc[4 * q4 + 2]), __uint_as_float(acc[4 * q4 + 3])));
+                m = fmaxf(m, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
             }
-            float sum = 0.f;
+            // p = 2^(s * scale - m * scale): one fused multiply-add and one hardware exp2 per score
+            const float ms = -m * p.scale_log2;
+            f32x2 sum2 = 0ull;
 #pragma unroll 1
             for (int c = 0; c < p.BN; c += CW) {
                 uint32_t acc[CW];
                 tmem_ld_x16(taddr + c, acc);
                 tmem_ld_wait_on(acc);
+                if (c + CW > p.T) {
+#pragma unroll
+                    for (int j = 0; j < CW; ++j)
+                        if (c + j >= p.T) acc[j] = 0xff800000u;          // -inf: probability 0
+                }
                 uint32_t pk[8];
 #pragma unroll
                 for (int j2 = 0; j2 < 8; ++j2) {
-                    float p0 = exp2f((__uint_as_float(acc[2 * j2]) - m) * p.scale_log2);
-                    float p1 = exp2f((__uint_as_float(acc[2 * j2 + 1]) - m) * p.scale_log2);
-                    if (c + 2 * j2 >= p.T) p0 = 0.f;
-                    if (c + 2 * j2 + 1 >= p.T) p1 = 0.f;
-                    sum += p0 + p1;
+                    float p0, p1;
+                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(fmaf(__uint_as_float(acc[2 * j2]), p.scale_log2, ms)));
+                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(fmaf(__uint_as_float(acc[2 * j2 + 1]), p.scale_log2, ms)));
+                    sum2 = add2(sum2, pack2(p0, p1));
                     __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
                     pk[j2] = *reinterpret_cast<uint32_t*>(&hh);
                 }
@@ -243,6 +266,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(base + (((seg + 1) ^ (r & 7)) << 4)), "r"(pk[4]),
                              "r"(pk[5]), "r"(pk[6]), "r"(pk[7]) : "memory");
             }
+            float sum_lo, sum_hi;
+            unpack2(sum2, sum_lo, sum_hi);
+            const float sum = sum_lo + sum_hi;
             fence_proxy_async();
             tc_fence_before_sync();
             __syncwarp();

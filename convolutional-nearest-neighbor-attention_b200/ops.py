@@ -291,6 +291,8 @@ def _flat_rows(t: torch.Tensor) -> Tuple[torch.Tensor, int, int]:
     if t.dim() == 3:
         v, ld = _rows_view(t)
         return v, v.shape[0] * v.shape[1], ld
+    if t.dim() == 2 and t.stride(1) == 1 and t.stride(0) >= D:
+        return t, t.shape[0], t.stride(0)          # evenly strided rows, e.g. the class-token rows x[:, 0]
     t = t.contiguous()
     return t, t.numel() // D, D
 
