@@ -57,6 +57,8 @@ SIGNATURES = {
     "convnn_b200_linear": (ctypes.c_int, [ctypes.c_int, c_void, c_i64, c_void, c_void, c_void, c_i64, c_void, c_i64,
                                           c_i64, c_i32, c_i32, c_i32, c_void]),
     "convnn_b200_patchify": (ctypes.c_int, [ctypes.c_int, c_void, c_void, c_i32, c_i32, c_i32, c_i32, c_i32, c_void]),
+    "convnn_b200_patchify_u8": (ctypes.c_int, [ctypes.c_int, c_void, c_void, c_void, c_void, c_i32, c_i32, c_i32, c_i32,
+                                               c_i32, c_void]),
     "convnn_b200_embed_tokens": (ctypes.c_int, [ctypes.c_int, c_void, c_void, c_void, ctypes.c_float, c_void, c_void,
                                                 c_void, c_i32, c_i32, c_i32, c_void]),
     "convnn_b200_attention_workspace_bytes": (c_size, [ctypes.c_int, c_i32, c_i32, c_i32]),

@@ -374,6 +374,16 @@ int convnn_b200_patchify(int dtype, const void* img, void* out, int32_t B, int32
     return launch_patchify(dtype, img, out, B, C, Hh, Ww, P, static_cast<cudaStream_t>(stream));
 }
 
+int convnn_b200_patchify_u8(int dtype, const uint8_t* img, const float* mean, const float* inv_std, void* out, int32_t B,
+                            int32_t C, int32_t Hh, int32_t Ww, int32_t P, void* stream) {
+    if (dtype != CONVNN_F32 && dtype != CONVNN_BF16) return set_error(CONVNN_E_INVALID, "unknown dtype %d", dtype);
+    REQUIRE_PTR(img); REQUIRE_PTR(mean); REQUIRE_PTR(inv_std); REQUIRE_PTR(out);
+    if (B < 1 || C < 1 || Hh < 1 || Ww < 1 || P < 1) return set_error(CONVNN_E_INVALID, "patchify: bad shape");
+    int rc = check_device();
+    if (rc) return rc;
+    return launch_patchify_u8(dtype, img, mean, inv_std, out, B, C, Hh, Ww, P, static_cast<cudaStream_t>(stream));
+}
+
 int convnn_b200_linear(int dtype, const void* a, int64_t lda, const void* w, const void* bias, const void* residual,
                        int64_t ldr, void* out, int64_t ldo, int64_t M, int32_t N, int32_t K, int32_t gelu,
                        void* stream) {

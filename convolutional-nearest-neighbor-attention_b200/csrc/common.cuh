@@ -123,6 +123,8 @@ int launch_layernorm(int dtype, const void* x, long long ldx, const void* gamma,
                      long long ldy, long long rows, int D, const void* pe, const void* cls, int Np,
                      long long cls_rows, cudaStream_t st);
 int launch_patchify(int dtype, const void* img, void* out, int B, int C, int Hh, int Ww, int P, cudaStream_t st);
+int launch_patchify_u8(int dtype, const uint8_t* img, const float* mean, const float* inv_std, void* out, int B, int C,
+                       int Hh, int Ww, int P, cudaStream_t st);
 int launch_gather_rows(int dtype, const void* x, long long ldx, const int32_t* cand, void* xq, int B, int Tn, int S,
                        int D, cudaStream_t st);
 int launch_merge_heads(int dtype, const void* o, void* y, int B, int Tn, int H, int dk, cudaStream_t st);

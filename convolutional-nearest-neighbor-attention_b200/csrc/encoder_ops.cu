@@ -115,9 +115,12 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const T* __restrict__ x,
     }
 }
 
-// bfloat16 rows of at most 256 channels: one 16-byte vector per lane, arithmetic on packed fp32
-// pairs, affine parameters held in registers.  Same results as the generic kernel.
-__global__ void __launch_bounds__(256) layernorm_bf16_row256_kernel(
+// bfloat16 rows of at most 256 channels: one 16-byte vector per lane and row, arithmetic on packed
+// fp32 pairs, affine parameters held in registers.  Same results as the generic kernel.  A warp
+// works on R consecutive rows at a time and requests the next R while it does so: what bounds
+// the kernel is the number of bytes an SM has in flight, not its arithmetic.
+template <int R, int MINB>
+__global__ void __launch_bounds__(256, MINB) layernorm_bf16_row256_kernel(
     const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bfloat16* __restrict__ gamma,
     const __nv_bfloat16* __restrict__ beta, float eps, __nv_bfloat16* __restrict__ y, long long ldy, long long rows,
     int D) {
@@ -131,34 +134,58 @@ __global__ void __launch_bounds__(256) layernorm_bf16_row256_kernel(
         bf16x8_to_f32x2(act ? *reinterpret_cast<const uint4*>(gamma + lane * 8) : z, g2);
         bf16x8_to_f32x2(act ? *reinterpret_cast<const uint4*>(beta + lane * 8) : z, b2);
     }
-    const long long stride = (long long)gridDim.x * wpb;
-    long long r = blockIdx.x * wpb + (threadIdx.x >> 5);
-    uint4 nxt = make_uint4(0, 0, 0, 0);
-    if (act && r < rows) nxt = *reinterpret_cast<const uint4*>(x + r * ldx + lane * 8);
-    for (; r < rows; r += stride) {
-        f32x2 v2[4];
-        bf16x8_to_f32x2(nxt, v2);
-        if (act && r + stride < rows)                     // next row's load overlaps this row's arithmetic
-            nxt = *reinterpret_cast<const uint4*>(x + (r + stride) * ldx + lane * 8);
-        float s0, s1;
-        unpack2(add2(add2(v2[0], v2[1]), add2(v2[2], v2[3])), s0, s1);
-        const float mean = warp_sum(s0 + s1) * invD;
-        const f32x2 nm = pack2(-mean, -mean);
-        f32x2 d2[4], q2 = 0ull;
+    const long long stride = (long long)gridDim.x * wpb * R;
+    long long r0 = (blockIdx.x * wpb + (threadIdx.x >> 5)) * R;
+    uint4 nxt[R];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            d2[e] = add2(v2[e], nm);
-            q2 = fma2(d2[e], d2[e], q2);
+    for (int j = 0; j < R; ++j)
+        nxt[j] = (act && r0 + j < rows) ? *reinterpret_cast<const uint4*>(x + (r0 + j) * ldx + lane * 8) : make_uint4(0, 0, 0, 0);
+    for (; r0 < rows; r0 += stride) {
+        f32x2 d2[R][4];
+        float mean[R], q[R];
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+            bf16x8_to_f32x2(nxt[j], d2[j]);
+            float s0, s1;
+            unpack2(add2(add2(d2[j][0], d2[j][1]), add2(d2[j][2], d2[j][3])), s0, s1);
+            mean[j] = s0 + s1;
         }
-        float q0, q1;
-        unpack2(q2, q0, q1);
-        const float rstd = rsqrtf(warp_sum(act ? q0 + q1 : 0.f) * invD + eps);
-        if (act) {
-            const f32x2 r2 = pack2(rstd, rstd);
-            f32x2 o2[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) o2[e] = fma2(mul2(d2[e], r2), g2[e], b2[e]);
-            *reinterpret_cast<uint4*>(y + r * ldy + lane * 8) = f32x2_to_bf16x8(o2);
+        for (int j = 0; j < R; ++j)                        // next rows' loads overlap this group's arithmetic
+            if (act && r0 + stride + j < rows)
+                nxt[j] = *reinterpret_cast<const uint4*>(x + (r0 + stride + j) * ldx + lane * 8);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int j = 0; j < R; ++j) mean[j] += __shfl_xor_sync(0xffffffffu, mean[j], o);
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+            mean[j] *= invD;
+            const f32x2 nm = pack2(-mean[j], -mean[j]);
+            f32x2 q2 = 0ull;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                d2[j][e] = add2(d2[j][e], nm);
+                q2 = fma2(d2[j][e], d2[j][e], q2);
+            }
+            float q0, q1;
+            unpack2(q2, q0, q1);
+            q[j] = act ? q0 + q1 : 0.f;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int j = 0; j < R; ++j) q[j] += __shfl_xor_sync(0xffffffffu, q[j], o);
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+            const float rstd = rsqrtf(q[j] * invD + eps);
+            if (act && r0 + j < rows) {
+                const f32x2 r2 = pack2(rstd, rstd);
+                f32x2 o2[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) o2[e] = fma2(mul2(d2[j][e], r2), g2[e], b2[e]);
+                *reinterpret_cast<uint4*>(y + (r0 + j) * ldy + lane * 8) = f32x2_to_bf16x8(o2);
+            }
         }
     }
 }
@@ -184,6 +211,35 @@ __global__ void patchify_kernel(const T* __restrict__ img, T* __restrict__ out, 
         const T* src = img + (((b * C + c) * Hh + (py * P + i)) * (long long)Ww + px * P + jv * V);
         T* dst = out + ((b * Hp + py) * Wp + px) * (long long)(C * P * P) + (c * P + i) * P + jv * V;
         *reinterpret_cast<VT*>(dst) = *reinterpret_cast<const VT*>(src);
+    }
+}
+
+// The same unfold for images that are still 8-bit (what an image decoder hands over): the
+// loader's ToTensor + Normalize, out = (img / 255 - mean[c]) * inv_std[c], happens on the way.
+// VEC pixels of one patch row per thread (8: one 8-byte load, 16 / 32 bytes stored).
+template <typename T, int VEC>
+__global__ void patchify_u8_kernel(const uint8_t* __restrict__ img, const float* __restrict__ mean,
+                                   const float* __restrict__ inv_std, T* __restrict__ out, int B, int C, int Hh, int Ww,
+                                   int P, long long total_vec) {
+    const int Hp = Hh / P, Wp = Ww / P;
+    const int vec_per_prow = P / VEC;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total_vec;
+         e += (long long)gridDim.x * blockDim.x) {
+        long long t = e;
+        const int jv = (int)(t % vec_per_prow); t /= vec_per_prow;
+        const int i = (int)(t % P); t /= P;
+        const int c = (int)(t % C); t /= C;
+        const int px = (int)(t % Wp); t /= Wp;
+        const int py = (int)(t % Hp); t /= Hp;
+        const long long b = t;
+        const uint8_t* src = img + (((b * C + c) * Hh + (py * P + i)) * (long long)Ww + px * P + jv * VEC);
+        T* dst = out + ((b * Hp + py) * Wp + px) * (long long)(C * P * P) + (c * P + i) * P + jv * VEC;
+        const float m = mean[c], is = inv_std[c];
+        uint8_t raw[VEC];
+        if (VEC == 8) *reinterpret_cast<uint2*>(raw) = *reinterpret_cast<const uint2*>(src);
+        else raw[0] = src[0];
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) dst[k] = from_f32<T>(((float)raw[k] * (1.0f / 255.0f) - m) * is);
     }
 }
 
@@ -230,13 +286,14 @@ int launch_layernorm(int dtype, const void* x, long long ldx, const void* gamma,
         !aligned16(beta) || (pe && (!aligned16(pe) || !aligned16(cls))))
         return set_error(CONVNN_E_ALIGN, "layernorm: D, strides and pointers must be multiples of 16 bytes");
     if (dtype == CONVNN_BF16 && !pe && D <= 256) {
-        // Four 8-warp CTAs on every SM (a whole number per SM keeps the SMs level; about ten rows
-        // per warp amortise its load of the affine parameters): 11.6 us against 12.4 us with
-        // sixteen CTAs per SM at 50 k rows of 192 channels.
-        int blocks = (int)((rows + 7) / 8);
-        if (blocks > 148 * 4) blocks = 148 * 4;
+        // Two 8-warp CTAs per SM (the kernel keeps 121 registers: four rows in flight and four
+        // requested per warp), measured 9.6 us at 50 k rows of 192 channels against 11.0 us with
+        // one row per step and four CTAs per SM; register-capped variants that spill are twice as slow.
+        constexpr int R = 4, MINB = 2;
+        int blocks = (int)((rows + 8 * R - 1) / (8 * R));
+        if (blocks > 148 * MINB) blocks = 148 * MINB;
         if (blocks < 1) blocks = 1;
-        layernorm_bf16_row256_kernel<<<blocks, 256, 0, st>>>(
+        layernorm_bf16_row256_kernel<R, MINB><<<blocks, 256, 0, st>>>(
             static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(gamma),
             static_cast<const __nv_bfloat16*>(beta), eps, static_cast<__nv_bfloat16*>(y), ldy, rows, D);
         CONVNN_CHECK_LAUNCH("layernorm_bf16_row256");
@@ -245,6 +302,21 @@ int launch_layernorm(int dtype, const void* x, long long ldx, const void* gamma,
     if (dtype == CONVNN_F32)
         return ln_dispatch<float>(x, ldx, gamma, beta, eps, y, ldy, rows, D, pe, cls, Np, cls_rows, st);
     return ln_dispatch<__nv_bfloat16>(x, ldx, gamma, beta, eps, y, ldy, rows, D, pe, cls, Np, cls_rows, st);
+}
+
+int launch_patchify_u8(int dtype, const uint8_t* img, const float* mean, const float* inv_std, void* out, int B, int C,
+                       int Hh, int Ww, int P, cudaStream_t st) {
+    if (Hh % P != 0 || Ww % P != 0) return set_error(CONVNN_E_INVALID, "patchify: image not divisible into patches");
+    const bool v8 = P % 8 == 0 && Ww % 8 == 0 && (reinterpret_cast<uintptr_t>(img) & 7u) == 0 && aligned16(out);
+    const long long total = (long long)B * C * Hh * Ww / (v8 ? 8 : 1);
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > 148 * 32) blocks = 148 * 32;
+#define CONVNN_PU8(T, V) patchify_u8_kernel<T, V><<<blocks, 256, 0, st>>>(img, mean, inv_std, static_cast<T*>(out), B, C, Hh, Ww, P, total)
+    if (dtype == CONVNN_F32) { if (v8) CONVNN_PU8(float, 8); else CONVNN_PU8(float, 1); }
+    else { if (v8) CONVNN_PU8(__nv_bfloat16, 8); else CONVNN_PU8(__nv_bfloat16, 1); }
+#undef CONVNN_PU8
+    CONVNN_CHECK_LAUNCH("patchify_u8");
+    return CONVNN_OK;
 }
 
 int launch_patchify(int dtype, const void* img, void* out, int B, int C, int Hh, int Ww, int P, cudaStream_t st) {

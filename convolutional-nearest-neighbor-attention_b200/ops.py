@@ -326,20 +326,30 @@ def linear(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
 
 
 def patch_embed(images: torch.Tensor, conv_weight: torch.Tensor, conv_bias: torch.Tensor, norm_weight, norm_bias,
-                cls: torch.Tensor, pe: torch.Tensor, patch: int, eps: float = 1e-5) -> torch.Tensor:
+                cls: torch.Tensor, pe: torch.Tensor, patch: int, eps: float = 1e-5,
+                pixel_mean: Optional[torch.Tensor] = None, pixel_inv_std: Optional[torch.Tensor] = None) -> torch.Tensor:
     """PatchEmbedding + PositionalEncoding (reference vit.py:104-109, 126-135): unfold, GEMM
-    with the (D, C*P*P) weight view, LayerNorm, class token and positional table -> (B, T, D)."""
+    with the (D, C*P*P) weight view, LayerNorm, class token and positional table -> (B, T, D).
+    uint8 images are normalised on the way ((img / 255 - pixel_mean[c]) * pixel_inv_std[c], the
+    loader's ToTensor + Normalize, reference dataset.py:22-23) and computed in the weights' dtype."""
     _require_cuda(images, conv_weight)
     L = _capi.lib()
     B, C, Hh, Ww = images.shape
     D = conv_weight.shape[0]
     Np = (Hh // patch) * (Ww // patch)
-    dt = _dtype_code(images.dtype)
+    act = conv_weight.dtype if images.dtype == torch.uint8 else images.dtype
+    dt = _dtype_code(act)
     images = images.contiguous()
-    cols = torch.empty(B * Np, C * patch * patch, dtype=images.dtype, device=images.device)
-    _capi.check(L.convnn_b200_patchify(dt, images.data_ptr(), cols.data_ptr(), B, C, Hh, Ww, patch, _stream(images)))
+    cols = torch.empty(B * Np, C * patch * patch, dtype=act, device=images.device)
+    if images.dtype == torch.uint8:
+        if pixel_mean is None or pixel_inv_std is None:
+            raise ValueError("uint8 images need pixel_mean and pixel_inv_std (float32, one value per channel)")
+        _capi.check(L.convnn_b200_patchify_u8(dt, images.data_ptr(), pixel_mean.data_ptr(), pixel_inv_std.data_ptr(),
+                                              cols.data_ptr(), B, C, Hh, Ww, patch, _stream(images)))
+    else:
+        _capi.check(L.convnn_b200_patchify(dt, images.data_ptr(), cols.data_ptr(), B, C, Hh, Ww, patch, _stream(images)))
     proj = linear(cols, conv_weight.reshape(D, -1), conv_bias)
-    out = torch.empty(B, Np + 1, D, dtype=images.dtype, device=images.device)
+    out = torch.empty(B, Np + 1, D, dtype=act, device=images.device)
     pe2 = pe.reshape(-1, D)[: Np + 1].contiguous()
     _capi.check(L.convnn_b200_embed_tokens(dt, proj.data_ptr(), norm_weight.data_ptr(), norm_bias.data_ptr(), float(eps),
                                            cls.reshape(-1).contiguous().data_ptr(), pe2.data_ptr(), out.data_ptr(),

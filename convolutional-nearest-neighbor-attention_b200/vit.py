@@ -45,8 +45,9 @@ class PatchEmbedding(nn.Module):
 
 
 def _library_path(x: torch.Tensor) -> bool:
-    """The fused encoder ops cover CUDA float32 / bfloat16 inference."""
-    return x.is_cuda and x.dtype in (torch.float32, torch.bfloat16) and not torch.is_grad_enabled()
+    """The fused encoder ops cover CUDA float32 / bfloat16 inference (and, for the model input,
+    8-bit images that the patch unfold normalises on the way)."""
+    return x.is_cuda and x.dtype in (torch.float32, torch.bfloat16, torch.uint8) and not torch.is_grad_enabled()
 
 
 class PositionalEncoding(nn.Module):
@@ -126,14 +127,27 @@ class ViT(nn.Module):
                                args.attention_dropout) for _ in range(args.num_layers)])
         self.classifier = nn.Linear(args.d_hidden, args.num_classes)
         self.device = getattr(args, "device", "cuda")
+        # Normalisation applied to uint8 inputs (plain attributes, not buffers: the state_dict stays
+        # the reference's).  Defaults: the ImageNet statistics of the reference's loader (dataset.py:23).
+        self.pixel_mean = (0.485, 0.456, 0.406)
+        self.pixel_std = (0.229, 0.224, 0.225)
+        self._pixel_stats = None
         self.name = f"VIT {args.layer}"
         self.to(self.device)
 
     def forward(self, x):
         if _library_path(x):
             pe_mod, pemb = self.positional_encoding, self.patch_embedding
+            mean = inv_std = None
+            if x.dtype == torch.uint8:
+                key = (tuple(self.pixel_mean), tuple(self.pixel_std), x.device)
+                if self._pixel_stats is None or self._pixel_stats[0] != key:
+                    self._pixel_stats = (key, torch.tensor(self.pixel_mean, dtype=torch.float32, device=x.device),
+                                         1.0 / torch.tensor(self.pixel_std, dtype=torch.float32, device=x.device))
+                _, mean, inv_std = self._pixel_stats
             x = ops.patch_embed(x, pemb.linear_projection.weight, pemb.linear_projection.bias, pemb.norm.weight,
-                                pemb.norm.bias, pe_mod.cls_tokens, pe_mod.pe, self.args.patch_size, pemb.norm.eps)
+                                pemb.norm.bias, pe_mod.cls_tokens, pe_mod.pe, self.args.patch_size, pemb.norm.eps,
+                                pixel_mean=mean, pixel_inv_std=inv_std)
             x = self.transformer_encoder(x)
             return ops.linear(x[:, 0], self.classifier.weight, self.classifier.bias)
         x = self.positional_encoding(self.patch_embedding(x))

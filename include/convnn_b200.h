@@ -221,6 +221,13 @@ int convnn_b200_linear(int dtype, const void* a, int64_t lda, const void* w, con
 int convnn_b200_patchify(int dtype, const void* img, void* out, int32_t B, int32_t C, int32_t Hh,
                          int32_t Ww, int32_t P, void* stream);
 
+/* The same unfold for images that are still 8-bit, with the loader's ToTensor + Normalize
+ * (reference dataset.py:22-23, 73-74, 84-85) applied on the way: out = (img / 255 - mean[c]) *
+ * inv_std[c] in `dtype`.  img (B, C, Hh, Ww) uint8, mean / inv_std (C) float32, all DEVICE
+ * pointers.  Lets a caller ship a quarter of the bytes of float32 images over PCIe. */
+int convnn_b200_patchify_u8(int dtype, const uint8_t* img, const float* mean, const float* inv_std, void* out,
+                            int32_t B, int32_t C, int32_t Hh, int32_t Ww, int32_t P, void* stream);
+
 /* Embedding tail: out[b, 0] = cls + pe[0]; out[b, 1 + n] = LayerNorm(proj[b, n]) + pe[1 + n]
  * (PatchEmbedding.norm, class token and positional table: vit.py:108, 126-135).
  * proj (B, Np, D), cls (D), pe (Np + 1, D), out (B, Np + 1, D), all contiguous. */

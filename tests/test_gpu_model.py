@@ -192,6 +192,44 @@ def test_encoder_ops_match_torch(dtype, tol):
     assert rel_err(got, ref) < max(tol, 6e-3 if dtype == torch.bfloat16 else tol)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_uint8_images_are_normalised_in_the_unfold(dtype):
+    """8-bit images through convnn_b200_patchify_u8 equal the float path fed with the loader's
+    ToTensor + Normalize of the same pixels (reference dataset.py:22-23)."""
+    g = torch.Generator().manual_seed(1)
+    cfg, sd, _, _ = vit_case("vit_tiny_cifar_convnn")
+    model = build_vit(cfg, sd, dtype)
+    img8 = torch.randint(0, 256, (3, *cfg.img_size), generator=g, dtype=torch.uint8)
+    mean = torch.tensor(model.pixel_mean).view(1, 3, 1, 1)
+    std = torch.tensor(model.pixel_std).view(1, 3, 1, 1)
+    as_float = ((img8.float() / 255.0 - mean) / std)
+    with torch.no_grad():
+        got = model(img8.to(DEV))
+        want = model(as_float.to(DEV, dtype))
+    # the float path rounds the normalised pixels to `dtype` on the host side, the 8-bit path in the
+    # kernel: same values up to the last place of (x/255 - m) * (1/s) against (x/255 - m) / s
+    assert rel_err(got, want) < (1e-4 if dtype == torch.float32 else 3e-2)
+
+
+def test_logits_gather_groups_batches_in_order():
+    """One rank: LogitsGather only collects; groups complete every `batches_per_flush` adds, a
+    final partial group comes out of drain(), slots alternate without losing a batch."""
+    from convnn_b200.sharded import LogitsGather
+    gth = LogitsGather(1, 3, 4, 5, torch.float32, torch.device(DEV))
+    batches = [torch.full((4, 5), float(i), device=DEV) for i in range(8)]
+    groups = []
+    for b in batches:
+        done = gth.add(b)
+        if done is not None:
+            groups.append(done[0].clone())
+    gth.drain()
+    groups.append(gth.last[0].clone())
+    torch.cuda.synchronize()
+    assert [g.shape[0] for g in groups] == [3, 3, 2]
+    seen = torch.cat([g[:, 0, 0] for g in groups]).tolist()
+    assert seen == [float(i) for i in range(8)]
+
+
 def test_residual_is_folded_into_the_output_projection():
     cfg = ConvNNConfig(d_hidden=192, num_heads=1, K=9, magnitude_type="cosine")
     w = {n: bf16_round(t) for n, t in make_layer_weights(cfg, seed=5).items()}
