@@ -61,6 +61,20 @@ SIGNATURES = {
                                                c_i32, c_void]),
     "convnn_b200_embed_tokens": (ctypes.c_int, [ctypes.c_int, c_void, c_void, c_void, ctypes.c_float, c_void, c_void,
                                                 c_void, c_i32, c_i32, c_i32, c_void]),
+    "convnn_b200_moment_planes": (ctypes.c_int, [c_i32]),
+    "convnn_b200_moment_stride": (c_i64, [c_i64]),
+    "convnn_b200_prenorm_linear_supported": (ctypes.c_int, [c_i32, c_i32, c_i32]),
+    "convnn_b200_prenorm_forward_supported": (ctypes.c_int, [ctypes.POINTER(ConvnnDesc)]),
+    "convnn_b200_row_moments": (ctypes.c_int, [c_void, c_i64, c_i64, c_i32, c_void, c_void]),
+    "convnn_b200_fold_layernorm": (ctypes.c_int, [c_void, c_void, c_void, c_void, c_i32, c_i32, c_void, c_void,
+                                                  c_void]),
+    "convnn_b200_prenorm_linear": (ctypes.c_int, [c_void, c_i64, c_void, c_i32, ctypes.c_float, c_void, c_void, c_void,
+                                                  c_i64, c_i64, c_i32, c_i32, c_i32, c_void]),
+    "convnn_b200_linear_moments": (ctypes.c_int, [c_void, c_i64, c_void, c_void, c_void, c_i64, c_void, c_i64, c_i64,
+                                                  c_i32, c_i32, c_void, c_void]),
+    "convnn_b200_prenorm_forward": (ctypes.c_int, [ctypes.POINTER(ConvnnDesc), c_void, c_i64, c_void, c_i32,
+                                                   ctypes.c_float, c_void, c_void, c_void, c_void, c_void, c_void, c_i64,
+                                                   c_void, c_i64, c_void, c_void, c_size, c_void]),
     "convnn_b200_attention_workspace_bytes": (c_size, [ctypes.c_int, c_i32, c_i32, c_i32]),
     "convnn_b200_softmax_attention": (ctypes.c_int, [ctypes.c_int, c_void, c_i64, c_void, c_void, c_void, c_i64, c_i32,
                                                      c_i32, c_i32, c_i32, c_void, c_size, c_void]),

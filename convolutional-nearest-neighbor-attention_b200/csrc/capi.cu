@@ -190,9 +190,27 @@ size_t convnn_b200_workspace_bytes(const convnn_desc* d) {
     return carve(dm, d->conv_type, nullptr).total;
 }
 
-int convnn_b200_qkv_proj(const convnn_desc* d, const void* x, int64_t ldx, const void* w_qkv,
-                         const int32_t* cand, void* q, void* k, void* v, float* qstat, float* kstat,
-                         void* scratch, void* stream) {
+}  // extern "C"
+
+namespace {
+// Pre-norm fold of the layer's first GEMM: x holds the rows before norm1, w_qkv the folded weight.
+struct PreNorm {
+    const float* moments;
+    int planes;
+    float eps;
+    const void* w_extra;
+};
+
+bool qkv_fold_supported(const convnn_desc* d, const Dims& dm) {
+    if (d->dtype != CONVNN_BF16 || d->coord || d->sampled || force_simt()) return false;
+    const bool stats = d->metric != CONVNN_MATMUL;
+    if (stats && gemm_tc_stat_pieces(dm.D, dm.dk) != 1) return false;
+    return gemm_tc_prenorm_supported(3 * dm.D, dm.D, 3, stats, false);
+}
+
+int qkv_proj_impl(const convnn_desc* d, const void* x, int64_t ldx, const void* w_qkv,
+                  const int32_t* cand, void* q, void* k, void* v, float* qstat, float* kstat,
+                  void* scratch, void* stream, const PreNorm* pn) {
     Dims dm;
     int rc = validate(d, &dm);
     if (rc) return rc;
@@ -223,6 +241,12 @@ int convnn_b200_qkv_proj(const convnn_desc* d, const void* x, int64_t ldx, const
         GemmTcOpts o;
         o.stat_mode = d->metric; o.dk = dm.dk; o.heads = dm.H;
         bool done = false;
+        if (pn) {
+            if (!qkv_fold_supported(d, dm) || !gemm_tc_supported(x, ldx, w_qkv, dm.D, 3 * dm.D, 3, kvq, dm.D))
+                return set_error(CONVNN_E_UNSUPPORTED, "prenorm_forward: this descriptor takes the unfused path "
+                                                       "(see convnn_b200_prenorm_forward_supported)");
+            o.ln_moments = pn->moments; o.ln_planes = pn->planes; o.ln_eps = pn->eps; o.ln_wextra = pn->w_extra;
+        }
         if (!d->sampled && gemm_tc_supported(x, ldx, w_qkv, dm.D, 3 * dm.D, 3, kvq, dm.D)) {
             if (fuse) { o.stat[0] = kstat; o.stat[2] = qstat; o.rows_per_batch = dm.T; o.stat_scratch = sc_k; }
             if ((rc = launch_gemm_tc(x, ldx, w_qkv, dm.B * dm.T, 3 * dm.D, dm.D, 3, kvq, dm.D, o, st))) return rc;
@@ -245,6 +269,7 @@ int convnn_b200_qkv_proj(const convnn_desc* d, const void* x, int64_t ldx, const
             return launch_head_fill_and_stats(d, dm, k, dm.T, kstat, st);
         }
     }
+    if (pn) return set_error(CONVNN_E_UNSUPPORTED, "prenorm_forward: this descriptor takes the unfused path");
     GemmParams p{};
     p.a = x; p.lda = ldx; p.bias = nullptr; p.N = dm.D; p.Kd = dm.D;
     p.a_mode = A_TOKENS; p.c_mode = C_HEADS; p.T = dm.T; p.H = dm.H; p.dk = dm.dk; p.Cp = dm.Cp; p.gelu = 0;
@@ -262,6 +287,15 @@ int convnn_b200_qkv_proj(const convnn_desc* d, const void* x, int64_t ldx, const
     if ((rc = launch_head_fill_and_stats(d, dm, k, dm.T, stats ? kstat : nullptr, st))) return rc;
     if ((rc = launch_head_fill_and_stats(d, dm, v, dm.T, nullptr, st))) return rc;
     return CONVNN_OK;
+}
+}  // namespace
+
+extern "C" {
+
+int convnn_b200_qkv_proj(const convnn_desc* d, const void* x, int64_t ldx, const void* w_qkv,
+                         const int32_t* cand, void* q, void* k, void* v, float* qstat, float* kstat,
+                         void* scratch, void* stream) {
+    return qkv_proj_impl(d, x, ldx, w_qkv, cand, q, k, v, qstat, kstat, scratch, stream, nullptr);
 }
 
 int convnn_b200_sim_topk(const convnn_desc* d, const void* q, const void* k, const float* qstat,
@@ -291,8 +325,11 @@ int convnn_b200_gather_conv(const convnn_desc* d, const void* v, const int32_t* 
     return launch_gather_conv_simt(d, dm, v, idx, val, w_conv, w_pw, o, scratch, static_cast<cudaStream_t>(stream));
 }
 
-int convnn_b200_out_proj(const convnn_desc* d, const void* o, const void* w_o, const void* residual, int64_t ldr,
-                         void* out, int64_t ldo, void* scratch, void* stream) {
+}  // extern "C"
+
+namespace {
+int out_proj_impl(const convnn_desc* d, const void* o, const void* w_o, const void* residual, int64_t ldr,
+                  void* out, int64_t ldo, void* scratch, void* stream, float* moments_out) {
     Dims dm;
     int rc = validate(d, &dm);
     if (rc) return rc;
@@ -304,7 +341,7 @@ int convnn_b200_out_proj(const convnn_desc* d, const void* o, const void* w_o, c
         cudaStream_t st = static_cast<cudaStream_t>(stream);
         void* cs[1] = {out};
         GemmTcOpts go;
-        go.residual = residual; go.ldr = ldr;
+        go.residual = residual; go.ldr = ldr; go.moments_out = moments_out;
         const bool res_ok = !residual || (ldr % 8 == 0 && aligned16(residual));
         if (res_ok && dm.H == 1 && gemm_tc_supported(o, dm.D, w_o, dm.D, dm.D, 1, cs, ldo))
             return launch_gemm_tc(o, dm.D, w_o, dm.B * dm.T, dm.D, dm.D, 1, cs, ldo, go, st);
@@ -313,6 +350,7 @@ int convnn_b200_out_proj(const convnn_desc* d, const void* o, const void* w_o, c
             return launch_gemm_tc(scratch, dm.D, w_o, dm.B * dm.T, dm.D, dm.D, 1, cs, ldo, go, st);
         }
     }
+    if (moments_out) return set_error(CONVNN_E_UNSUPPORTED, "out_proj: row moments need the tensor-core path");
     GemmParams p{};
     p.a = o; p.w = w_o; p.bias = nullptr; p.c = out; p.cand = nullptr;
     p.lda = dm.D; p.ldc = ldo; p.M = dm.B * dm.T; p.N = dm.D; p.Kd = dm.D;
@@ -320,6 +358,14 @@ int convnn_b200_out_proj(const convnn_desc* d, const void* o, const void* w_o, c
     p.rows_per_batch = dm.T; p.T = dm.T; p.H = dm.H; p.dk = dm.dk; p.Cp = dm.Cp; p.gelu = 0;
     p.residual = residual; p.ldr = ldr;
     return launch_gemm_simt(d->dtype, p, static_cast<cudaStream_t>(stream));
+}
+}  // namespace
+
+extern "C" {
+
+int convnn_b200_out_proj(const convnn_desc* d, const void* o, const void* w_o, const void* residual, int64_t ldr,
+                         void* out, int64_t ldo, void* scratch, void* stream) {
+    return out_proj_impl(d, o, w_o, residual, ldr, out, ldo, scratch, stream, nullptr);
 }
 
 int convnn_b200_forward(const convnn_desc* d, const void* x, int64_t ldx, const void* w_qkv,
@@ -410,6 +456,101 @@ int convnn_b200_linear(int dtype, const void* a, int64_t lda, const void* w, con
     p.a_mode = A_ROWS; p.c_mode = C_ROWS; p.rows_per_batch = 1; p.T = 1; p.H = 1; p.dk = N; p.Cp = N;
     p.gelu = gelu; p.residual = residual; p.ldr = ldr;
     return launch_gemm_simt(dtype, p, st);
+}
+
+// ---- LayerNorm folded into the GEMM that consumes it ----------------------------------------------
+
+int convnn_b200_moment_planes(int32_t N) { return N < 1 ? 0 : gemm_tc_moment_planes(N); }
+int64_t convnn_b200_moment_stride(int64_t M) { return M < 0 ? 0 : gemm_tc_moment_stride(M); }
+
+int convnn_b200_prenorm_linear_supported(int32_t N, int32_t K, int32_t gelu) {
+    return (N >= 1 && K >= 1 && !force_simt() && gemm_tc_prenorm_supported(N, K, 1, false, gelu != 0)) ? 1 : 0;
+}
+
+int convnn_b200_prenorm_forward_supported(const convnn_desc* d) {
+    Dims dm;
+    if (validate(d, &dm) != CONVNN_OK) return 0;
+    return qkv_fold_supported(d, dm) ? 1 : 0;
+}
+
+int convnn_b200_row_moments(const void* x, int64_t ldx, int64_t rows, int32_t D, float* moments, void* stream) {
+    REQUIRE_PTR(x); REQUIRE_PTR(moments);
+    if (rows < 0 || D < 1 || ldx < D) return set_error(CONVNN_E_INVALID, "row_moments: bad shape");
+    int rc = check_device();
+    if (rc) return rc;
+    if (rows == 0) return CONVNN_OK;
+    return launch_row_moments(x, ldx, rows, D, moments, static_cast<cudaStream_t>(stream));
+}
+
+int convnn_b200_fold_layernorm(const void* w, const void* bias, const void* gamma, const void* beta, int32_t N,
+                               int32_t K, void* w_folded, void* w_extra, void* stream) {
+    REQUIRE_PTR(w); REQUIRE_PTR(gamma); REQUIRE_PTR(beta); REQUIRE_PTR(w_folded); REQUIRE_PTR(w_extra);
+    if (N < 1 || K < 1) return set_error(CONVNN_E_INVALID, "fold_layernorm: bad shape");
+    int rc = check_device();
+    if (rc) return rc;
+    return launch_fold_layernorm(w, bias, gamma, beta, N, K, w_folded, w_extra, static_cast<cudaStream_t>(stream));
+}
+
+int convnn_b200_prenorm_linear(const void* a, int64_t lda, const float* moments, int32_t planes, float eps,
+                               const void* w_folded, const void* w_extra, void* out, int64_t ldo, int64_t M,
+                               int32_t N, int32_t K, int32_t gelu, void* stream) {
+    REQUIRE_PTR(a); REQUIRE_PTR(moments); REQUIRE_PTR(w_folded); REQUIRE_PTR(w_extra); REQUIRE_PTR(out);
+    if (M < 0 || N < 1 || K < 1 || lda < K || ldo < N || planes < 1 || M >= (1ll << 31))
+        return set_error(CONVNN_E_INVALID, "prenorm_linear: bad shape (M=%lld N=%d K=%d planes=%d)", (long long)M, N, K, planes);
+    int rc = check_device();
+    if (rc) return rc;
+    if (M == 0) return CONVNN_OK;
+    void* cs[1] = {out};
+    if (force_simt() || !gemm_tc_supported(a, lda, w_folded, K, N, 1, cs, ldo) ||
+        !gemm_tc_prenorm_supported(N, K, 1, false, gelu != 0))
+        return set_error(CONVNN_E_UNSUPPORTED, "prenorm_linear: N=%d K=%d takes the unfused path "
+                                               "(see convnn_b200_prenorm_linear_supported)", N, K);
+    GemmTcOpts o;
+    o.gelu = gelu;
+    o.ln_moments = moments; o.ln_planes = planes; o.ln_eps = eps; o.ln_wextra = w_extra;
+    return launch_gemm_tc(a, lda, w_folded, (int)M, N, K, 1, cs, ldo, o, static_cast<cudaStream_t>(stream));
+}
+
+int convnn_b200_linear_moments(const void* a, int64_t lda, const void* w, const void* bias, const void* residual,
+                               int64_t ldr, void* out, int64_t ldo, int64_t M, int32_t N, int32_t K,
+                               float* moments_out, void* stream) {
+    REQUIRE_PTR(a); REQUIRE_PTR(w); REQUIRE_PTR(residual); REQUIRE_PTR(out); REQUIRE_PTR(moments_out);
+    if (M < 0 || N < 1 || K < 1 || lda < K || ldo < N || ldr < N || M >= (1ll << 31))
+        return set_error(CONVNN_E_INVALID, "linear_moments: bad shape (M=%lld N=%d K=%d)", (long long)M, N, K);
+    int rc = check_device();
+    if (rc) return rc;
+    if (M == 0) return CONVNN_OK;
+    void* cs[1] = {out};
+    const bool extra_ok = (!bias || aligned16(bias)) && aligned16(residual) && ldr % 8 == 0 &&
+                          (reinterpret_cast<uintptr_t>(moments_out) & 7u) == 0;
+    if (force_simt() || !extra_ok || !gemm_tc_supported(a, lda, w, K, N, 1, cs, ldo))
+        return set_error(CONVNN_E_UNSUPPORTED, "linear_moments: needs the bfloat16 tensor-core path");
+    GemmTcOpts o;
+    o.bias = bias; o.residual = residual; o.ldr = ldr; o.moments_out = moments_out;
+    return launch_gemm_tc(a, lda, w, (int)M, N, K, 1, cs, ldo, o, static_cast<cudaStream_t>(stream));
+}
+
+int convnn_b200_prenorm_forward(const convnn_desc* d, const void* x, int64_t ldx, const float* moments,
+                                int32_t planes, float eps, const void* w_qkv_folded, const void* w_qkv_extra,
+                                const void* w_conv, const void* w_pw, const void* w_o, const void* residual,
+                                int64_t ldr, void* out, int64_t ldo, float* moments_out, void* workspace,
+                                size_t workspace_bytes, void* stream) {
+    Dims dm;
+    int rc = validate(d, &dm);
+    if (rc) return rc;
+    REQUIRE_PTR(workspace); REQUIRE_PTR(moments); REQUIRE_PTR(w_qkv_extra);
+    if (planes < 1) return set_error(CONVNN_E_INVALID, "prenorm_forward: planes must be positive");
+    if (moments_out && !residual)
+        return set_error(CONVNN_E_UNSUPPORTED, "prenorm_forward: row moments come with the skip connection");
+    if (!aligned16(workspace)) return set_error(CONVNN_E_ALIGN, "workspace must be 16-byte aligned");
+    Workspace w = carve(dm, d->conv_type, workspace);
+    if (workspace_bytes < w.total)
+        return set_error(CONVNN_E_WORKSPACE, "workspace has %zu bytes, %zu needed", workspace_bytes, w.total);
+    const PreNorm pn{moments, planes, eps, w_qkv_extra};
+    if ((rc = qkv_proj_impl(d, x, ldx, w_qkv_folded, nullptr, w.q, w.k, w.v, w.qstat, w.kstat, w.scratch, stream, &pn))) return rc;
+    if ((rc = convnn_b200_sim_topk(d, w.q, w.k, w.qstat, w.kstat, nullptr, w.idx, w.val, stream))) return rc;
+    if ((rc = convnn_b200_gather_conv(d, w.v, w.idx, w.val, w_conv, w_pw, w.o, w.scratch, stream))) return rc;
+    return out_proj_impl(d, w.o, w_o, residual, ldr, out, ldo, w.scratch, stream, moments_out);
 }
 
 // ---- the other halves of the branching wrappers ------------------------------------------------

@@ -112,7 +112,19 @@ struct GemmTcOpts {
     // heads wider than a tile: room for gemm_tc_stat_pieces() x M x heads floats per part with a
     // statistic (the tiles' partial sums, combined by a second small kernel)
     float* stat_scratch = nullptr;
+    // Pre-norm fold: `a` holds the rows BEFORE their LayerNorm, `w` is W * diag(gamma) and ln_wextra
+    // the (N, 16) extra rows of fold_layernorm(); ln_moments = [ln_planes][gemm_tc_moment_stride(M)][2]
+    // partial (sum, sum of squares) of the rows of a.  No bias / skip connection (the bias is folded).
+    const float* ln_moments = nullptr;
+    int ln_planes = 0;
+    float ln_eps = 0.f;
+    const void* ln_wextra = nullptr;
+    // Row moments of the stored rows, [gemm_tc_moment_planes(N)][gemm_tc_moment_stride(M)][2]; needs a skip connection.
+    float* moments_out = nullptr;
 };
+bool gemm_tc_prenorm_supported(int N, int Kd, int parts, bool has_stat, bool gelu);
+int gemm_tc_moment_planes(int N);
+long long gemm_tc_moment_stride(long long M);   // entries between the planes of a moments buffer
 bool gemm_tc_can_fuse_stats(int part_cols, int dk);
 // Column tiles a head is spread over when the statistic is fused: 1 = a tile holds whole heads,
 // m >= 2 = each head spans m tiles (partial sums + combine), 0 = cannot be fused.
@@ -122,6 +134,9 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
 int launch_layernorm(int dtype, const void* x, long long ldx, const void* gamma, const void* beta, float eps, void* y,
                      long long ldy, long long rows, int D, const void* pe, const void* cls, int Np,
                      long long cls_rows, cudaStream_t st);
+int launch_row_moments(const void* x, long long ldx, long long rows, int D, float* moments, cudaStream_t st);
+int launch_fold_layernorm(const void* w, const void* bias, const void* gamma, const void* beta, int N, int K,
+                          void* w_folded, void* w_extra, cudaStream_t st);
 int launch_patchify(int dtype, const void* img, void* out, int B, int C, int Hh, int Ww, int P, cudaStream_t st);
 int launch_patchify_u8(int dtype, const uint8_t* img, const float* mean, const float* inv_std, void* out, int B, int C,
                        int Hh, int Ww, int P, cudaStream_t st);

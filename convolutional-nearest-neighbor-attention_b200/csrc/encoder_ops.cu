@@ -304,6 +304,86 @@ int launch_layernorm(int dtype, const void* x, long long ldx, const void* gamma,
     return ln_dispatch<__nv_bfloat16>(x, ldx, gamma, beta, eps, y, ldy, rows, D, pe, cls, Np, cls_rows, st);
 }
 
+namespace {
+// One warp per row: (sum, sum of squares) of a bfloat16 row, what the pre-norm fold of the GEMM
+// needs from the producer of its rows.  Used once per forward (the rows the embedding wrote); every
+// later set of moments comes out of a GEMM epilogue.
+__global__ void __launch_bounds__(256) row_moments_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+                                                          long long rows, int D, float2* __restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    float s1 = 0.f, s2 = 0.f;
+    for (int c = lane * 8; c < D; c += 256) {
+        const uint4 v = *reinterpret_cast<const uint4*>(x + r * ldx + c);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float lo = __uint_as_float(w[e] << 16), hi = __uint_as_float(w[e] & 0xffff0000u);
+            s1 += lo + hi;
+            s2 = fmaf(hi, hi, fmaf(lo, lo, s2));
+        }
+    }
+    s1 = warp_sum(s1);
+    s2 = warp_sum(s2);
+    if (lane == 0) out[r] = make_float2(s1, s2);
+}
+
+// One warp per output row n of a Linear that follows a LayerNorm: w_folded[n, k] = round(w[n, k] *
+// gamma[k]) and the 16-element extra row [c_hi, c_hi, c_lo, c_lo, b_hi, b_hi, b_lo, b_lo, 0 x 8] with
+// c = sum_k w_folded[n, k] (of the ROUNDED products, so that x W'^T - mean c cancels exactly) and
+// b = sum_k w[n, k] beta[k] + bias[n], each as a bfloat16 hi + lo pair.
+__global__ void __launch_bounds__(256) fold_layernorm_kernel(const __nv_bfloat16* __restrict__ w,
+                                                             const __nv_bfloat16* __restrict__ bias,
+                                                             const __nv_bfloat16* __restrict__ gamma,
+                                                             const __nv_bfloat16* __restrict__ beta, int N, int K,
+                                                             __nv_bfloat16* __restrict__ wf,
+                                                             __nv_bfloat16* __restrict__ wx) {
+    const int lane = threadIdx.x & 31;
+    const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (n >= N) return;
+    float c = 0.f, b = 0.f;
+    for (int k = lane; k < K; k += 32) {
+        const float wv = __bfloat162float(w[(long long)n * K + k]);
+        const __nv_bfloat16 f = __float2bfloat16_rn(wv * __bfloat162float(gamma[k]));
+        wf[(long long)n * K + k] = f;
+        c += __bfloat162float(f);
+        b = fmaf(wv, __bfloat162float(beta[k]), b);
+    }
+    c = warp_sum(c);
+    b = warp_sum(b);
+    if (lane == 0) {
+        if (bias) b += __bfloat162float(bias[n]);
+        const __nv_bfloat16 ch = __float2bfloat16_rn(c), bh = __float2bfloat16_rn(b);
+        const __nv_bfloat16 cl = __float2bfloat16_rn(c - __bfloat162float(ch));
+        const __nv_bfloat16 bl = __float2bfloat16_rn(b - __bfloat162float(bh));
+        const __nv_bfloat16 z = __float2bfloat16_rn(0.f);
+        const __nv_bfloat16 row[16] = {ch, ch, cl, cl, bh, bh, bl, bl, z, z, z, z, z, z, z, z};
+#pragma unroll
+        for (int j = 0; j < 16; ++j) wx[(long long)n * 16 + j] = row[j];
+    }
+}
+}  // namespace
+
+int launch_row_moments(const void* x, long long ldx, long long rows, int D, float* moments, cudaStream_t st) {
+    if (D % 8 != 0 || ldx % 8 != 0 || !aligned16(x) || (reinterpret_cast<uintptr_t>(moments) & 7u))
+        return set_error(CONVNN_E_ALIGN, "row_moments: D and ldx must be multiples of 8 elements, x 16-byte aligned");
+    row_moments_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), ldx, rows, D,
+                                                                  reinterpret_cast<float2*>(moments));
+    CONVNN_CHECK_LAUNCH("row_moments");
+    return CONVNN_OK;
+}
+
+int launch_fold_layernorm(const void* w, const void* bias, const void* gamma, const void* beta, int N, int K,
+                          void* w_folded, void* w_extra, cudaStream_t st) {
+    fold_layernorm_kernel<<<(N + 7) / 8, 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(w), static_cast<const __nv_bfloat16*>(bias),
+        static_cast<const __nv_bfloat16*>(gamma), static_cast<const __nv_bfloat16*>(beta), N, K,
+        static_cast<__nv_bfloat16*>(w_folded), static_cast<__nv_bfloat16*>(w_extra));
+    CONVNN_CHECK_LAUNCH("fold_layernorm");
+    return CONVNN_OK;
+}
+
 int launch_patchify_u8(int dtype, const uint8_t* img, const float* mean, const float* inv_std, void* out, int B, int C,
                        int Hh, int Ww, int P, cudaStream_t st) {
     if (Hh % P != 0 || Ww % P != 0) return set_error(CONVNN_E_INVALID, "patchify: image not divisible into patches");

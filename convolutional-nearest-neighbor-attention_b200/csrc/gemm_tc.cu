@@ -18,6 +18,17 @@
 // preloads the accumulator with it.
 // The N range may be split into up to three equal parts with their own output tensors,
 // which lets one launch produce k, v and q from the packed [W_k; W_v; W_q].
+// Pre-norm fold (LNF): the GEMM consumes the rows x BEFORE their LayerNorm.  With W' = W * diag(gamma),
+// c[n] = sum_k W'[n,k] and b'[n] = sum_k W[n,k] beta[k] + bias[n],
+//   LayerNorm(x) W^T + bias = rstd * (x W'^T - mean * c + sigma * b'),    sigma = 1 / rstd,
+// so the normalised rows are never written or read.  The row moments (sum x, sum x^2; produced by
+// the kernel that wrote x, see MOM) are turned by one extra warp into a 128 x 16 operand chunk
+// [-mean_hi, -mean_lo, -mean_hi, -mean_lo, sigma_hi, sigma_lo, sigma_hi, sigma_lo] (bfloat16 hi + lo
+// splits, both 16-byte halves alike) that one extra K = 16 MMA per tile multiplies with the
+// matching [c_hi, c_hi, c_lo, c_lo, b'_hi, b'_hi, b'_lo, b'_lo | 0 ...] rows fetched with the W tile;
+// the epilogue multiplies by rstd.
+// Row moments out (MOM): the epilogue of a GEMM with a skip connection also emits, per row and per
+// (column tile, column half), the sum and the sum of squares of the values it stored.
 // Every mbarrier wait is bounded (see sm100.cuh); an expiry latches the device status.
 #include <atomic>
 
@@ -45,6 +56,8 @@ constexpr int BM = 128;
 constexpr int MAX_STAGES = 8;
 constexpr int NTHREADS = 320;         // TMA warp, MMA warp, 2 x 4 epilogue warps
 constexpr int NTHREADS_WIDE = 576;    // ... or 2 x 8 epilogue warps (each tile's columns split in two)
+constexpr int MOM_SLOTS = 4;          // pre-norm fold: ring of row-moment tiles (128 rows x planes), fetched
+constexpr int MOM_AHEAD = 3;          // this many tiles ahead of their use
 
 struct GemmTcParams {
     __nv_bfloat16* c[3];
@@ -65,6 +78,12 @@ struct GemmTcParams {
     int stages;            // depth of the shared-memory ring
     int wstat;             // 1: the whole W tile (BN x Kd) stays in shared memory; the ring holds A only
     int tiles_per_cta;     // wstat: each CTA owns a contiguous range of the n-major tile list
+    // pre-norm fold: the moments of the A rows, [ln_planes][mom_ld] (sum, sum of squares) partial sums,
+    // arrive through the tensor map tmM
+    int ln_planes;
+    float ln_eps, ln_inv_k;
+    float2* moments_out;   // MOM: [2 * n_n_tiles][mom_ld] partial moments of the stored rows
+    long long mom_ld;      // plane stride of moments_out (M rounded up to an even count)
 };
 
 __device__ __forceinline__ void fail(volatile int* abort_flag, int code) {
@@ -113,9 +132,9 @@ __device__ __forceinline__ f32x2 gelu_pair(f32x2 x) {
 // row-wise write and the 8-rows-per-instruction read-back of phase B free of bank
 // conflicts.  With STAT it returns the sum of squares of the ROUNDED values (the statistic
 // is defined on what is stored), accumulated in four independent partial sums.
-template <bool STAT, bool BIAS, bool GELU>
+template <bool STAT, bool BIAS, bool GELU, bool LNF>
 __device__ __forceinline__ float stage_chunk(const uint32_t (&sts)[4], const uint32_t (&acc)[32],
-                                             const __nv_bfloat16* bias, int bias_valid) {
+                                             const __nv_bfloat16* bias, int bias_valid, float rstd) {
     float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
@@ -129,10 +148,12 @@ __device__ __forceinline__ float stage_chunk(const uint32_t (&sts)[4], const uin
         for (int e = 0; e < 4; ++e) {
             float a = __uint_as_float(acc[g * 8 + 2 * e]);
             float b = __uint_as_float(acc[g * 8 + 2 * e + 1]);
+            if (LNF && !(BIAS || GELU)) { a *= rstd; b *= rstd; }
             if (BIAS || GELU) {
                 // both elements of the pair go through one packed instruction per step; the
                 // packed operations round like their scalar counterparts
                 f32x2 x = pack2(a, b);
+                if (LNF) x = mul2(x, pack2(rstd, rstd));
                 if (BIAS) x = add2(x, pack2(__uint_as_float(bw[e] << 16), __uint_as_float(bw[e] & 0xffff0000u)));
                 if (GELU) x = gelu_pair(x);
                 unpack2(x, a, b);
@@ -157,10 +178,14 @@ __device__ __forceinline__ float stage_chunk(const uint32_t (&sts)[4], const uin
 // fetches half the W bytes per flop.  The even CTA issues the MMAs; loads of both CTAs credit its
 // "full" barriers, completions are committed to the barriers of both CTAs, and the epilogue
 // warps of both release the accumulator on the leader's "tempty" barriers.  Streaming mode only.
-template <bool STAT, bool BIAS, bool GELU, bool RES, bool WIDE, bool PAIR>
-__global__ void __launch_bounds__(WIDE ? NTHREADS_WIDE : NTHREADS, 1)
+template <bool STAT, bool BIAS, bool GELU, bool RES, bool WIDE, bool PAIR, bool LNF = false, bool MOM = false>
+__global__ void __launch_bounds__((WIDE ? NTHREADS_WIDE : NTHREADS) + (LNF ? 32 : 0), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
+               const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmM,
                const GemmTcParams p) {
+    static_assert(!(LNF && (PAIR || BIAS || RES)), "the pre-norm fold is built for single CTAs without bias / skip");
+    static_assert(!MOM || (RES && WIDE && !PAIR && !LNF), "row moments come from the wide skip-connection epilogue");
+    constexpr int STATW = WIDE ? 18 : 10;                      // LNF: the warp that prepares the extra operand chunk
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t pitch = p.KCH * 2;
@@ -179,14 +204,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // 16-element row holding the bias in element 0 (32 B per column, all column tiles)
     uint8_t* ones = slabs + (WIDE ? 16 : 8) * 2048;
     uint8_t* btile = ones + (p.mma_bias ? 4096 : 0);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(btile + (p.mma_bias ? (size_t)p.n_n_tiles * bn_cta * 32 : 0));
+    // pre-norm fold: the extra A chunk of both accumulator buffers (2 x 4 KB), the extra W rows of the
+    // resident tile (bn_cta x 32 B) and rstd of the rows of both buffers, from a 1 KB boundary
+    uint8_t* xa = reinterpret_cast<uint8_t*>(
+        (reinterpret_cast<uintptr_t>(btile + (p.mma_bias ? (size_t)p.n_n_tiles * bn_cta * 32 : 0)) + 1023) & ~(uintptr_t)1023);
+    uint8_t* xb = xa + 2 * 4096;
+    float* rstd_s = reinterpret_cast<float*>(xb + (((size_t)bn_cta * 32 + 1023) & ~(size_t)1023));
+    uint8_t* mring = reinterpret_cast<uint8_t*>(rstd_s + 2 * BM);      // [MOM_SLOTS][ln_planes][128] float2
+    uint64_t* bars = LNF ? reinterpret_cast<uint64_t*>(mring + (size_t)MOM_SLOTS * p.ln_planes * 1024)
+                         : reinterpret_cast<uint64_t*>(btile + (p.mma_bias ? (size_t)p.n_n_tiles * bn_cta * 32 : 0));
     static_assert(!(STAT && WIDE), "the fused statistic needs a row's whole head in one warp");
     uint64_t* full = bars;
     uint64_t* empty = bars + MAX_STAGES;
     uint64_t* tfull = bars + 2 * MAX_STAGES;
     uint64_t* tempty = tfull + 2;
     uint64_t* wfull = tempty + 2;                              // resident W tile landed
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(wfull + 1);
+    uint64_t* xfull = wfull + 1;                               // LNF: extra A chunk of buffer 0 / 1 written
+    uint64_t* mfull = xfull + 2;                               // LNF: moment tile landed in ring slot 0..3
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mfull + MOM_SLOTS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -202,10 +237,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             mbar_init(&tempty[b], (WIDE ? 8 : 4) * (PAIR ? 2 : 1));
         }
         mbar_init(wfull, 1);
+        mbar_init(&xfull[0], 1);
+        mbar_init(&xfull[1], 1);
+        for (int i = 0; i < MOM_SLOTS; ++i) mbar_init(&mfull[i], 1);
         *abort_flag = 0;
         fence_barrier_init();
         prefetch_tensormap(&tmA);
         prefetch_tensormap(&tmW);
+        if (LNF) { prefetch_tensormap(&tmX); prefetch_tensormap(&tmM); }
     }
     if (PAIR) __syncthreads();                  // barriers initialised before the pair-wide allocation returns
     if (warp == 1) {
@@ -273,9 +312,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     // every MMA that reads the old W tile has completed once the most recently
                     // filled ring stage has been released
                     if (any && !mbar_wait_a(empty0 + 8 * last_s, last_ph, abort_flag)) { give_up(15); ok = false; break; }
-                    mbar_expect_tx_a(wfull_a, p.KC * b_bytes);
+                    mbar_expect_tx_a(wfull_a, p.KC * b_bytes + (LNF ? (uint32_t)bn_cta * 32u : 0u));
                     for (int kc = 0; kc < p.KC; ++kc)
                         tma_load_2d_a(sB0 + kc * b_bytes, &tmW, wfull_a, kc * p.KCH, nt * p.BN);
+                    if (LNF) tma_load_2d_a(smem_u32(xb), &tmX, wfull_a, 0, nt * p.BN);
                     cur_nt = nt;
                     ++wloads;
                 }
@@ -349,12 +389,82 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     }
                     if (++s == STAGES) { s = 0; ph ^= 1u; }
                 }
+                if (LNF && ok) {
+                    // accumulator += [-mean, sigma] x [c, b']: the chunk the extra warp wrote for this buffer
+                    if (!mbar_wait_a(smem_u32(&xfull[buf]), u & 1u, abort_flag)) { give_up(17); ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint64_t xa_desc = dhi32 | (uint64_t)(((smem_u32(xa) + buf * 4096u) & 0x3FFFFu) >> 4);
+                    const uint64_t xb_desc = dhi32 | (uint64_t)((smem_u32(xb) & 0x3FFFFu) >> 4);
+                    mma_bf16_ss(d_tmem, xa_desc, xb_desc, idesc, 1);
+                }
                 if (ok) {
                     if (PAIR) { mma_commit_pair(tfull0 + 8 * buf); mma_commit_pair(peer_tfull0 + 8 * buf); }
                     else mma_commit_a(tfull0 + 8 * buf);
                 }
                 trace(tr, 1, tn);                           // tile issued
             }
+        }
+    } else if (LNF && warp == STATW) {
+        // Extra operand chunk of every tile: lane l prepares rows l, l + 32, l + 64, l + 96.  The
+        // moments of a tile (128 rows x planes, 1 KB per plane) are fetched by TMA into a ring of
+        // four slots, three tiles ahead of their use, so their DRAM latency is off the tile cadence.
+        const uint32_t slot_bytes = (uint32_t)p.ln_planes * 1024u;
+        auto fetch = [&](uint32_t k, int t) {                 // tile number k of this CTA, tile id t
+            int mt, nt;
+            tile_mn(t, mt, nt);
+            const uint32_t slot = k % MOM_SLOTS;
+            mbar_expect_tx(&mfull[slot], slot_bytes);
+            tma_load_2d(mring + slot * slot_bytes, &tmM, &mfull[slot], mt * BM * 2, 0);
+        };
+        if (lane == 0)
+            for (int k = 0; k < MOM_AHEAD; ++k)
+                if (first + k * step < last) fetch((uint32_t)k, first + k * step);
+        uint32_t tile = 0;
+        bool ok = true;
+        for (int t = first; t < last && ok; t += step, ++tile) {
+            const uint32_t buf = tile & 1u, u = tile >> 1, slot = tile % MOM_SLOTS;
+            // the slot tile + MOM_AHEAD lands in was read during the previous iteration (all lanes
+            // passed its __syncwarp)
+            if (lane == 0 && t + MOM_AHEAD * step < last) fetch(tile + MOM_AHEAD, t + MOM_AHEAD * step);
+            ok = mbar_wait(&mfull[slot], (tile / MOM_SLOTS) & 1u, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) { if (lane == 0) give_up(19); break; }
+            const float2* mt_s = reinterpret_cast<const float2*>(mring + slot * slot_bytes);
+            uint32_t wm[4], wsg[4];
+            float rs[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float s1 = 0.f, s2 = 0.f;
+                for (int pl = 0; pl < p.ln_planes; ++pl) {    // rows past M read the TMA's zero fill
+                    const float2 m = mt_s[pl * BM + j * 32 + lane];
+                    s1 += m.x; s2 += m.y;
+                }
+                const float mean = s1 * p.ln_inv_k;
+                const float var = fmaxf(fmaf(-mean, mean, s2 * p.ln_inv_k), 0.f) + p.ln_eps;
+                const float rstd = rsqrtf(var), sigma = var * rstd;
+                rs[j] = rstd;
+                // hi + lo bfloat16 splits: the products with the hi + lo splits of c and b' keep ~16 bits
+                const __nv_bfloat16 mh = __float2bfloat16_rn(-mean), sh = __float2bfloat16_rn(sigma);
+                const __nv_bfloat16 ml = __float2bfloat16_rn(-mean - __bfloat162float(mh));
+                const __nv_bfloat16 sl = __float2bfloat16_rn(sigma - __bfloat162float(sh));
+                wm[j] = (uint32_t)__bfloat16_as_ushort(mh) | ((uint32_t)__bfloat16_as_ushort(ml) << 16);
+                wsg[j] = (uint32_t)__bfloat16_as_ushort(sh) | ((uint32_t)__bfloat16_as_ushort(sl) << 16);
+            }
+            ok = mbar_wait(&tempty[buf], (u & 1u) ^ 1u, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) { if (lane == 0) give_up(18); break; }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int r = j * 32 + lane;
+                const uint4 v = make_uint4(wm[j], wm[j], wsg[j], wsg[j]);
+                uint4* dst = reinterpret_cast<uint4*>(xa + buf * 4096 + r * 32);
+                dst[0] = v;
+                dst[1] = v;
+                rstd_s[buf * BM + r] = rs[j];
+            }
+            fence_proxy_async();                    // generic-proxy writes -> visible to the MMA's reads
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&xfull[buf]);
         }
     } else {
         const int half = ((warp - 2) >> 2) & 1;  // which TMEM buffer / tile parity this warp drains
@@ -422,6 +532,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             trace(tr, 2 + half, tn);                        // accumulator ready
             tc_fence_after_sync();
             const uint32_t taddr = tmem_base + ((uint32_t)(lq * 32) << 16) + buf * p.BNpad;
+            const float rstd = LNF ? rstd_s[buf * BM + r] : 1.0f;
+            float mo1[4] = {0.f, 0.f, 0.f, 0.f}, mo2[4] = {0.f, 0.f, 0.f, 0.f};   // MOM: this lane's partial moments
             float ss = 0.f;
             // TMEM reads run one chunk ahead of the conversion / store work (ping-pong registers)
             uint32_t ra[32], rb[32];
@@ -446,7 +558,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             };
             auto finish = [&](int c, const uint32_t (&acc)[32], const uint4 (&resv)[4], uint4 (&resn)[4]) {
                 if (!WIDE && c + 32 < p.BN) load_res(c + 32, resn);    // next chunk's residual, a chunk ahead of its use
-                const float css = stage_chunk<STAT, BIAS, GELU>(sts, acc, BIAS ? p.bias + n0 + c : nullptr, ncol - c);
+                const float css = stage_chunk<STAT, BIAS, GELU, LNF>(sts, acc, BIAS ? p.bias + n0 + c : nullptr, ncol - c, rstd);
                 if (STAT) {
                     if (stat) {
                         ss += css;
@@ -480,6 +592,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
                             for (int e = 0; e < 4; ++e) vh[e] = __hadd2(vh[e], rh[e]);
                         }
+                        if (MOM) {
+                            const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float lo = __uint_as_float(vw[e] << 16), hi = __uint_as_float(vw[e] & 0xffff0000u);
+                                mo1[g] += lo + hi;
+                                mo2[g] = fmaf(hi, hi, fmaf(lo, lo, mo2[g]));
+                            }
+                        }
                         *reinterpret_cast<uint4*>(optr[g] + c) = v;
                     }
                 }
@@ -512,6 +633,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (lane == 0) {
                 if (PAIR) mbar_arrive_cluster(lead_tempty0 + 8 * buf);
                 else mbar_arrive(&tempty[buf]);
+            }
+            if (MOM) {
+                // the four lanes that share a row add up; plane = (column tile, column half)
+                float2* mplane = p.moments_out + (long long)(nt * 2 + chalf) * p.mom_ld;
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    float a = mo1[g], b = mo2[g];
+                    a += __shfl_xor_sync(0xffffffffu, a, 1); b += __shfl_xor_sync(0xffffffffu, b, 1);
+                    a += __shfl_xor_sync(0xffffffffu, a, 2); b += __shfl_xor_sync(0xffffffffu, b, 2);
+                    const int grow = mt * TM + (int)rank * BM + lq * 32 + g * 8 + (lane >> 2);
+                    if ((lane & 3) == 0 && grow < p.M) mplane[grow] = make_float2(a, b);
+                }
             }
             trace(tr, 2 + half, tn);                        // tile drained
         }
@@ -562,6 +695,36 @@ bool gemm_tc_can_fuse_stats(int part_cols, int dk) {
     return bn != 0 && dk % 32 == 0 && bn % dk == 0;
 }
 
+// Shared-memory plan of the pre-norm fold (W-resident mode is required: the extra W rows travel with
+// the W tile).  Returns the ring depth (>= 3) or 0 when the W tile does not fit.
+static int prenorm_stages(int BN, int Kd, bool wide, int planes) {
+    const int KCH = Kd % 64 == 0 ? 64 : (Kd % 32 == 0 ? 32 : 16);
+    const size_t pitch = (size_t)KCH * 2, a_bytes = BM * pitch, w_tile = (size_t)(Kd / KCH) * BN * pitch;
+    const size_t fixed = 1024 + (wide ? 16 : 8) * 2048 + 1024 + 2 * 4096 + (((size_t)BN * 32 + 1023) & ~(size_t)1023) +
+                         2 * BM * 4 + (size_t)MOM_SLOTS * planes * 1024 + (2 * MAX_STAGES + 7 + MOM_SLOTS) * 8 + 16;
+    if (fixed + w_tile + 3 * a_bytes > 226 * 1024) return 0;
+    const int st = (int)((226 * 1024 - fixed - w_tile) / a_bytes);
+    return st > MAX_STAGES ? MAX_STAGES : st;
+}
+
+static int tile_width(int N, int parts, bool has_stat) {
+    if (parts > 1 || has_stat) return dividing_tile(N / parts);
+    const int nt = (N + 255) / 256;
+    return (((N + nt - 1) / nt) + 15) / 16 * 16;
+}
+
+// Planes of partial row moments a GEMM with `moments_out` writes for N output columns.
+int gemm_tc_moment_planes(int N) { return 2 * ((N + tile_width(N, 1, false) - 1) / tile_width(N, 1, false)); }
+
+bool gemm_tc_prenorm_supported(int N, int Kd, int parts, bool has_stat, bool gelu) {
+    if (Kd % 16 != 0 || N % 8 != 0 || (parts > 1 && N % parts != 0)) return false;
+    const int bn = tile_width(N, parts, has_stat);
+    // the rows of A come from a GEMM with Kd output columns (or from row_moments: one plane)
+    return bn != 0 && prenorm_stages(bn, Kd, gelu && !has_stat, gemm_tc_moment_planes(Kd)) >= 3;
+}
+
+long long gemm_tc_moment_stride(long long M) { return (M + 1) & ~1ll; }
+
 int gemm_tc_stat_pieces(int part_cols, int dk) {
     const int bn = dividing_tile(part_cols);
     if (bn == 0 || dk % 32 != 0) return 0;
@@ -598,12 +761,13 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
     p.part_cols = N / parts;
     p.KCH = Kd % 64 == 0 ? 64 : (Kd % 32 == 0 ? 32 : 16);
     p.KC = Kd / p.KCH;
-    if (parts > 1 || o.stat[0]) {
-        p.BN = dividing_tile(p.part_cols);
-    } else {
-        const int nt = (N + 255) / 256;
-        p.BN = (((N + nt - 1) / nt) + 15) / 16 * 16;
-    }
+    p.BN = tile_width(N, parts, o.stat[0] != nullptr);
+    const bool lnf = o.ln_moments != nullptr;
+    p.ln_planes = o.ln_planes; p.ln_eps = o.ln_eps; p.ln_inv_k = 1.0f / (float)Kd;
+    p.moments_out = static_cast<float2*>(static_cast<void*>(o.moments_out));
+    p.mom_ld = gemm_tc_moment_stride(M);
+    if (lnf && (o.bias || o.residual || !o.ln_wextra || o.ln_planes < 1 || o.moments_out))
+        return set_error(CONVNN_E_UNSUPPORTED, "gemm_tc: the pre-norm fold takes no bias / skip connection (fold the bias)");
     p.BNpad = pow2_at_least(p.BN, 32);
     float* stat_final[3] = {p.stat[0], p.stat[1], p.stat[2]};
     if (o.stat[0] || o.stat[1] || o.stat[2]) {
@@ -634,12 +798,14 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
     // per element in the epilogue) when the bias rows of all column tiles fit in 24 KB.
     const size_t bias_rows = (size_t)p.n_n_tiles * p.BN * 32;
     const bool bias_by_mma = p.bias && !has_stat && bias_rows <= 24 * 1024;
+    if (o.moments_out && (!o.residual || o.gelu || has_stat || (p.bias && !bias_by_mma)))
+        return set_error(CONVNN_E_UNSUPPORTED, "gemm_tc: row moments are produced by the skip-connection epilogue only");
     // An epilogue that does more than convert and store (bias added per element, GELU, skip
     // connection) is bound by its own instruction latencies: sixteen epilogue warps (each tile's
     // columns split between two warps per TMEM lane quarter) cover them better than eight warps
     // with ping-pong registers.
     const bool wide = !has_stat && ((o.bias && !bias_by_mma) || o.gelu || o.residual);
-    size_t fixed = 1024 + (wide ? 16 : 8) * 2048 + (2 * MAX_STAGES + 5) * 8 + 16;
+    size_t fixed = 1024 + (wide ? 16 : 8) * 2048 + (2 * MAX_STAGES + 7 + MOM_SLOTS) * 8 + 16;
     // W-resident mode is judged against 200 KB (with more, shapes whose W tile barely fits would
     // be left with a ring too short to cover the TMA latency); the streaming ring takes all the
     // shared memory there is, which is worth 5-10 % on deep reductions (K >= 384).
@@ -654,13 +820,20 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
     const size_t a_bytes = (size_t)BM * pitch, b_bytes = (size_t)p.BN * pitch;
     const size_t w_tile = (size_t)p.KC * b_bytes;
     p.wstat = (w_tile + 3 * a_bytes + fixed <= budget && p.n_tiles >= 2 * sms) ? 1 : 0;
+    int lnf_stages = 0;
+    if (lnf) {
+        lnf_stages = prenorm_stages(p.BN, Kd, wide, o.ln_planes);
+        if (lnf_stages < 3)
+            return set_error(CONVNN_E_UNSUPPORTED, "gemm_tc: the pre-norm fold needs the %d x %d tile of W resident in shared memory", p.BN, Kd);
+        p.wstat = 1;
+    }
     // CTA pairs (M = 256 tiles, each CTA staging half of the W rows) where both operands stream and
     // the reduction is deep enough for operand traffic to matter.
     static const bool pair_allowed = [] { const char* e = getenv("CONVNN_B200_GEMM_PAIR"); return !(e && e[0] == '0'); }();
     // Measured: +5-7 % with many column tiles (N >= 1024), a loss with one to three of them, and
     // never worth a worse last wave (tiles of 256 rows on sms / 2 clusters quantise differently).
     bool pair = pair_allowed && !p.wstat && parts == 1 && !has_stat && p.KCH == 64 && Kd >= 384 && N >= 1024 &&
-                p.BN % 32 == 0;
+                p.BN % 32 == 0 && !o.moments_out;
     if (pair) {
         const long long tp = (long long)((M + 2 * BM - 1) / (2 * BM)) * p.n_n_tiles, nc = sms / 2;
         const double eff_pair = (double)tp / (double)(((tp + nc - 1) / nc) * nc);
@@ -694,22 +867,44 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
     } else if (p.wstat) {
         p.tiles_per_cta = (p.n_tiles + sms - 1) / sms;
         grid = (p.n_tiles + p.tiles_per_cta - 1) / p.tiles_per_cta;
-        int st_a = (int)((budget - fixed - w_tile) / a_bytes);
-        p.stages = st_a > MAX_STAGES ? MAX_STAGES : st_a;
-        smem = fixed + w_tile + (size_t)p.stages * a_bytes;
+        if (lnf) {
+            p.stages = lnf_stages;
+            smem = 226 * 1024;
+        } else {
+            int st_a = (int)((budget - fixed - w_tile) / a_bytes);
+            p.stages = st_a > MAX_STAGES ? MAX_STAGES : st_a;
+            smem = fixed + w_tile + (size_t)p.stages * a_bytes;
+        }
     } else {
         grid = p.n_tiles < sms ? p.n_tiles : sms;
         int st_ab = (int)((budget_stream - fixed) / (a_bytes + b_bytes));
         p.stages = st_ab > 6 ? 6 : (st_ab < 2 ? 2 : st_ab);
         smem = fixed + (size_t)p.stages * (a_bytes + b_bytes);
     }
-    CUtensorMap tmA, tmW;
+    CUtensorMap tmA, tmW, tmX, tmM;
     const uint64_t dimsA[2] = {(uint64_t)Kd, (uint64_t)M}, dimsW[2] = {(uint64_t)Kd, (uint64_t)N};
     const uint64_t strA[1] = {(uint64_t)lda * 2}, strW[1] = {(uint64_t)Kd * 2};
     const uint32_t boxA[2] = {(uint32_t)p.KCH, (uint32_t)BM};
     const uint32_t boxW[2] = {(uint32_t)p.KCH, (uint32_t)(pair ? p.BN / 2 : p.BN)};
     if (!encode_tensor_map_bf16(&tmA, a, 2, dimsA, strA, boxA, pitch)) return CONVNN_E_CUDA;
     if (!encode_tensor_map_bf16(&tmW, w, 2, dimsW, strW, boxW, pitch)) return CONVNN_E_CUDA;
+    if (lnf) {
+        // the extra W rows: (N, 16) bfloat16, 32 bytes per row, fetched with the 32-byte swizzle
+        const uint64_t dimsX[2] = {16, (uint64_t)N}, strX[1] = {32};
+        const uint32_t boxX[2] = {16, (uint32_t)p.BN};
+        if (!aligned16(o.ln_wextra)) return set_error(CONVNN_E_ALIGN, "gemm_tc: the folded extra rows must be 16-byte aligned");
+        if (!encode_tensor_map_bf16(&tmX, o.ln_wextra, 2, dimsX, strX, boxX, 32)) return CONVNN_E_CUDA;
+        // the moments as float32 [planes][2 * stride]: a tile is 256 floats (128 rows) of every plane;
+        // rows past M read as zero
+        const uint64_t dimsM[2] = {(uint64_t)2 * M, (uint64_t)o.ln_planes}, strM[1] = {(uint64_t)gemm_tc_moment_stride(M) * 8};
+        const uint32_t boxM[2] = {256, (uint32_t)o.ln_planes};
+        if (!aligned16(o.ln_moments)) return set_error(CONVNN_E_ALIGN, "gemm_tc: the row moments must be 16-byte aligned");
+        if (o.ln_planes > 16) return set_error(CONVNN_E_UNSUPPORTED, "gemm_tc: at most 16 planes of row moments");
+        if (!encode_tensor_map_f32(&tmM, o.ln_moments, 2, dimsM, strM, boxM)) return CONVNN_E_CUDA;
+    } else {
+        tmX = tmW;
+        tmM = tmW;
+    }
     if (has_stat && (p.bias || p.residual || p.gelu))
         return set_error(CONVNN_E_UNSUPPORTED, "gemm_tc: statistics cannot be combined with bias / GELU / residual");
     if (p.gelu && p.residual) return set_error(CONVNN_E_UNSUPPORTED, "gemm_tc: GELU with a residual is not built");
@@ -718,7 +913,14 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
         auto kern = gemm_tc_kernel<S, B, G, R, W, false>;                                                   \
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         if (e != cudaSuccess) return set_error(CONVNN_E_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e)); \
-        kern<<<grid, W ? NTHREADS_WIDE : NTHREADS, smem, st>>>(tmA, tmW, p);                                \
+        kern<<<grid, W ? NTHREADS_WIDE : NTHREADS, smem, st>>>(tmA, tmW, tmX, tmM, p);                           \
+    } while (0)
+#define CONVNN_GEMM_LAUNCH_X(S, G, R, W, LNFv, MOMv)                                                        \
+    do {                                                                                                    \
+        auto kern = gemm_tc_kernel<S, false, G, R, W, false, LNFv, MOMv>;                                   \
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (e != cudaSuccess) return set_error(CONVNN_E_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e)); \
+        kern<<<grid, (W ? NTHREADS_WIDE : NTHREADS) + (LNFv ? 32 : 0), smem, st>>>(tmA, tmW, tmX, tmM, p);       \
     } while (0)
 #define CONVNN_GEMM_LAUNCH_PAIR(G, R, W)                                                                    \
     do {                                                                                                    \
@@ -746,7 +948,7 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
         }                                                                                                   \
         const int nc = p.n_tiles < max_clusters ? p.n_tiles : max_clusters;                                 \
         cfg.gridDim = dim3(2 * nc);                                                                         \
-        e = cudaLaunchKernelEx(&cfg, kern, tmA, tmW, p);                                                    \
+        e = cudaLaunchKernelEx(&cfg, kern, tmA, tmW, tmX, tmM, p);                                                    \
         if (e != cudaSuccess) return set_error(CONVNN_E_CUDA, "gemm_tc pair launch: %s", cudaGetErrorString(e)); \
     } while (0)
 #define CONVNN_GEMM_LAUNCH(S, B, G, R)                          \
@@ -754,6 +956,13 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
         if (wide) CONVNN_GEMM_LAUNCH1(false, B, G, R, true);    \
         else CONVNN_GEMM_LAUNCH1(S, B, G, R, false);            \
     } while (0)
+    if (lnf) {
+        if (has_stat) CONVNN_GEMM_LAUNCH_X(true, false, false, false, true, false);
+        else if (p.gelu) CONVNN_GEMM_LAUNCH_X(false, true, false, true, true, false);
+        else CONVNN_GEMM_LAUNCH_X(false, false, false, false, true, false);
+    } else if (o.moments_out) {
+        CONVNN_GEMM_LAUNCH_X(false, false, true, true, false, true);
+    } else
     if (pair) {
         if (p.gelu) CONVNN_GEMM_LAUNCH_PAIR(true, false, true);
         else if (p.residual) CONVNN_GEMM_LAUNCH_PAIR(false, true, true);
@@ -768,6 +977,7 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
 #undef CONVNN_GEMM_LAUNCH
 #undef CONVNN_GEMM_LAUNCH1
 #undef CONVNN_GEMM_LAUNCH_PAIR
+#undef CONVNN_GEMM_LAUNCH_X
     CONVNN_CHECK_LAUNCH("gemm_tc");
     if (p.stat_pieces > 1) {
         for (int i = 0; i < parts; ++i) {

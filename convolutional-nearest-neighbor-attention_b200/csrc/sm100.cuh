@@ -348,6 +348,8 @@ __device__ __forceinline__ bool elect_one() {
 // Returns false (with last_error set) if the driver entry point is unavailable or the
 // encode call rejects the arguments.  dims / strides are innermost first; strides[0]
 // (the element stride) is implicit, strides_bytes has rank-1 entries.
+bool encode_tensor_map_f32(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                           const uint64_t* strides_bytes, const uint32_t* box);
 bool encode_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
                             const uint64_t* strides_bytes, const uint32_t* box, int swizzle_bytes);
 

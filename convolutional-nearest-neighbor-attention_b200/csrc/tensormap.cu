@@ -29,8 +29,8 @@ EncodeTiledFn resolve_encode() {
 }
 }  // namespace
 
-bool encode_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
-                            const uint64_t* strides_bytes, const uint32_t* box, int swizzle_bytes) {
+static bool encode_tensor_map(CUtensorMap* out, CUtensorMapDataType type, const void* base, int rank, const uint64_t* dims,
+                              const uint64_t* strides_bytes, const uint32_t* box, int swizzle_bytes) {
     EncodeTiledFn fn = resolve_encode();
     if (!fn) {
         set_error(CONVNN_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
@@ -48,7 +48,7 @@ bool encode_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const 
                           : swizzle_bytes == 64  ? CU_TENSOR_MAP_SWIZZLE_64B
                           : swizzle_bytes == 32  ? CU_TENSOR_MAP_SWIZZLE_32B
                                                  : CU_TENSOR_MAP_SWIZZLE_NONE;
-    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), gdims, gstr,
+    CUresult r = fn(out, type, (cuuint32_t)rank, const_cast<void*>(base), gdims, gstr,
                     gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
@@ -57,6 +57,17 @@ bool encode_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const 
         return false;
     }
     return true;
+}
+
+bool encode_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                            const uint64_t* strides_bytes, const uint32_t* box, int swizzle_bytes) {
+    return encode_tensor_map(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, base, rank, dims, strides_bytes, box, swizzle_bytes);
+}
+
+// float32 elements, no swizzle (the row moments of the pre-norm fold)
+bool encode_tensor_map_f32(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                           const uint64_t* strides_bytes, const uint32_t* box) {
+    return encode_tensor_map(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, base, rank, dims, strides_bytes, box, 0);
 }
 
 }  // namespace convnn

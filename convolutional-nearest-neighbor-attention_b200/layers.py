@@ -146,6 +146,26 @@ class MultiHeadConvNNAttention(nn.Module):
             return self._forward_staged(x, packed, cand, out, residual)
         return ops.forward(self._spec(), x, packed, cand, out=out, residual=residual)
 
+    def prenorm_supported(self, x) -> bool:
+        """Whether ``forward_prenorm`` takes this input (bfloat16, sampling 'all', a K/V/Q weight tile
+        that stays resident in shared memory); otherwise the caller normalises and calls ``forward``."""
+        return (x.is_cuda and x.dtype == torch.bfloat16 and self.stage_timer is None and
+                ops.prenorm_forward_supported(self._spec(), x.shape[0], x.shape[1], x.dtype))
+
+    def forward_prenorm(self, x, moments, norm: nn.LayerNorm, residual: Optional[torch.Tensor] = None,
+                        want_moments: bool = False):
+        """``layer(norm(x))`` (``+ residual``) from the rows ``x`` BEFORE ``norm`` and their moments,
+        the LayerNorm folded into the K/V/Q projection.  Returns (out, moments of out or None)."""
+        self._check_mode(x)
+        w_qkv, w_conv, w_pw, w_o = self.packed_weights(x.dtype, x.device)
+        if getattr(self, "_folded", None) is None:
+            self._folded = _PackedParams()
+        wf, wx = self._folded.get((w_qkv, norm.weight, norm.bias), x.dtype, x.device, lambda: ops.fold_layernorm(
+            w_qkv.view(-1, w_qkv.shape[-1]), None, norm.weight.detach().to(x.device, x.dtype),
+            norm.bias.detach().to(x.device, x.dtype)))
+        return ops.prenorm_forward(self._spec(), x, moments, norm.eps, (wf, wx, w_conv, w_pw, w_o),
+                                   residual=residual, want_moments=want_moments)
+
     def _forward_staged(self, x, packed, cand, out, residual=None):
         """The same kernels in the same order as ``convnn_b200_forward``, issued through the
         four stage entry points so a profiler hook can bracket each with CUDA events."""

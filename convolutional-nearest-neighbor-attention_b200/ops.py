@@ -235,6 +235,101 @@ def forward(spec: LayerSpec, x: torch.Tensor, packed, cand: Optional[torch.Tenso
     return out
 
 
+# ---- LayerNorm folded into the GEMM that consumes it (bfloat16) --------------------------------
+
+def prenorm_linear_supported(N: int, K: int, gelu: bool) -> bool:
+    return bool(_capi.lib().convnn_b200_prenorm_linear_supported(N, K, int(gelu)))
+
+
+def prenorm_forward_supported(spec: LayerSpec, B: int, T: int, dtype) -> bool:
+    if dtype != torch.bfloat16 or spec.sampling_type != "all":
+        return False
+    return bool(_capi.lib().convnn_b200_prenorm_forward_supported(descriptor(spec, B, T, T, dtype)))
+
+
+def row_moments(x: torch.Tensor) -> torch.Tensor:
+    """(1, stride, 2) float32 (sum, sum of squares) of every row of a bfloat16 ``x`` (..., D); stride =
+    the row count rounded up to the plane stride of moments buffers (``convnn_b200_moment_stride``)."""
+    _require_cuda(x)
+    xv, rows, ldx = _flat_rows(x)
+    out = torch.empty(1, _capi.lib().convnn_b200_moment_stride(rows), 2, dtype=torch.float32, device=x.device)
+    _capi.check(_capi.lib().convnn_b200_row_moments(xv.data_ptr(), ldx, rows, x.shape[-1], out.data_ptr(), _stream(x)))
+    return out
+
+
+def fold_layernorm(weight: torch.Tensor, bias: Optional[torch.Tensor], gamma: torch.Tensor,
+                   beta: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(w_folded (N, K), w_extra (N, 16)) for ``prenorm_linear`` / ``prenorm_forward``: the Linear's
+    weight with the LayerNorm's gamma multiplied in, and the mean / beta / bias correction rows."""
+    _require_cuda(weight, gamma, beta, bias)
+    w = weight.detach().contiguous()
+    N, K = w.shape
+    wf = torch.empty(N, K, dtype=torch.bfloat16, device=w.device)
+    wx = torch.empty(N, 16, dtype=torch.bfloat16, device=w.device)
+    _capi.check(_capi.lib().convnn_b200_fold_layernorm(w.data_ptr(), _capi.ptr(bias), gamma.data_ptr(), beta.data_ptr(),
+                                                       N, K, wf.data_ptr(), wx.data_ptr(), _stream(w)))
+    return wf, wx
+
+
+def prenorm_linear(a: torch.Tensor, moments: torch.Tensor, eps: float, w_folded: torch.Tensor,
+                   w_extra: torch.Tensor, gelu: bool = False) -> torch.Tensor:
+    """[GELU](LayerNorm(a) @ W.T + bias) from the un-normalised rows ``a`` and their moments."""
+    _require_cuda(a, moments, w_folded, w_extra)
+    av, M, lda = _flat_rows(a)
+    N, K = w_folded.shape
+    out = torch.empty(*a.shape[:-1], N, dtype=a.dtype, device=a.device)
+    _capi.check(_capi.lib().convnn_b200_prenorm_linear(av.data_ptr(), lda, moments.data_ptr(), moments.shape[0],
+                                                       float(eps), w_folded.data_ptr(), w_extra.data_ptr(),
+                                                       out.data_ptr(), N, M, N, K, int(gelu), _stream(a)))
+    return out
+
+
+def linear_moments(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                   residual: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(residual + a @ weight.T + bias, moments of its rows) through ``convnn_b200_linear_moments``."""
+    _require_cuda(a, weight, bias, residual)
+    L = _capi.lib()
+    av, M, lda = _flat_rows(a)
+    N, K = weight.shape
+    w = weight if weight.is_contiguous() else weight.contiguous()
+    out = torch.empty(*a.shape[:-1], N, dtype=a.dtype, device=a.device)
+    mom = torch.empty(L.convnn_b200_moment_planes(N), L.convnn_b200_moment_stride(M), 2, dtype=torch.float32,
+                      device=a.device)
+    res, _, ldr = _flat_rows(residual)
+    _capi.check(L.convnn_b200_linear_moments(av.data_ptr(), lda, w.data_ptr(), _capi.ptr(bias), res.data_ptr(), ldr,
+                                             out.data_ptr(), N, M, N, K, mom.data_ptr(), _stream(a)))
+    return out, mom
+
+
+def prenorm_forward(spec: LayerSpec, x: torch.Tensor, moments: torch.Tensor, eps: float, packed_folded,
+                    residual: Optional[torch.Tensor] = None, want_moments: bool = False,
+                    workspace: Optional[torch.Tensor] = None):
+    """``[residual +] layer(LayerNorm(x))`` through ``convnn_b200_prenorm_forward``; ``packed_folded`` =
+    (w_qkv_folded (3D, D), w_qkv_extra (3D, 16), w_conv, w_pw, w_o).  Returns (out, moments of out or None)."""
+    w_qkv, w_qkv_x, w_conv, w_pw, w_o = packed_folded
+    _require_cuda(x, w_qkv, moments)
+    L = _capi.lib()
+    x, ldx = _rows_view(x)
+    B, T, D = x.shape
+    d = descriptor(spec, B, T, T, x.dtype)
+    need = L.convnn_b200_workspace_bytes(d)
+    if need == 0:
+        _capi.check(min(L.convnn_b200_head_channels(d), 0))
+    if workspace is None or workspace.numel() < need:
+        workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+    out = torch.empty(B, T, D, dtype=x.dtype, device=x.device)
+    res, ldr = _residual_arg(residual, x)
+    mom = None
+    if want_moments:
+        mom = torch.empty(L.convnn_b200_moment_planes(D), L.convnn_b200_moment_stride(B * T), 2, dtype=torch.float32,
+                          device=x.device)
+    _capi.check(L.convnn_b200_prenorm_forward(d, x.data_ptr(), ldx, moments.data_ptr(), moments.shape[0], float(eps),
+                                              w_qkv.data_ptr(), w_qkv_x.data_ptr(), w_conv.data_ptr(), _capi.ptr(w_pw),
+                                              w_o.data_ptr(), _capi.ptr(res), ldr, out.data_ptr(), D,
+                                              _capi.ptr(mom), workspace.data_ptr(), workspace.numel(), _stream(x)))
+    return out, mom
+
+
 # ---- the other halves of the branching wrappers ------------------------------------------------
 
 def _out_slice(out: Optional[torch.Tensor], like: torch.Tensor) -> Tuple[torch.Tensor, int]:

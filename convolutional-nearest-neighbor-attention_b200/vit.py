@@ -18,7 +18,7 @@ import torch
 import torch.nn as nn
 
 from . import ops
-from .layers import MultiHeadBranchingAttention, MultiHeadBranchingConv, MultiHeadConvNNAttention
+from .layers import MultiHeadBranchingAttention, MultiHeadBranchingConv, MultiHeadConvNNAttention, _PackedParams
 
 _DEFAULTS = dict(layer="ConvNNAttention", patch_size=16, num_layers=12, num_heads=3, d_hidden=192, d_mlp=768,
                  dropout=0.1, attention_dropout=0.1, convolution_type="depthwise", softmax_topk_val=True, K=9,
@@ -91,22 +91,55 @@ class TransformerEncoder(nn.Module):
         self.dropout2 = nn.Dropout(dropout)
         self.mlp = nn.Sequential(nn.Linear(d_hidden, d_mlp), nn.GELU(), nn.Dropout(dropout),
                                  nn.Linear(d_mlp, d_hidden))
+        # bfloat16 library path: fold norm1 / norm2 into the GEMMs that consume them where the shapes
+        # allow (set to False for a LayerNorm kernel followed by the plain GEMM, the reference's order
+        # of roundings)
+        self.fold_layernorm = True
+        self._fc1_folded = _PackedParams()
 
     def forward(self, x):
         if _library_path(x) and not (self.training and (self.dropout1.p > 0 or self.dropout2.p > 0)):
-            return self._forward_library(x)
+            return self._forward_library(x)[0]
         x = x + self.dropout1(self.attention(self.norm1(x)))
         return x + self.dropout2(self.mlp(self.norm2(x)))
 
-    def _forward_library(self, x):
-        """The same block with LayerNorm, both Linear layers (GELU and the skip connections
-        folded into their stores) and the attention output projection (+ skip) in libconvnn_b200."""
+    def folds_norm1(self, x) -> bool:
+        """Whether this block consumes un-normalised rows plus their moments (norm1 folded into the
+        K/V/Q projection): the block before it then emits the moments from its last GEMM."""
+        return (self.fold_layernorm and isinstance(self.attention, MultiHeadConvNNAttention) and
+                self.attention.prenorm_supported(x))
+
+    def _forward_library(self, x, moments=None, want_moments=False):
+        """The same block in libconvnn_b200: both Linear layers (GELU and the skip connections folded
+        into their stores), the attention layer with its output projection (+ skip), and the two
+        LayerNorms either as kernels of their own or, where the shapes allow (``fold_layernorm``),
+        folded into the GEMMs that consume them: those read the un-normalised rows and their moments
+        (sum, sum of squares), which the GEMM that wrote the rows emits from its epilogue.
+        Returns (x, moments of x or None)."""
         n1, n2, fc1, fc2 = self.norm1, self.norm2, self.mlp[0], self.mlp[3]
-        xn = ops.layernorm(x, n1.weight, n1.bias, n1.eps)
-        x = self.attention(xn, residual=x)       # skip connection folded into the layer's last store
-        xn = ops.layernorm(x, n2.weight, n2.bias, n2.eps)
-        h = ops.linear(xn, fc1.weight, fc1.bias, gelu=True)
-        return ops.linear(h, fc2.weight, fc2.bias, residual=x)
+        bf16 = x.dtype == torch.bfloat16
+        fold_mlp = (self.fold_layernorm and bf16 and
+                    ops.prenorm_linear_supported(fc1.out_features, fc1.in_features, True))
+        m1 = None
+        if self.folds_norm1(x):
+            if moments is None:
+                moments = ops.row_moments(x)
+            x, m1 = self.attention.forward_prenorm(x, moments, n1, residual=x, want_moments=fold_mlp)
+        else:
+            xn = ops.layernorm(x, n1.weight, n1.bias, n1.eps)
+            x = self.attention(xn, residual=x)       # skip connection folded into the layer's last store
+        if fold_mlp:
+            if m1 is None:
+                m1 = ops.row_moments(x)
+            wf, wx = self._fc1_folded.get((fc1.weight, fc1.bias, n2.weight, n2.bias), x.dtype, x.device,
+                                          lambda: ops.fold_layernorm(fc1.weight, fc1.bias, n2.weight, n2.bias))
+            h = ops.prenorm_linear(x, m1, n2.eps, wf, wx, gelu=True)
+        else:
+            xn = ops.layernorm(x, n2.weight, n2.bias, n2.eps)
+            h = ops.linear(xn, fc1.weight, fc1.bias, gelu=True)
+        if want_moments and bf16:
+            return ops.linear_moments(h, fc2.weight, fc2.bias, residual=x)
+        return ops.linear(h, fc2.weight, fc2.bias, residual=x), None
 
 
 class ViT(nn.Module):
@@ -148,7 +181,14 @@ class ViT(nn.Module):
             x = ops.patch_embed(x, pemb.linear_projection.weight, pemb.linear_projection.bias, pemb.norm.weight,
                                 pemb.norm.bias, pe_mod.cls_tokens, pe_mod.pe, self.args.patch_size, pemb.norm.eps,
                                 pixel_mean=mean, pixel_inv_std=inv_std)
-            x = self.transformer_encoder(x)
+            blocks = list(self.transformer_encoder)
+            moments = None
+            for i, blk in enumerate(blocks):
+                if blk.training and (blk.dropout1.p > 0 or blk.dropout2.p > 0):
+                    x, moments = blk(x), None
+                    continue
+                nxt = blocks[i + 1] if i + 1 < len(blocks) else None
+                x, moments = blk._forward_library(x, moments, want_moments=nxt is not None and nxt.folds_norm1(x))
             return ops.linear(x[:, 0], self.classifier.weight, self.classifier.bias)
         x = self.positional_encoding(self.patch_embedding(x))
         x = self.transformer_encoder(x)

@@ -235,6 +235,52 @@ int convnn_b200_embed_tokens(int dtype, const void* proj, const void* gamma, con
                              const void* cls, const void* pe, void* out, int32_t B, int32_t Np,
                              int32_t D, void* stream);
 
+/* ---- LayerNorm folded into the GEMM that consumes it (bfloat16 only) ----
+ * No reference counterpart as functions: together they compute exactly what vit.py:262-269 does
+ * (norm1 -> attention, norm2 -> mlp) without writing or re-reading the normalised rows.  With
+ * W' = W diag(gamma), c[n] = sum_k W'[n,k], b'[n] = sum_k W[n,k] beta[k] + bias[n]:
+ *     LayerNorm(x) W^T + bias = rstd (x W'^T - mean c + sigma b'),   sigma = 1 / rstd,
+ * so the consumer GEMM reads the rows x themselves plus their moments (sum x, sum x^2), and the
+ * GEMM that produced x (always one with a skip connection in the encoder) emits those moments from
+ * its epilogue.  `moments` buffers are float32 [planes][convnn_b200_moment_stride(M)][2], 16-byte
+ * aligned: partial sums that the consumer adds up over the planes (it fetches them by TMA, hence
+ * the even plane stride).  Rounding differs from the unfused order only in where the bfloat16 rounding
+ * of the normalised activations happens (here the weights W' are rounded instead). */
+
+/* Planes a GEMM with N output columns writes into `moments_out` (2 per 256-column tile), and the
+ * entries (of two floats) from one plane of an M-row moments buffer to the next. */
+int convnn_b200_moment_planes(int32_t N);
+int64_t convnn_b200_moment_stride(int64_t M);
+/* 1 if convnn_b200_prenorm_linear / _forward take this shape (the folded W tile must stay resident
+ * in shared memory: small K), else 0 and the caller keeps LayerNorm + linear / forward. */
+int convnn_b200_prenorm_linear_supported(int32_t N, int32_t K, int32_t gelu);
+int convnn_b200_prenorm_forward_supported(const convnn_desc* d);
+/* moments[r] = (sum, sum of squares) of row r of x (rows x D bfloat16, stride ldx): one plane, for
+ * rows that no GEMM of this library produced (the embedding's output). */
+int convnn_b200_row_moments(const void* x, int64_t ldx, int64_t rows, int32_t D, float* moments, void* stream);
+/* Prepares the operands of the folded GEMM from nn.Linear(K -> N) weights w (N, K), bias (N) or
+ * NULL and the LayerNorm's gamma, beta (K): w_folded (N, K) and w_extra (N, 16), all bfloat16. */
+int convnn_b200_fold_layernorm(const void* w, const void* bias, const void* gamma, const void* beta, int32_t N,
+                               int32_t K, void* w_folded, void* w_extra, void* stream);
+/* out = [GELU](LayerNorm(a) w^T + bias) from the un-normalised rows a (M, K) and their moments
+ * (vit.py:267 with 253-255).  CONVNN_E_UNSUPPORTED where _supported() says 0. */
+int convnn_b200_prenorm_linear(const void* a, int64_t lda, const float* moments, int32_t planes, float eps,
+                               const void* w_folded, const void* w_extra, void* out, int64_t ldo, int64_t M,
+                               int32_t N, int32_t K, int32_t gelu, void* stream);
+/* convnn_b200_linear with a skip connection (residual != NULL) that also writes the moments of
+ * the rows it stores: moments_out = float32 [convnn_b200_moment_planes(N)][convnn_b200_moment_stride(M)][2]. */
+int convnn_b200_linear_moments(const void* a, int64_t lda, const void* w, const void* bias, const void* residual,
+                               int64_t ldr, void* out, int64_t ldo, int64_t M, int32_t N, int32_t K,
+                               float* moments_out, void* stream);
+/* convnn_b200_forward on rows x that have NOT been normalised yet (norm1 folded into the K/V/Q
+ * projection; sampling 'all' only), optionally emitting the moments of residual + layer(x) for the
+ * next folded GEMM (moments_out may be NULL; it needs residual != NULL). */
+int convnn_b200_prenorm_forward(const convnn_desc* d, const void* x, int64_t ldx, const float* moments,
+                                int32_t planes, float eps, const void* w_qkv_folded, const void* w_qkv_extra,
+                                const void* w_conv, const void* w_pw, const void* w_o, const void* residual,
+                                int64_t ldr, void* out, int64_t ldo, float* moments_out, void* workspace,
+                                size_t workspace_bytes, void* stream);
+
 /* ---- the other halves of the reference's branching wrappers (layers.py:574-577, 648-651) ---- */
 
 /* MultiHeadAttention.forward (layers.py:105-130), eval mode, no mask: q, k, v projections with the

@@ -1,0 +1,159 @@
+"""LayerNorm folded into the GEMM that consumes it (vit.py:262-269 of the reference computed without
+materialising the normalised rows): the folded entry points against float64 arithmetic on the same
+bfloat16 inputs, and against the library's own LayerNorm + GEMM order."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+import convnn_b200
+from convnn_b200 import _capi, ops
+from oracle.convnn_oracle import ConvNNConfig, make_input, make_layer_weights
+from gpu_util import DEV, module_of, rel_err
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+
+def rnd(*shape, seed, scale=1.0, shift=0.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale + shift).to(BF).to(DEV)
+
+
+@pytest.mark.parametrize("rows,D", [(1, 192), (777, 192), (300, 768), (65, 64)])
+def test_row_moments(rows, D):
+    x = rnd(rows, D, seed=1, shift=0.5)
+    m = ops.row_moments(x)
+    assert m.shape == (1, rows + rows % 2, 2)
+    xd = x.double()
+    assert torch.allclose(m[0, :rows, 0].double(), xd.sum(1), rtol=1e-5, atol=1e-4)
+    assert torch.allclose(m[0, :rows, 1].double(), (xd * xd).sum(1), rtol=1e-5, atol=1e-4)
+
+
+@pytest.mark.parametrize("M,N,K,bias", [(777, 192, 768, True), (50432, 192, 768, True), (1000, 192, 192, False),
+                                         (300, 768, 768, True), (130, 80, 64, True)])
+def test_linear_moments_is_linear_plus_row_sums(M, N, K, bias):
+    """Same bits as convnn_b200_linear with the skip connection; the planes add up to the moments of
+    the stored rows."""
+    a, w, res = rnd(M, K, seed=2), rnd(N, K, seed=3, scale=K ** -0.5), rnd(M, N, seed=4)
+    b = rnd(N, seed=5) if bias else None
+    want = ops.linear(a, w, b, residual=res)
+    got, mom = ops.linear_moments(a, w, b, res)
+    assert torch.equal(got, want)
+    assert mom.shape == (_capi.lib().convnn_b200_moment_planes(N), M + M % 2, 2)
+    gd = got.double()
+    tot = mom.double()[:, :M].sum(0)
+    assert torch.allclose(tot[:, 0], gd.sum(1), rtol=1e-5, atol=1e-3)
+    assert torch.allclose(tot[:, 1], (gd * gd).sum(1), rtol=1e-5, atol=1e-3)
+    assert _capi.device_status() == 0
+
+
+def layernorm_linear_f64(x, gamma, beta, w, b, eps, gelu):
+    y = F.layer_norm(x.double(), (x.shape[-1],), gamma.double(), beta.double(), eps)
+    out = y @ w.double().t()
+    if b is not None:
+        out = out + b.double()
+    return F.gelu(out) if gelu else out
+
+
+@pytest.mark.parametrize("gelu", [False, True])
+@pytest.mark.parametrize("M,N,K,shift", [(777, 768, 192, 0.0), (1, 768, 192, 0.0), (50432, 768, 192, 0.0), (1000, 192, 192, 3.0),
+                                          (129, 576, 192, -1.0), (4000, 256, 64, 0.5)])
+def test_prenorm_linear_against_float64(M, N, K, shift, gelu):
+    """[GELU](LayerNorm(x) W^T + b) from the raw rows and their moments: within the bfloat16 output
+    tolerance (2e-2, relative to the output's scale) of float64 arithmetic on the same inputs, and no
+    worse than LayerNorm kernel + GEMM; rows with a mean several times their spread included."""
+    assert ops.prenorm_linear_supported(N, K, gelu)
+    x = rnd(M, K, seed=6, shift=shift)
+    gamma, beta = rnd(K, seed=7, scale=0.2, shift=1.0), rnd(K, seed=8, scale=0.2)
+    w, b = rnd(N, K, seed=9, scale=K ** -0.5), rnd(N, seed=10, scale=0.3)
+    wf, wx = ops.fold_layernorm(w, b, gamma, beta)
+    got = ops.prenorm_linear(x, ops.row_moments(x), 1e-5, wf, wx, gelu=gelu)
+    want = layernorm_linear_f64(x, gamma, beta, w, b, 1e-5, gelu)
+    unfused = ops.linear(ops.layernorm(x, gamma, beta, 1e-5), w, b, gelu=gelu)
+    scale = want.abs().max().item()
+    err = (got.double().cpu() - want.cpu()).abs().max().item() / scale
+    err_unfused = (unfused.double().cpu() - want.cpu()).abs().max().item() / scale
+    print(f"max err / scale: folded {err:.2e}, LayerNorm + GEMM {err_unfused:.2e}")
+    assert err < 2e-2
+    assert rel_err(got, want) < 6e-3
+    assert _capi.device_status() == 0
+
+
+def test_prenorm_linear_takes_moments_in_several_planes():
+    """The consumer adds the planes up: moments split arbitrarily over three planes give the same bits."""
+    M, N, K = 500, 768, 192
+    x, gamma, beta = rnd(M, K, seed=11), rnd(K, seed=12, shift=1.0, scale=0.1), rnd(K, seed=13, scale=0.1)
+    w = rnd(N, K, seed=14, scale=K ** -0.5)
+    wf, wx = ops.fold_layernorm(w, None, gamma, beta)
+    m = ops.row_moments(x)
+    parts = torch.stack([m[0] * 0.25, m[0] * 0.5, m[0] * 0.25]).contiguous()
+    a = ops.prenorm_linear(x, m, 1e-5, wf, wx)
+    b = ops.prenorm_linear(x, parts, 1e-5, wf, wx)
+    assert torch.equal(a, b)
+
+
+def test_unsupported_shapes_are_refused_not_computed():
+    assert not ops.prenorm_linear_supported(3072, 768, True)       # the W tile does not fit in shared memory
+    x = rnd(64, 768, seed=15)
+    wf, wx = torch.zeros(3072, 768, dtype=BF, device=DEV), torch.zeros(3072, 16, dtype=BF, device=DEV)
+    with pytest.raises(_capi.ConvnnError):
+        ops.prenorm_linear(x, ops.row_moments(x), 1e-5, wf, wx, gelu=True)
+
+
+@pytest.mark.parametrize("metric,H", [("cosine", 1), ("euclidean", 1), ("matmul", 1), ("cosine", 3)])
+def test_prenorm_forward_matches_layernorm_then_forward(metric, H):
+    """norm1 folded into the K/V/Q projection: the layer output (with the skip connection) agrees with
+    LayerNorm kernel + convnn_b200_forward except on rows whose neighbour choice sits on a near-tie, and
+    the emitted moments are those of the stored rows."""
+    B, T, D = 8, 197, 192
+    cfg = ConvNNConfig(d_hidden=D, num_heads=H, K=9, magnitude_type=metric, seq_length=T)
+    layer = module_of(cfg, make_layer_weights(cfg, seed=21), BF)
+    norm = torch.nn.LayerNorm(D).to(DEV, BF)
+    with torch.no_grad():
+        norm.weight.copy_(rnd(D, seed=22, scale=0.1, shift=1.0))
+        norm.bias.copy_(rnd(D, seed=23, scale=0.1))
+        x = rnd(B, T, D, seed=24, shift=0.3)
+        assert layer.prenorm_supported(x)
+        got, mom = layer.forward_prenorm(x, ops.row_moments(x), norm, residual=x, want_moments=True)
+        want = layer(ops.layernorm(x, norm.weight, norm.bias, norm.eps), residual=x)
+    assert _capi.device_status() == 0
+    diff = (got.float() - want.float()).abs().amax(-1)
+    scale = want.float().abs().amax().item()
+    close = (diff < 2e-2 * scale).float().mean().item()
+    print(f"rows within 2e-2 of the unfused order: {close:.4f}")
+    assert close > 0.97
+    gd = got.double().view(B * T, D)
+    tot = mom.double()[:, : B * T].sum(0)
+    assert torch.allclose(tot[:, 0], gd.sum(1), rtol=1e-5, atol=1e-3)
+    assert torch.allclose(tot[:, 1], (gd * gd).sum(1), rtol=1e-5, atol=1e-3)
+
+
+def test_vit_with_and_without_the_fold():
+    """Whole model (ViT-Tiny shape, 4 layers): folding both LayerNorms of every block changes where
+    bfloat16 roundings happen, not what is computed."""
+    from oracle.vit_oracle import ViTConfig, make_images, make_vit_weights
+    from oracle.convnn_oracle import bf16_round
+    cfg = ViTConfig(layer="ConvNNAttention", d_hidden=192, d_mlp=768, num_heads=1, num_layers=4,
+                    magnitude_type="cosine", convolution_type="depthwise")
+    sd = {k: bf16_round(v) for k, v in make_vit_weights(cfg, seed=5).items()}
+    args = convnn_b200.make_args(**{f: getattr(cfg, f) for f in cfg.__dataclass_fields__}, device=DEV)
+    model = convnn_b200.ViT(args).eval()
+    model.load_state_dict(sd, strict=True)
+    model = model.to(DEV, BF)
+    img = bf16_round(make_images(4, cfg, seed=6)).to(DEV, BF)
+    lib = _capi.lib()
+    with torch.no_grad():
+        model(img)                                   # builds the folded weights (two launches per block, once)
+        n0 = lib.convnn_b200_launch_count()
+        folded = model(img).float()
+        n1 = lib.convnn_b200_launch_count()
+        for blk in model.transformer_encoder:
+            blk.fold_layernorm = False
+        plain = model(img).float()
+        n2 = lib.convnn_b200_launch_count()
+    assert _capi.device_status() == 0
+    # per block: two LayerNorm launches fewer; once per forward one row-moments launch more
+    assert (n2 - n1) - (n1 - n0) == 2 * cfg.num_layers - 1
+    err = rel_err(folded, plain)
+    print(f"logits, folded against unfused: rel err {err:.3e}")
+    assert err < 0.1
