@@ -166,6 +166,7 @@ int convnn_b200_device_status(int* code) {
     if ((rc = read_sim_topk2_status(&c))) return rc;
     if (!c && (rc = read_dw_stream_status(&c))) return rc;
     if (!c && (rc = read_attention_status(&c))) return rc;
+    if (!c && (rc = read_mlp_tc_status(&c))) return rc;
     *code = a ? a : (b ? b : c);
     return CONVNN_OK;
 }
@@ -551,6 +552,26 @@ int convnn_b200_prenorm_forward(const convnn_desc* d, const void* x, int64_t ldx
     if ((rc = convnn_b200_sim_topk(d, w.q, w.k, w.qstat, w.kstat, nullptr, w.idx, w.val, stream))) return rc;
     if ((rc = convnn_b200_gather_conv(d, w.v, w.idx, w.val, w_conv, w_pw, w.o, w.scratch, stream))) return rc;
     return out_proj_impl(d, w.o, w_o, residual, ldr, out, ldo, w.scratch, stream, moments_out);
+}
+
+int convnn_b200_prenorm_mlp_supported(int32_t D, int32_t DM, int32_t planes) {
+    return (!force_simt() && mlp_tc_supported(D, DM, planes)) ? 1 : 0;
+}
+
+int convnn_b200_prenorm_mlp_moment_planes(void) { return mlp_tc_moment_planes(); }
+
+int convnn_b200_prenorm_mlp(const void* x, int64_t ldx, const float* moments, int32_t planes, float eps,
+                            const void* w1_folded, const void* w1_extra, const void* w2, const void* b2, void* out,
+                            int64_t ldo, int64_t M, int32_t D, int32_t DM, float* moments_out, void* stream) {
+    REQUIRE_PTR(x); REQUIRE_PTR(moments); REQUIRE_PTR(w1_folded); REQUIRE_PTR(w1_extra); REQUIRE_PTR(w2); REQUIRE_PTR(out);
+    if (M < 0 || D < 1 || DM < 1 || ldx < D || ldo < D || planes < 1 || M >= (1ll << 31))
+        return set_error(CONVNN_E_INVALID, "prenorm_mlp: bad shape (M=%lld D=%d d_mlp=%d planes=%d)", (long long)M, D, DM, planes);
+    int rc = check_device();
+    if (rc) return rc;
+    if (M == 0) return CONVNN_OK;
+    if (force_simt()) return set_error(CONVNN_E_UNSUPPORTED, "prenorm_mlp: needs the tensor-core path");
+    return launch_mlp_tc(x, ldx, moments, planes, eps, w1_folded, w1_extra, w2, b2, out, ldo, (int)M, D, DM, moments_out,
+                         static_cast<cudaStream_t>(stream));
 }
 
 // ---- the other halves of the branching wrappers ------------------------------------------------

@@ -134,6 +134,13 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
 int launch_layernorm(int dtype, const void* x, long long ldx, const void* gamma, const void* beta, float eps, void* y,
                      long long ldy, long long rows, int D, const void* pe, const void* cls, int Np,
                      long long cls_rows, cudaStream_t st);
+// The encoder's MLP block (norm2 folded, GELU, both Linear layers, skip connection) as one kernel.
+bool mlp_tc_supported(int D, int DM, int planes);
+int mlp_tc_moment_planes();
+int launch_mlp_tc(const void* x, long long ldx, const float* moments, int planes, float eps, const void* w1_folded,
+                  const void* w1_extra, const void* w2, const void* b2, void* out, long long ldo, int M, int D, int DM,
+                  float* moments_out, cudaStream_t st);
+int read_mlp_tc_status(int* out);
 int launch_row_moments(const void* x, long long ldx, long long rows, int D, float* moments, cudaStream_t st);
 int launch_fold_layernorm(const void* w, const void* bias, const void* gamma, const void* beta, int N, int K,
                           void* w_folded, void* w_extra, cudaStream_t st);

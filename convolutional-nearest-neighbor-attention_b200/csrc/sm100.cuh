@@ -306,6 +306,14 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t bar_cluster) {
                  : "memory");
 }
 
+// The same for the barriers at this shared-memory offset in BOTH CTAs of the pair: one instruction.
+__device__ __forceinline__ void mma_commit_pair_both(uint32_t bar_local) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(bar_local), "h"((unsigned short)3)
+        : "memory");
+}
+
 // ---- TMEM -> registers ---------------------------------------------------------------
 // Each thread of the warp reads N consecutive 32-bit columns of its own TMEM lane
 // (lane = 32 * (warp_id % 4) + lane_id must be encoded in taddr bits 16-31 by the caller).

@@ -330,6 +330,30 @@ def prenorm_forward(spec: LayerSpec, x: torch.Tensor, moments: torch.Tensor, eps
     return out, mom
 
 
+def prenorm_mlp_supported(D: int, DM: int, planes: int) -> bool:
+    return bool(_capi.lib().convnn_b200_prenorm_mlp_supported(D, DM, planes))
+
+
+def prenorm_mlp(x: torch.Tensor, moments: torch.Tensor, eps: float, w1_folded: torch.Tensor, w1_extra: torch.Tensor,
+                w2: torch.Tensor, b2: Optional[torch.Tensor], want_moments: bool = False):
+    """``x + (GELU(LayerNorm(x) @ W1.T + b1) @ W2.T + b2)`` in one kernel (``convnn_b200_prenorm_mlp``).
+    Returns (out, moments of out (planes, stride, 2) or None)."""
+    _require_cuda(x, moments, w1_folded, w1_extra, w2, b2)
+    L = _capi.lib()
+    xv, M, ldx = _flat_rows(x)
+    DM, D = w1_folded.shape
+    w2c = w2 if w2.is_contiguous() else w2.contiguous()
+    out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    mom = None
+    if want_moments:
+        mom = torch.empty(L.convnn_b200_prenorm_mlp_moment_planes(), L.convnn_b200_moment_stride(M), 2,
+                          dtype=torch.float32, device=x.device)
+    _capi.check(L.convnn_b200_prenorm_mlp(xv.data_ptr(), ldx, moments.data_ptr(), moments.shape[0], float(eps),
+                                          w1_folded.data_ptr(), w1_extra.data_ptr(), w2c.data_ptr(), _capi.ptr(b2),
+                                          out.data_ptr(), D, M, D, DM, _capi.ptr(mom), _stream(x)))
+    return out, mom
+
+
 # ---- the other halves of the branching wrappers ------------------------------------------------
 
 def _out_slice(out: Optional[torch.Tensor], like: torch.Tensor) -> Tuple[torch.Tensor, int]:

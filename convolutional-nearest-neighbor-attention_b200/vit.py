@@ -95,6 +95,7 @@ class TransformerEncoder(nn.Module):
         # allow (set to False for a LayerNorm kernel followed by the plain GEMM, the reference's order
         # of roundings)
         self.fold_layernorm = True
+        self.fuse_mlp = True          # with the fold: norm2 + mlp + skip connection as one kernel where it is built
         self._fc1_folded = _PackedParams()
 
     def forward(self, x):
@@ -133,6 +134,9 @@ class TransformerEncoder(nn.Module):
                 m1 = ops.row_moments(x)
             wf, wx = self._fc1_folded.get((fc1.weight, fc1.bias, n2.weight, n2.bias), x.dtype, x.device,
                                           lambda: ops.fold_layernorm(fc1.weight, fc1.bias, n2.weight, n2.bias))
+            if self.fuse_mlp and ops.prenorm_mlp_supported(fc1.in_features, fc1.out_features, m1.shape[0]):
+                # the whole block in one kernel: the hidden activations never reach HBM
+                return ops.prenorm_mlp(x, m1, n2.eps, wf, wx, fc2.weight, fc2.bias, want_moments=want_moments)
             h = ops.prenorm_linear(x, m1, n2.eps, wf, wx, gelu=True)
         else:
             xn = ops.layernorm(x, n2.weight, n2.bias, n2.eps)

@@ -281,6 +281,21 @@ int convnn_b200_prenorm_forward(const convnn_desc* d, const void* x, int64_t ldx
                                 int64_t ldr, void* out, int64_t ldo, float* moments_out, void* workspace,
                                 size_t workspace_bytes, void* stream);
 
+/* The whole MLP block of the encoder as one kernel (vit.py:267-269 with 253-258):
+ *     out = x + (GELU(LayerNorm(x) w1^T + b1) w2^T + b2)
+ * from the un-normalised rows x (M, D) and their moments; the hidden activations (M, d_mlp) stay in
+ * shared memory / TMEM.  w1_folded (d_mlp, D) and w1_extra (d_mlp, 16) come from
+ * convnn_b200_fold_layernorm(w1, b1, gamma, beta); w2 (D, d_mlp) and b2 (D) or NULL as nn.Linear
+ * stores them.  moments_out (or NULL): float32 [convnn_b200_prenorm_mlp_moment_planes()]
+ * [convnn_b200_moment_stride(M)][2], the moments of the rows of out as partial sums.  bfloat16;
+ * D in {64, 128, 192}, d_mlp a multiple of 128, at most 16 planes of incoming moments
+ * (CONVNN_E_UNSUPPORTED otherwise: use prenorm_linear + linear_moments).  out may not alias x. */
+int convnn_b200_prenorm_mlp_supported(int32_t D, int32_t DM, int32_t planes);
+int convnn_b200_prenorm_mlp_moment_planes(void);
+int convnn_b200_prenorm_mlp(const void* x, int64_t ldx, const float* moments, int32_t planes, float eps,
+                            const void* w1_folded, const void* w1_extra, const void* w2, const void* b2, void* out,
+                            int64_t ldo, int64_t M, int32_t D, int32_t DM, float* moments_out, void* stream);
+
 /* ---- the other halves of the reference's branching wrappers (layers.py:574-577, 648-651) ---- */
 
 /* MultiHeadAttention.forward (layers.py:105-130), eval mode, no mask: q, k, v projections with the

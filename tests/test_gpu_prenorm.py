@@ -152,8 +152,71 @@ def test_vit_with_and_without_the_fold():
         plain = model(img).float()
         n2 = lib.convnn_b200_launch_count()
     assert _capi.device_status() == 0
-    # per block: two LayerNorm launches fewer; once per forward one row-moments launch more
-    assert (n2 - n1) - (n1 - n0) == 2 * cfg.num_layers - 1
+    # per block: two LayerNorm launches and (fused MLP) one GEMM launch fewer; once per forward one
+    # row-moments launch more
+    assert (n2 - n1) - (n1 - n0) == 3 * cfg.num_layers - 1
     err = rel_err(folded, plain)
     print(f"logits, folded against unfused: rel err {err:.3e}")
     assert err < 0.1
+
+
+def mlp_f64(x, gamma, beta, w1, b1, w2, b2, eps):
+    xd = x.double()
+    y = F.layer_norm(xd, (x.shape[-1],), gamma.double(), beta.double(), eps)
+    h = F.gelu(y @ w1.double().t() + b1.double())
+    out = h @ w2.double().t()
+    if b2 is not None:
+        out = out + b2.double()
+    return xd + out
+
+
+@pytest.mark.parametrize("M,D,DM,shift,bias2", [(777, 192, 768, 0.0, True), (1, 192, 768, 0.0, True), (256, 192, 768, 2.0, False),
+                                                (50432, 192, 768, 0.0, True), (5000, 192, 768, -1.0, True),
+                                                (1000, 128, 512, 0.5, True), (1000, 64, 256, 0.0, True),
+                                                (300, 192, 1536, 0.0, True)])
+def test_prenorm_mlp_against_float64(M, D, DM, shift, bias2):
+    """The whole MLP block in one kernel (norm2 folded, GELU, both Linear layers, skip connection): within
+    the bfloat16 tolerance of float64 arithmetic on the same inputs and as close as the two-kernel path
+    (prenorm_linear + linear_moments); the emitted moments are those of the stored rows; ragged last
+    tiles, a single row, rows with a large mean, every supported width."""
+    assert ops.prenorm_mlp_supported(D, DM, 1)
+    x = rnd(M, D, seed=31, shift=shift)
+    gamma, beta = rnd(D, seed=32, scale=0.2, shift=1.0), rnd(D, seed=33, scale=0.2)
+    w1, b1 = rnd(DM, D, seed=34, scale=D ** -0.5), rnd(DM, seed=35, scale=0.3)
+    w2, b2 = rnd(D, DM, seed=36, scale=DM ** -0.5), (rnd(D, seed=37, scale=0.3) if bias2 else None)
+    wf, wx = ops.fold_layernorm(w1, b1, gamma, beta)
+    mom = ops.row_moments(x)
+    got, mo = ops.prenorm_mlp(x, mom, 1e-5, wf, wx, w2, b2, want_moments=True)
+    again, _ = ops.prenorm_mlp(x, mom, 1e-5, wf, wx, w2, b2)
+    torch.cuda.synchronize()
+    assert _capi.device_status() == 0
+    assert torch.equal(got, again)
+    want = mlp_f64(x, gamma, beta, w1, b1, w2, b2, 1e-5)
+    two = ops.linear(ops.prenorm_linear(x, mom, 1e-5, wf, wx, gelu=True), w2, b2, residual=x)
+    scale = want.abs().max().item()
+    err = (got.double() - want).abs().max().item() / scale
+    err_two = (two.double() - want).abs().max().item() / scale
+    print(f"max err / scale: one kernel {err:.2e}, two kernels {err_two:.2e}")
+    assert err < 2e-2 and err < 1.5 * err_two + 1e-3
+    assert rel_err(got, want) < 6e-3
+    gd = got.double()
+    tot = mo.double()[:, :M].sum(0)
+    assert torch.allclose(tot[:, 0], gd.sum(1), rtol=1e-5, atol=1e-3)
+    assert torch.allclose(tot[:, 1], (gd * gd).sum(1), rtol=1e-5, atol=1e-3)
+
+
+def test_prenorm_mlp_takes_moments_in_several_planes_and_refuses_other_shapes():
+    M, D, DM = 600, 192, 768
+    x, gamma, beta = rnd(M, D, seed=41), rnd(D, seed=42, shift=1.0, scale=0.1), rnd(D, seed=43, scale=0.1)
+    w1, b1, w2 = rnd(DM, D, seed=44, scale=D ** -0.5), rnd(DM, seed=45), rnd(D, DM, seed=46, scale=DM ** -0.5)
+    wf, wx = ops.fold_layernorm(w1, b1, gamma, beta)
+    m = ops.row_moments(x)
+    parts = torch.stack([m[0] * 0.25, m[0] * 0.5, m[0] * 0.25]).contiguous()
+    a, _ = ops.prenorm_mlp(x, m, 1e-5, wf, wx, w2, None)
+    b, _ = ops.prenorm_mlp(x, parts, 1e-5, wf, wx, w2, None)
+    assert torch.equal(a, b)
+    assert not ops.prenorm_mlp_supported(768, 3072, 2) and not ops.prenorm_mlp_supported(192, 704, 2)
+    with pytest.raises(_capi.ConvnnError):
+        ops.prenorm_mlp(rnd(64, 768, seed=47), ops.row_moments(rnd(64, 768, seed=47)), 1e-5,
+                        torch.zeros(3072, 768, dtype=BF, device=DEV), torch.zeros(3072, 16, dtype=BF, device=DEV),
+                        torch.zeros(768, 3072, dtype=BF, device=DEV), None)
