@@ -50,27 +50,34 @@ namespace {
 
 using namespace sm100;
 
-// GELU (tanh form, as in gelu.cuh) with the two tanh of a pair evaluated by ONE half-precision
-// instruction of the special-function unit, which is what bounds the activation of a 128 x 128
-// super-chunk (16 results per clock and SM).  The half-precision tanh is accurate to ~2^-11, the
-// result is rounded to bfloat16 (2^-9) right after.
-__device__ __forceinline__ f32x2 gelu_pair_h2(f32x2 x) {
-    const f32x2 c1 = pack2(0.0356774081f, 0.0356774081f), c0 = pack2(0.7978845608f, 0.7978845608f);
-    const f32x2 hf = pack2(0.5f, 0.5f);
-    const f32x2 inner = mul2(x, fma2(c1, mul2(x, x), c0));
-    float ia, ib;
-    unpack2(inner, ia, ib);
-    uint32_t h2, t2;
-    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h2) : "f"(ib), "f"(ia));
-    asm("tanh.approx.f16x2 %0, %1;" : "=r"(t2) : "r"(h2));
+// GELU (tanh form, as in gelu.cuh) of a pair of accumulator values, result packed as bfloat16 x 2.
+// With hx = 0.5 * rstd * acc (fp32):  GELU = hx + hx * tanh(u),  u = hx * (2 c0 + 8 c1 hx^2).  The
+// argument u and the tanh are evaluated on the pair in half precision (three packed instructions
+// and ONE special-function instruction for both values; the fp32 form costs four two-cycle packed
+// instructions and two special-function instructions, and the activation of a 128 x 128 super-chunk
+// is what bounds this kernel); the dominant term hx and the final multiply-add stay in fp32.  The
+// half-precision tanh is accurate to ~2^-11, below the bfloat16 rounding (2^-9) of the result.
+__device__ __forceinline__ uint32_t gelu_pair_bf16x2(float a, float b, f32x2 half_rstd) {
+    const f32x2 hx = mul2(pack2(a, b), half_rstd);
+    float ha, hb;
+    unpack2(hx, ha, hb);
+    uint32_t h, t;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h) : "f"(hb), "f"(ha));
+    asm("{\n\t.reg .b32 s, w;\n\t"
+        "mul.rn.f16x2 s, %1, %1;\n\t"
+        "fma.rn.f16x2 w, s, %2, %3;\n\t"
+        "mul.rn.f16x2 w, w, %1;\n\t"
+        "tanh.approx.f16x2 %0, w;\n\t}"
+        : "=r"(t) : "r"(h), "r"(0x34913491u), "r"(0x3e623e62u));      // 8 c1 = 0.2854, 2 c0 = 1.5958
     float ta, tb;
-    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tcvt.f32.f16 %0, lo;\n\tcvt.f32.f16 %1, hi;\n\t}" : "=f"(ta), "=f"(tb) : "r"(t2));
-    const f32x2 hx = mul2(hf, x);
-    return fma2(hx, pack2(ta, tb), hx);
+    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tcvt.f32.f16 %0, lo;\n\tcvt.f32.f16 %1, hi;\n\t}"
+        : "=f"(ta), "=f"(tb) : "r"(t));
+    float oa, ob;
+    unpack2(fma2(hx, pack2(ta, tb), hx), oa, ob);
+    __nv_bfloat162 hv = __floats2bfloat162_rn(oa, ob);
+    return *reinterpret_cast<uint32_t*>(&hv);
 }
-#ifndef GELU_FN
-#define GELU_FN gelu_pair_h2
-#endif
+
 
 constexpr int BM = 128;        // rows per CTA
 constexpr int SC = 128;        // hidden columns per MMA 1 step ("super-chunk"): two h chunks
@@ -326,9 +333,14 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                 const int row = row0_of(it) + j * 32 + lane;
                 float s1 = 0.f, s2 = 0.f;
                 if (row < p.M)
-                    for (int pl = 0; pl < p.planes; ++pl) {
-                        const float2 m = __ldg(p.moments + (long long)pl * p.mom_ld_in + row);
-                        s1 += m.x; s2 += m.y;
+                    for (int pl0 = 0; pl0 < p.planes; pl0 += 4) {      // four independent loads in flight per row
+                        float2 m[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            m[k] = pl0 + k < p.planes ? __ldg(p.moments + (long long)(pl0 + k) * p.mom_ld_in + row)
+                                                      : make_float2(0.f, 0.f);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) { s1 += m[k].x; s2 += m[k].y; }
                     }
                 const float mean = s1 * p.inv_d;
                 const float var = fmaxf(fmaf(-mean, mean, s2 * p.inv_d), 0.f) + p.eps;
@@ -387,16 +399,10 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(leadbar(A1EMPTY + b));              // acc1 buffer may be overwritten
             uint32_t pk[16];
-            const f32x2 r2 = pack2(rstd, rstd);
+            const f32x2 r2 = pack2(0.5f * rstd, 0.5f * rstd);
 #pragma unroll
-            for (int e = 0; e < 16; ++e) {
-                f32x2 x = pack2(__uint_as_float(acc[2 * e]), __uint_as_float(acc[2 * e + 1]));
-                x = GELU_FN(mul2(x, r2));
-                float a, bb;
-                unpack2(x, a, bb);
-                __nv_bfloat162 hv = __floats2bfloat162_rn(a, bb);
-                pk[e] = *reinterpret_cast<uint32_t*>(&hv);
-            }
+            for (int e = 0; e < 16; ++e)
+                pk[e] = gelu_pair_bf16x2(__uint_as_float(acc[2 * e]), __uint_as_float(acc[2 * e + 1]), r2);
             mtrace(cluster_id == 0 && rank == 0 && ew == 0 && lane == 0, 9, n);
             // MMA 2 of the previous super-chunk has read this h chunk
             ok = mbar_wait(&bars[HEMPTY + hb], (n & 1u) ^ 1u, abort_flag);
