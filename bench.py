@@ -294,6 +294,15 @@ def stage_profile(model, B, cfg, dev, sets=4, reps=5):
         "gather_conv": lambda d: ops.gather_conv(spec, d["v"], d["idx"], d["val"], w_conv, w_pw),
         "out_proj": lambda d: ops.out_proj(spec, d["o"], w_o, residual=d["x"]),
     }
+    # the encoder's MLP block as the model runs it: one kernel where the fused form is built
+    blk = model.transformer_encoder[0]
+    n2, fc1, fc2 = blk.norm2, blk.mlp[0], blk.mlp[3]
+    if blk.fold_layernorm and blk.fuse_mlp and ops.prenorm_mlp_supported(fc1.in_features, fc1.out_features, 2):
+        wf, wx = ops.fold_layernorm(fc1.weight, fc1.bias, n2.weight, n2.bias)
+        for d in data:
+            d["mom"] = ops.linear_moments(d["o"], w_o, None, d["x"])[1]      # two planes, as the output projection emits
+        fns["mlp_block"] = lambda d: ops.prenorm_mlp(d["x"], d["mom"], n2.eps, wf, wx, fc2.weight, fc2.bias,
+                                                     want_moments=True)
     out = {}
     torch.cuda.synchronize()
     for name, fn in fns.items():
@@ -381,6 +390,15 @@ def run_single_stage(args) -> int:
            "mlp0": lambda: ops.linear(x, W1, b1, gelu=True),
            "mlp3": lambda: ops.linear(h, W2, b2, residual=x),
            "layernorm": lambda: ops.layernorm(x, gam, bet)}
+    if args.stage in ("mlp_fused", "mlp0_prenorm", "qkv_prenorm", "mlp3_moments"):
+        # the kernels of the folded-LayerNorm encoder path
+        mom = ops.row_moments(x)
+        wf1, wx1 = ops.fold_layernorm(W1, b1, gam, bet)
+        wfq, wxq = ops.fold_layernorm(w_qkv.view(-1, D), None, gam, bet)
+        fns.update({"mlp_fused": lambda: ops.prenorm_mlp(x, mom, 1e-5, wf1, wx1, W2, b2, want_moments=True),
+                    "mlp0_prenorm": lambda: ops.prenorm_linear(x, mom, 1e-5, wf1, wx1, gelu=True),
+                    "qkv_prenorm": lambda: ops.prenorm_linear(x, mom, 1e-5, wfq, wxq),
+                    "mlp3_moments": lambda: ops.linear_moments(h, W2, b2, x)})
     if args.stage in ("attention", "conv1d_attention"):
         # the other halves of the ViT-Base branching wrappers (cfg-4): 384 channels, 12 heads
         Dh, Hh = 384, 12
@@ -570,7 +588,7 @@ NCU_TRAFFIC_BYTES = {"qkv_proj": 19.69e6 + 10.28e6, "sim_topk": 39.2e6 + 0.009e6
                      "out_proj": 19.5e6}
 
 
-def algorithmic_work(B, T, S, D, H, K, elt=2):
+def algorithmic_work(B, T, S, D, H, K, DM=0, elt=2):
     """Compulsory bytes / flops per launch of each stage (one layer call)."""
     idxval = 8 * B * H * T * K
     return {
@@ -580,6 +598,8 @@ def algorithmic_work(B, T, S, D, H, K, elt=2):
         "gather_conv": dict(bytes=elt * (2 * B * T * D + K * D) + idxval, flops=2 * B * T * D * K),
         # (with the skip connection read: one more activation-sized tensor)
         "out_proj": dict(bytes=elt * (3 * B * T * D + D * D), flops=2 * B * T * D * D),
+        # norm2 + mlp.0 + GELU + mlp.3 + skip in one kernel: x in, x out, both weights, moments in (2 planes) / out (4)
+        "mlp_block": dict(bytes=elt * (2 * B * T * D + 2 * D * DM) + 8 * B * T * 6, flops=4 * B * T * D * DM),
     }
 
 
@@ -756,13 +776,14 @@ def run_ours(args) -> int:
     if rank == 0:
         pk = peaks()
         T = cfg.seq_len
-        work = algorithmic_work(B, T, T, cfg.d_hidden, cfg.num_heads, cfg.K)
+        work = algorithmic_work(B, T, T, cfg.d_hidden, cfg.num_heads, cfg.K, cfg.d_mlp)
         dom = max(stage_ms, key=stage_ms.get)
         per_launch_ms = stage_ms[dom]
         ridge = pk["tf_sustained"] * 1e3 / pk["hbm"]
         ai = work[dom]["flops"] / work[dom]["bytes"]
         if ai > ridge:
-            bound, ach, peak, unit = "tensor", work[dom]["flops"] / per_launch_ms / 1e9, pk["tf_sustained"], "TFLOP/s"
+            # a kernel timed alone (a graph of four launches): the burst figure is its denominator
+            bound, ach, peak, unit = "tensor", work[dom]["flops"] / per_launch_ms / 1e9, pk["tf_burst"], "TFLOP/s"
         else:
             bound, ach, peak, unit = "hbm", work[dom]["bytes"] / per_launch_ms / 1e6, pk["hbm"], "GB/s"
         stages = {k: {"ms_per_launch": stage_ms[k], "GBps": work[k]["bytes"] / stage_ms[k] / 1e6,
@@ -832,7 +853,8 @@ def main() -> int:
     ap.add_argument("--no-extras", action="store_true", help="skip the cfg-3 / cfg-4 models and the layer sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--stage", choices=["qkv_proj", "sim_topk", "gather_conv", "out_proj", "out_proj_skip", "mlp0",
-                                        "mlp3", "layernorm", "attention", "conv1d_attention"],
+                                        "mlp3", "layernorm", "attention", "conv1d_attention", "mlp_fused",
+                                        "mlp0_prenorm", "qkv_prenorm", "mlp3_moments"],
                     help="run only this stage of one layer (profiling aid)")
     ap.add_argument("--forward-of", choices=["cfg-2", "cfg-3", "cfg-4"],
                     help="one eager forward of that configuration's whole model (for launch lists)")
