@@ -79,6 +79,8 @@ SIGNATURES = {
     "convnn_b200_prenorm_mlp_moment_planes": (ctypes.c_int, []),
     "convnn_b200_prenorm_mlp": (ctypes.c_int, [c_void, c_i64, c_void, c_i32, ctypes.c_float, c_void, c_void, c_void,
                                                c_void, c_void, c_i64, c_i64, c_i32, c_i32, c_void, c_void]),
+    "convnn_b200_outproj_mlp": (ctypes.c_int, [c_void, c_i64, c_void, c_void, c_i64, ctypes.c_float, c_void, c_void, c_void,
+                                               c_void, c_void, c_i64, c_i64, c_i32, c_i32, c_void, c_void]),
     "convnn_b200_attention_workspace_bytes": (c_size, [ctypes.c_int, c_i32, c_i32, c_i32]),
     "convnn_b200_softmax_attention": (ctypes.c_int, [ctypes.c_int, c_void, c_i64, c_void, c_void, c_void, c_i64, c_i32,
                                                      c_i32, c_i32, c_i32, c_void, c_size, c_void]),

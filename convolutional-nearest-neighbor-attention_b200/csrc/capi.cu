@@ -547,9 +547,14 @@ int convnn_b200_prenorm_forward(const convnn_desc* d, const void* x, int64_t ldx
     Workspace w = carve(dm, d->conv_type, workspace);
     if (workspace_bytes < w.total)
         return set_error(CONVNN_E_WORKSPACE, "workspace has %zu bytes, %zu needed", workspace_bytes, w.total);
+    if (!w_o && (dm.H != 1 || ldo != dm.D || residual || moments_out))
+        return set_error(CONVNN_E_INVALID, "prenorm_forward: without w_o the layer's pre-projection output is written to a "
+                                           "contiguous `out` (num_heads = 1, ldo = D, no residual, no moments)");
     const PreNorm pn{moments, planes, eps, w_qkv_extra};
     if ((rc = qkv_proj_impl(d, x, ldx, w_qkv_folded, nullptr, w.q, w.k, w.v, w.qstat, w.kstat, w.scratch, stream, &pn))) return rc;
     if ((rc = convnn_b200_sim_topk(d, w.q, w.k, w.qstat, w.kstat, nullptr, w.idx, w.val, stream))) return rc;
+    if (!w_o)      // the caller fuses the output projection into what follows (convnn_b200_outproj_mlp)
+        return convnn_b200_gather_conv(d, w.v, w.idx, w.val, w_conv, w_pw, out, w.scratch, stream);
     if ((rc = convnn_b200_gather_conv(d, w.v, w.idx, w.val, w_conv, w_pw, w.o, w.scratch, stream))) return rc;
     return out_proj_impl(d, w.o, w_o, residual, ldr, out, ldo, w.scratch, stream, moments_out);
 }
@@ -571,7 +576,22 @@ int convnn_b200_prenorm_mlp(const void* x, int64_t ldx, const float* moments, in
     if (M == 0) return CONVNN_OK;
     if (force_simt()) return set_error(CONVNN_E_UNSUPPORTED, "prenorm_mlp: needs the tensor-core path");
     return launch_mlp_tc(x, ldx, moments, planes, eps, w1_folded, w1_extra, w2, b2, out, ldo, (int)M, D, DM, moments_out,
-                         static_cast<cudaStream_t>(stream));
+                         nullptr, nullptr, 0, static_cast<cudaStream_t>(stream));
+}
+
+int convnn_b200_outproj_mlp(const void* o, int64_t ld_o, const void* w_o, const void* x, int64_t ldx, float eps,
+                            const void* w1_folded, const void* w1_extra, const void* w2, const void* b2, void* out,
+                            int64_t ldo, int64_t M, int32_t D, int32_t DM, float* moments_out, void* stream) {
+    REQUIRE_PTR(o); REQUIRE_PTR(w_o); REQUIRE_PTR(x); REQUIRE_PTR(w1_folded); REQUIRE_PTR(w1_extra); REQUIRE_PTR(w2);
+    REQUIRE_PTR(out);
+    if (M < 0 || D < 1 || DM < 1 || ld_o < D || ldx < D || ldo < D || M >= (1ll << 31))
+        return set_error(CONVNN_E_INVALID, "outproj_mlp: bad shape (M=%lld D=%d d_mlp=%d)", (long long)M, D, DM);
+    int rc = check_device();
+    if (rc) return rc;
+    if (M == 0) return CONVNN_OK;
+    if (force_simt()) return set_error(CONVNN_E_UNSUPPORTED, "outproj_mlp: needs the tensor-core path");
+    return launch_mlp_tc(o, ld_o, nullptr, 1, eps, w1_folded, w1_extra, w2, b2, out, ldo, (int)M, D, DM, moments_out, w_o, x,
+                         ldx, static_cast<cudaStream_t>(stream));
 }
 
 // ---- the other halves of the branching wrappers ------------------------------------------------

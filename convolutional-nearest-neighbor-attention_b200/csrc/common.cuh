@@ -139,7 +139,7 @@ bool mlp_tc_supported(int D, int DM, int planes);
 int mlp_tc_moment_planes();
 int launch_mlp_tc(const void* x, long long ldx, const float* moments, int planes, float eps, const void* w1_folded,
                   const void* w1_extra, const void* w2, const void* b2, void* out, long long ldo, int M, int D, int DM,
-                  float* moments_out, cudaStream_t st);
+                  float* moments_out, const void* w_o, const void* resid, long long ldr, cudaStream_t st);
 int read_mlp_tc_status(int* out);
 int launch_row_moments(const void* x, long long ldx, long long rows, int D, float* moments, cudaStream_t st);
 int launch_fold_layernorm(const void* w, const void* bias, const void* gamma, const void* beta, int N, int K,

@@ -94,6 +94,8 @@ struct MlpParams {
     long long mom_ld_in, mom_ld_out;
     float eps, inv_d;
     const float2* moments;
+    const __nv_bfloat16* resid;   // OP: the rows x of the skip connection x + o W_o^T, stride ldr
+    long long ldr;
     const __nv_bfloat16* bias2;
     float2* moments_out;   // [4][mom_ld_out] or nullptr
 };
@@ -135,13 +137,22 @@ enum Bar : int {            // indices into the barrier array
     A2EMPTY = 21,           // [1] leader: 16 warps x 2 CTAs have read it
     XAFULL = 22,            // [2] leader: extra chunk of both CTAs written
     OUTREADY = 24,          // [2] local: the 16 epilogue warps have finished the tile's rows in the x buffer
-    NBARS = 26
+    STATREADY = 26,         // [2] local (OP): the 16 epilogue warps have written x1 and its partial moments
+    NBARS = 28
 };
 
+// OP: the attention layer's output projection and skip connection run first, per tile:
+//     x1 = x + bf16(o W_o^T)           (reference layers.py:320 with vit.py:264)
+// o arrives where x would (TMA into the x buffer), W_o passes through the W1 ring as two items of D/2
+// output columns, the accumulators are the two acc1 buffers, and the epilogue warps write x1 over o in
+// the x buffer (the operand of MMA 1 and the skip connection of the final epilogue) together with the
+// partial moments of its rows, from which the extra-chunk warp derives mean and rstd: the block then
+// needs no moments from outside.
+template <bool OP>
 __global__ void __launch_bounds__(NT, 1)
 mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmO,
               const __grid_constant__ CUtensorMap tmW1, const __grid_constant__ CUtensorMap tmWX,
-              const __grid_constant__ CUtensorMap tmW2, const MlpParams p) {
+              const __grid_constant__ CUtensorMap tmW2, const __grid_constant__ CUtensorMap tmWO, const MlpParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const Smem L = smem_plan(p.D);
@@ -168,10 +179,12 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         init(A2FULL, 1, 1); init(A2EMPTY, 1, 32);
         init(XAFULL, 2, 2);
         init(OUTREADY, 2, 16);
+        init(STATREADY, 2, 16);
         *abort_flag = 0;
         fence_barrier_init();
         prefetch_tensormap(&tmX); prefetch_tensormap(&tmO); prefetch_tensormap(&tmW1);
         prefetch_tensormap(&tmWX); prefetch_tensormap(&tmW2);
+        if (OP) prefetch_tensormap(&tmWO);
     }
     __syncthreads();
     if (warp == 1) { tmem_alloc_pair(tmem_slot, 512); tmem_relinquish_pair(); }
@@ -194,6 +207,11 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     const uint32_t x_tile_bytes = (uint32_t)p.KC * 16384u;
     auto row0_of = [&](int it) { return (cluster_id + it * n_clusters) * 2 * BM + (int)rank * BM; };
     const uint32_t acc2_col = 2 * SC;            // TMEM: acc1[2] at columns 0 / 128, acc2 behind them
+    // Order of the accumulator items of a tile (the same in the producer, the MMA 1 thread and the epilogue
+    // warps): its super-chunks 0 .. nsc - 1 and, with OP, the two output-projection items of the NEXT tile in
+    // front of super-chunk kp, so that x1, its moments and the extra operand chunk of the next tile are
+    // ready long before that tile's first MMA 1; tile 0's own two items come first of all.
+    const int kp = nsc >= 4 ? nsc - 2 : nsc - 1;
 
     if (warp == 0) {
         // ---- TMA producers (each CTA fetches its own rows of x and its half of every weight chunk).
@@ -215,12 +233,28 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                     tma_load_2d_pair(base + L.x + xb * x_tile_bytes + lane * 16384u, &tmX, leadbar(XFULL + xb), lane * 64, row0_of(it));
             };
             if (my_tiles > 0) load_x(0);
-            uint32_t n = 0;                                        // running super-chunk number
+            uint32_t n = 0;                                        // running accumulator item number
+            // W_o as two items of D/2 output columns (D/4 rows per CTA), sub-chunks 8 KB apart
+            auto load_wo = [&]() {
+                for (int item = 0; item < 2 && ok; ++item, ++n) {
+                    const uint32_t b = n & 1u;
+                    ok = mbar_wait(&bars[A1FULL + b], ((n >> 1) & 1u) ^ 1u, abort_flag);
+                    ok = __all_sync(w1_mask, ok);
+                    if (!ok) { if (lane == 0) give_up(52); break; }
+                    mtrace(cluster_id == 0 && rank == 0 && lane == 0, 1, n);
+                    if (rank == 0 && lane == 0) mbar_expect_tx_a(lbar(W1FULL + b), 2u * (uint32_t)p.KC * (uint32_t)(p.D / 4) * 128u);
+                    __syncwarp(w1_mask);
+                    if (lane < p.KC)
+                        tma_load_2d_pair(base + L.w1 + b * L.w1_slot + lane * 8192u, &tmWO, leadbar(W1FULL + b), lane * 64,
+                                         item * (p.D / 2) + (int)rank * (p.D / 4));
+                }
+            };
+            if (OP && my_tiles > 0) load_wo();
             for (int it = 0; it < my_tiles && ok; ++it) {
                 for (int sc = 0; sc < nsc && ok; ++sc, ++n) {
+                    if (OP && sc == kp && it + 1 < my_tiles) { load_wo(); if (!ok) break; }
                     const uint32_t b = n & 1u;
-                    if (sc == nsc / 2 && it + 1 < my_tiles) { load_x(it + 1); if (!ok) break; }
-                    // the slot's previous super-chunk (n - 2) has been multiplied
+                    // the slot's previous item (n - 2) has been multiplied
                     ok = mbar_wait(&bars[A1FULL + b], ((n >> 1) & 1u) ^ 1u, abort_flag);
                     ok = __all_sync(w1_mask, ok);
                     if (!ok) { if (lane == 0) give_up(52); break; }
@@ -235,7 +269,15 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                 }
             }
         } else if (lane == p.KC + 2) {
-            // the finished rows of a tile leave through a TMA store of the x buffer they were written into
+            // the finished rows of a tile leave through a TMA store of the x buffer they were written into;
+            // the buffer is refilled at once with the tile after the next (tile 1 is requested up front)
+            auto load_next = [&](int it) {
+                const uint32_t xb = (uint32_t)it & 1u;
+                if (rank == 0) mbar_expect_tx_a(lbar(XFULL + xb), 2u * x_tile_bytes);
+                for (int kc = 0; kc < p.KC; ++kc)
+                    tma_load_2d_pair(base + L.x + xb * x_tile_bytes + kc * 16384u, &tmX, leadbar(XFULL + xb), kc * 64, row0_of(it));
+            };
+            if (my_tiles > 1) load_next(1);
             for (int it = 0; it < my_tiles; ++it) {
                 const uint32_t xb = (uint32_t)it & 1u;
                 if (!mbar_wait_a(lbar(OUTREADY + xb), (uint32_t)(it >> 1) & 1u, abort_flag)) { give_up(66); break; }
@@ -243,7 +285,8 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                     tma_store_2d(&tmO, smem + L.x + xb * x_tile_bytes + kc * 16384u, kc * 64, row0_of(it));
                 tma_store_commit();
                 tma_store_wait_read<0>();
-                mbar_arrive(&bars[XFREE + xb]);                   // the producer may refill this x buffer
+                mbar_arrive(&bars[XFREE + xb]);                   // the buffer's contents are no longer needed
+                if (it + 2 < my_tiles) load_next(it + 2);
             }
             tma_store_wait<0>();
         } else if (lane == p.KC + 1) {
@@ -268,28 +311,51 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             const uint32_t idesc1 = make_idesc_bf16_f32(2 * BM, SC);
             const uint64_t dhi = kmajor_desc_hi(128), dhi32 = kmajor_desc_hi(32);
             auto desc = [&](uint64_t hi, uint32_t addr) { return hi | (uint64_t)((addr & 0x3FFFFu) >> 4); };
-            const uint32_t total = (uint32_t)my_tiles * (uint32_t)nsc;
-            int sc = 0, it = 0;
-            for (uint32_t n = 0; n < total; ++n) {
-                const uint32_t b = n & 1u, xb = (uint32_t)it & 1u;
-                if (sc == 0) {
-                    if (!mbar_wait_a(lbar(XFULL + xb), (uint32_t)(it >> 1) & 1u, abort_flag)) { give_up(54); break; }
-                    if (!mbar_wait_a(lbar(XAFULL + xb), (uint32_t)(it >> 1) & 1u, abort_flag)) { give_up(55); break; }
+            const uint32_t idesc0 = make_idesc_bf16_f32(2 * BM, p.D / 2);
+            uint32_t n = 0;                                        // running accumulator item number
+            bool ok = true;
+            // the two output-projection items of tile `it`: acc1[n & 1] = o W_o[item]^T, N = D / 2
+            auto mma_wo = [&](int it) {
+                const uint32_t xb = (uint32_t)it & 1u;
+                if (!mbar_wait_a(lbar(XFULL + xb), (uint32_t)(it >> 1) & 1u, abort_flag)) { give_up(54); ok = false; return; }
+                for (int item = 0; item < 2; ++item, ++n) {
+                    const uint32_t b = n & 1u;
+                    if (!mbar_wait_a(lbar(A1EMPTY + b), ((n >> 1) & 1u) ^ 1u, abort_flag)) { give_up(56); ok = false; return; }
+                    mtrace(cluster_id == 0, 2, n);
+                    if (!mbar_wait_a(lbar(W1FULL + b), (n >> 1) & 1u, abort_flag)) { give_up(57); ok = false; return; }
+                    mtrace(cluster_id == 0, 3, n);
+                    tc_fence_after_sync();
+                    const uint32_t xs0 = base + L.x + xb * x_tile_bytes, w0s = base + L.w1 + b * L.w1_slot;
+                    for (int kc = 0; kc < p.KC; ++kc)
+                        mma_chunk_pair(tmem_base + b * SC, desc(dhi, xs0 + kc * 16384u), desc(dhi, w0s + kc * 8192u), idesc0, 4, kc != 0);
+                    mma_commit_pair_both(lbar(A1FULL + b));
+                    mtrace(cluster_id == 0, 4, n);
                 }
-                if (!mbar_wait_a(lbar(A1EMPTY + b), ((n >> 1) & 1u) ^ 1u, abort_flag)) { give_up(56); break; }
-                mtrace(cluster_id == 0, 2, n);
-                if (!mbar_wait_a(lbar(W1FULL + b), (n >> 1) & 1u, abort_flag)) { give_up(57); break; }
-                mtrace(cluster_id == 0, 3, n);
-                tc_fence_after_sync();
-                const uint32_t d1 = tmem_base + b * SC;
-                const uint32_t xs = base + L.x + xb * x_tile_bytes, w1s = base + L.w1 + b * L.w1_slot;
-                for (int kc = 0; kc < p.KC; ++kc)
-                    mma_chunk_pair(d1, desc(dhi, xs + kc * 16384u), desc(dhi, w1s + kc * 8192u), idesc1, 4, kc != 0);
-                // the pre-norm fold's extra step: [-mean, sigma] x [c, b']
-                mma_bf16_ss_pair(d1, desc(dhi32, base + L.xa + xb * 4096u), desc(dhi32, w1s + p.KC * 8192u), idesc1, 1);
-                mma_commit_pair_both(lbar(A1FULL + b));
-                mtrace(cluster_id == 0, 4, n);
-                if (++sc == nsc) { sc = 0; ++it; }
+            };
+            if (OP && my_tiles > 0) mma_wo(0);
+            for (int it = 0; it < my_tiles && ok; ++it) {
+                const uint32_t xb = (uint32_t)it & 1u;
+                for (int sc = 0; sc < nsc && ok; ++sc, ++n) {
+                    if (OP && sc == kp && it + 1 < my_tiles) { mma_wo(it + 1); if (!ok) break; }
+                    const uint32_t b = n & 1u;
+                    if (sc == 0) {
+                        if (!OP && !mbar_wait_a(lbar(XFULL + xb), (uint32_t)(it >> 1) & 1u, abort_flag)) { give_up(54); ok = false; break; }
+                        if (!mbar_wait_a(lbar(XAFULL + xb), (uint32_t)(it >> 1) & 1u, abort_flag)) { give_up(55); ok = false; break; }
+                    }
+                    if (!mbar_wait_a(lbar(A1EMPTY + b), ((n >> 1) & 1u) ^ 1u, abort_flag)) { give_up(56); ok = false; break; }
+                    mtrace(cluster_id == 0, 2, n);
+                    if (!mbar_wait_a(lbar(W1FULL + b), (n >> 1) & 1u, abort_flag)) { give_up(57); ok = false; break; }
+                    mtrace(cluster_id == 0, 3, n);
+                    tc_fence_after_sync();
+                    const uint32_t d1 = tmem_base + b * SC;
+                    const uint32_t xs = base + L.x + xb * x_tile_bytes, w1s = base + L.w1 + b * L.w1_slot;
+                    for (int kc = 0; kc < p.KC; ++kc)
+                        mma_chunk_pair(d1, desc(dhi, xs + kc * 16384u), desc(dhi, w1s + kc * 8192u), idesc1, 4, kc != 0);
+                    // the pre-norm fold's extra step: [-mean, sigma] x [c, b']
+                    mma_bf16_ss_pair(d1, desc(dhi32, base + L.xa + xb * 4096u), desc(dhi32, w1s + p.KC * 8192u), idesc1, 1);
+                    mma_commit_pair_both(lbar(A1FULL + b));
+                    mtrace(cluster_id == 0, 4, n);
+                }
             }
         }
     } else if (warp == 19) {
@@ -328,11 +394,24 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             const uint32_t xb = (uint32_t)it & 1u;
             uint32_t wm[4], wsg[4];
             float rs[4];
+            if (OP) {
+                // x1 and the partial moments of its rows (one partial per 32-column group of an item pair,
+                // kept in this buffer's extra-chunk space) are ready
+                ok = mbar_wait(&bars[STATREADY + xb], (uint32_t)(it >> 1) & 1u, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) { if (lane == 0) give_up(61); break; }
+            }
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const int row = row0_of(it) + j * 32 + lane;
                 float s1 = 0.f, s2 = 0.f;
-                if (row < p.M)
+                if (OP) {
+                    const float2* part = reinterpret_cast<const float2*>(smem + L.xa + xb * 4096u);
+                    for (int gq = 0; gq < p.D / 64; ++gq) {
+                        const float2 m = part[gq * BM + j * 32 + lane];
+                        s1 += m.x; s2 += m.y;
+                    }
+                } else if (row < p.M)
                     for (int pl0 = 0; pl0 < p.planes; pl0 += 4) {      // four independent loads in flight per row
                         float2 m[4];
 #pragma unroll
@@ -352,11 +431,15 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                 wm[j] = (uint32_t)__bfloat16_as_ushort(mh) | ((uint32_t)__bfloat16_as_ushort(ml) << 16);
                 wsg[j] = (uint32_t)__bfloat16_as_ushort(sh) | ((uint32_t)__bfloat16_as_ushort(sl) << 16);
             }
-            // the buffer's previous tile (it - 2) is completely done: its MMAs have read the extra chunk and
-            // its epilogue warps took rstd into registers at their first super-chunk
-            ok = mbar_wait(&bars[XFREE + xb], ((uint32_t)(it >> 1) & 1u) ^ 1u, abort_flag);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) { if (lane == 0) give_up(62); break; }
+            if (OP) {
+                __syncwarp();                                     // every lane has read its partials: the space is rewritten below
+            } else {
+                // the buffer's previous tile (it - 2) is completely done: its MMAs have read the extra chunk
+                // and its epilogue warps took rstd into registers at their first super-chunk
+                ok = mbar_wait(&bars[XFREE + xb], ((uint32_t)(it >> 1) & 1u) ^ 1u, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) { if (lane == 0) give_up(62); break; }
+            }
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const int r = j * 32 + lane;
@@ -381,7 +464,7 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         const int qcols = p.D / 4;                                // output columns of this warp: 16, 32 or 48
         bool alive = true;
         auto die = [&](int code) { if (lane == 0) give_up(code); alive = false; };
-        uint32_t n = 0;                                           // running super-chunk number
+        uint32_t n = 0, ns = 0;                                   // running accumulator item / super-chunk number
         float rstd = 1.0f;
         // one super-chunk: 32 columns of acc1 -> GELU -> this warp's 64 bytes of every row of an h chunk
         auto gelu_step = [&](int it, int sc) {
@@ -405,7 +488,7 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                 pk[e] = gelu_pair_bf16x2(__uint_as_float(acc[2 * e]), __uint_as_float(acc[2 * e + 1]), r2);
             mtrace(cluster_id == 0 && rank == 0 && ew == 0 && lane == 0, 9, n);
             // MMA 2 of the previous super-chunk has read this h chunk
-            ok = mbar_wait(&bars[HEMPTY + hb], (n & 1u) ^ 1u, abort_flag);
+            ok = mbar_wait(&bars[HEMPTY + hb], (ns & 1u) ^ 1u, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) { die(64); return; }
             mtrace(cluster_id == 0 && rank == 0 && ew == 0 && lane == 0, 10, n);
@@ -422,13 +505,92 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             mtrace(cluster_id == 0 && rank == 0 && ew == 0 && lane == 0, 11, n);
             if (lane == 0) mbar_arrive_cluster(leadbar(HFULL + hb));
             ++n;
+            ++ns;
         };
-        for (int it = 0; it < my_tiles; ++it) {
+        // OP: x1 = x + bf16(o W_o^T) for this warp's 32 columns of both items, written over o in the x buffer
+        auto outproj_prefetch = [&](int it) {
+            const int grow = row0_of(it) + r;
+            if (cg < p.D / 64 && grow < p.M) {
+#pragma unroll
+                for (int item = 0; item < 2; ++item)
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(p.resid + (long long)grow * p.ldr + item * (p.D / 2) + cg * 32));
+            }
+        };
+        auto outproj_step = [&](int it) {
+            const uint32_t xb2 = (uint32_t)it & 1u;
+            const uint32_t b0 = n & 1u, b1 = b0 ^ 1u;
+            const int ngrp = p.D / 64;                            // 32-column groups per item
+            const int grow = row0_of(it) + r;
+            // both items first: the MMAs of the second still read all of o
+            bool ok = mbar_wait(&bars[A1FULL + b0], (n >> 1) & 1u, abort_flag);
+            if (ok) ok = mbar_wait(&bars[A1FULL + b1], ((n + 1) >> 1) & 1u, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) { die(67); return; }
+            tc_fence_after_sync();
+            const uint32_t xrow = base + L.x + xb2 * x_tile_bytes + (uint32_t)r * 128u;
+            float m1 = 0.f, m2 = 0.f;
+#pragma unroll 1
+            for (int item = 0; item < 2; ++item) {
+                const uint32_t bi = item == 0 ? b0 : b1;
+                // the skip connection's values for these 32 columns (brought into L2 a super-chunk earlier)
+                uint4 rx[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    rx[j] = make_uint4(0, 0, 0, 0);
+                    if (cg < ngrp && grow < p.M)
+                        rx[j] = __ldg(reinterpret_cast<const uint4*>(p.resid + (long long)grow * p.ldr + item * (p.D / 2) + cg * 32 + j * 8));
+                }
+                uint32_t acc[32];
+                if (cg < ngrp) {
+                    tmem_ld_x32(tmem_base + lane_addr + bi * SC + cg * 32, acc);
+                    tmem_ld_wait();
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(leadbar(A1EMPTY + bi));
+                if (cg < ngrp) {
+                    const int col0 = item * (p.D / 2) + cg * 32;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint32_t xw[4] = {rx[j].x, rx[j].y, rx[j].z, rx[j].w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            __nv_bfloat162 hv = __floats2bfloat162_rn(__uint_as_float(acc[j * 8 + 2 * e]),
+                                                                      __uint_as_float(acc[j * 8 + 2 * e + 1]));
+                            hv = __hadd2(hv, *reinterpret_cast<__nv_bfloat162*>(&xw[e]));
+                            xw[e] = *reinterpret_cast<uint32_t*>(&hv);
+                            const float lo = __uint_as_float(xw[e] << 16), hi = __uint_as_float(xw[e] & 0xffff0000u);
+                            m1 += lo + hi;
+                            m2 = fmaf(hi, hi, fmaf(lo, lo, m2));
+                        }
+                        const int col = col0 + j * 8;
+                        const uint32_t addr = xrow + (uint32_t)(col >> 6) * 16384u +
+                                              ((((uint32_t)(col & 63) >> 3) ^ ((uint32_t)r & 7u)) << 4);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(xw[0]), "r"(xw[1]), "r"(xw[2]),
+                                     "r"(xw[3])
+                                     : "memory");
+                    }
+                }
+            }
+            if (cg < ngrp) reinterpret_cast<float2*>(smem + L.xa + xb2 * 4096u)[cg * BM + r] = make_float2(m1, m2);
+            fence_proxy_async();                                  // x1 in the x buffer -> visible to MMA 1
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars[STATREADY + xb2]);
+            n += 2;
+        };
+        // Per tile `it`: its super-chunks 1 .. nsc - 1, then super-chunk 0 of tile it + 1 (slot sc == nsc: it is
+        // activated before the final epilogue of tile it, whose last MMA 2 drains meanwhile), with the
+        // output-projection step of tile it + 1 in front of slot kp.  Round it = -1 (OP only) holds what
+        // precedes tile 0: its output-projection step and its super-chunk 0.
+        for (int it = OP ? -1 : 0; it < my_tiles; ++it) {
             const uint32_t xb = (uint32_t)it & 1u;
-            // the first super-chunk of a tile is activated before the final epilogue of the tile before it
-            // (its accumulator is ready long before the last MMA 2 of that tile has drained)
-            for (int sc = it == 0 ? 0 : 1; sc < nsc && alive; ++sc) gelu_step(it, sc);
-            if (it + 1 < my_tiles && alive) gelu_step(it + 1, 0);
+            for (int sc = it < 0 ? kp : ((it == 0 && !OP) ? 0 : 1); sc <= nsc && alive; ++sc) {
+                if (OP && sc == kp - 1 && it + 1 < my_tiles) outproj_prefetch(it + 1);
+                if (OP && sc == kp && it + 1 < my_tiles) outproj_step(it + 1);
+                const int git = sc < nsc ? it : it + 1, gsc = sc < nsc ? sc : 0;
+                if (alive && git >= 0 && git < my_tiles) gelu_step(git, gsc);
+            }
+            if (it < 0) continue;
             // ---- final epilogue of the tile: out = x + round(acc2 + b2), in place in the x tile ----
             if (alive) {
                 bool ok = mbar_wait(&bars[A2FULL], (uint32_t)it & 1u, abort_flag);
@@ -439,21 +601,18 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             if (alive) {
                 tc_fence_after_sync();
                 const uint32_t t2 = tmem_base + lane_addr + acc2_col + cg * qcols;
-                uint32_t a2[48];
-#pragma unroll
-                for (int k = 0; k < 3; ++k)
-                    if (k * 16 < qcols) tmem_ld_x16(t2 + k * 16, *reinterpret_cast<uint32_t(*)[16]>(&a2[k * 16]));
-                tmem_ld_wait();
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(leadbar(A2EMPTY));              // acc2 may be overwritten
-                mtrace(cluster_id == 0 && rank == 0 && ew == 0 && lane == 0, 13, it);
                 float m1 = 0.f, m2 = 0.f;
                 const uint32_t xrow = base + L.x + xb * x_tile_bytes + (uint32_t)r * 128u;
+                // 16 accumulator columns at a time (few live registers: this code shares its thread with the
+                // activation step)
+#pragma unroll 1
+                for (int k = 0; k * 16 < qcols; ++k) {
+                    uint32_t a2[16];
+                    tmem_ld_x16(t2 + k * 16, a2);
+                    tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 6; ++i) {
-                    if (i * 8 < qcols) {
-                        const int col = cg * qcols + i * 8;
+                    for (int i = 0; i < 2; ++i) {
+                        const int col = cg * qcols + k * 16 + i * 8;
                         const uint32_t addr = xrow + (uint32_t)(col >> 6) * 16384u +
                                               ((((uint32_t)(col & 63) >> 3) ^ ((uint32_t)r & 7u)) << 4);
                         uint4 xv, bv;
@@ -480,6 +639,9 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                                      : "memory");
                     }
                 }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(leadbar(A2EMPTY));              // acc2 may be overwritten
                 // this warp's quarter of the row moments: plane cg
                 const int grow = row0_of(it) + r;
                 if (p.moments_out && grow < p.M) p.moments_out[(long long)cg * p.mom_ld_out + grow] = make_float2(m1, m2);
@@ -515,12 +677,14 @@ int mlp_tc_moment_planes() { return 4; }
 
 int launch_mlp_tc(const void* x, long long ldx, const float* moments, int planes, float eps, const void* w1_folded,
                   const void* w1_extra, const void* w2, const void* b2, void* out, long long ldo, int M, int D, int DM,
-                  float* moments_out, cudaStream_t st) {
+                  float* moments_out, const void* w_o, const void* resid, long long ldr, cudaStream_t st) {
     if (!mlp_tc_supported(D, DM, planes))
         return set_error(CONVNN_E_UNSUPPORTED, "mlp_tc: D=%d d_mlp=%d planes=%d is outside the fused kernel's shapes", D, DM, planes);
     if (!aligned16(x) || !aligned16(out) || !aligned16(w1_folded) || !aligned16(w1_extra) || !aligned16(w2) ||
-        !aligned16(moments) || (b2 && !aligned16(b2)) || ldx % 8 != 0 || ldo % 8 != 0 || (moments_out && (reinterpret_cast<uintptr_t>(moments_out) & 7u)))
+        (!w_o && !aligned16(moments)) || (b2 && !aligned16(b2)) || (w_o && (!aligned16(w_o) || !aligned16(resid) || ldr % 8 != 0)) || ldx % 8 != 0 || ldo % 8 != 0 || (moments_out && (reinterpret_cast<uintptr_t>(moments_out) & 7u)))
         return set_error(CONVNN_E_ALIGN, "mlp_tc: pointers must be 16-byte aligned, leading dimensions multiples of 8");
+    if (w_o && DM < 256)
+        return set_error(CONVNN_E_UNSUPPORTED, "mlp_tc: the fused output projection needs d_mlp >= 256");
     MlpParams p{};
     p.M = M; p.D = D; p.DM = DM; p.KC = D / 64; p.n_sc = DM / SC;
     p.moments = reinterpret_cast<const float2*>(moments);
@@ -528,8 +692,9 @@ int launch_mlp_tc(const void* x, long long ldx, const float* moments, int planes
     p.n_ptiles = (M + 2 * BM - 1) / (2 * BM);
     p.planes = planes; p.eps = eps; p.inv_d = 1.0f / (float)D;
     p.bias2 = static_cast<const __nv_bfloat16*>(b2);
+    p.resid = static_cast<const __nv_bfloat16*>(resid); p.ldr = ldr;
     p.moments_out = reinterpret_cast<float2*>(moments_out);
-    CUtensorMap tmX, tmO, tmW1, tmWX, tmW2;
+    CUtensorMap tmX, tmO, tmW1, tmWX, tmW2, tmWO;
     {
         const uint64_t dims[2] = {(uint64_t)D, (uint64_t)M};
         const uint32_t box[2] = {64, (uint32_t)BM};
@@ -550,8 +715,15 @@ int launch_mlp_tc(const void* x, long long ldx, const float* moments, int planes
         const uint32_t box[2] = {64, (uint32_t)(D / 2)};
         if (!encode_tensor_map_bf16(&tmW2, w2, 2, dims, str, box, 128)) return CONVNN_E_CUDA;
     }
+    if (w_o) {
+        const uint64_t dims[2] = {(uint64_t)D, (uint64_t)D}, str[1] = {(uint64_t)D * 2};
+        const uint32_t box[2] = {64, (uint32_t)(D / 4)};
+        if (!encode_tensor_map_bf16(&tmWO, w_o, 2, dims, str, box, 128)) return CONVNN_E_CUDA;
+    } else {
+        tmWO = tmW2;
+    }
     const size_t smem = smem_plan(D).total + 1024;
-    auto kern = mlp_tc_kernel;
+    auto kern = w_o ? mlp_tc_kernel<true> : mlp_tc_kernel<false>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return set_error(CONVNN_E_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     cudaLaunchConfig_t cfg{};
@@ -574,7 +746,7 @@ int launch_mlp_tc(const void* x, long long ldx, const float* moments, int planes
     }
     const int nc = p.n_ptiles < max_clusters ? p.n_ptiles : max_clusters;
     cfg.gridDim = dim3(2 * nc);
-    e = cudaLaunchKernelEx(&cfg, kern, tmX, tmO, tmW1, tmWX, tmW2, p);
+    e = cudaLaunchKernelEx(&cfg, kern, tmX, tmO, tmW1, tmWX, tmW2, tmWO, p);
     if (e != cudaSuccess) return set_error(CONVNN_E_CUDA, "mlp_tc launch: %s", cudaGetErrorString(e));
     CONVNN_CHECK_LAUNCH("mlp_tc");
     return CONVNN_OK;

@@ -153,9 +153,11 @@ class MultiHeadConvNNAttention(nn.Module):
                 ops.prenorm_forward_supported(self._spec(), x.shape[0], x.shape[1], x.dtype))
 
     def forward_prenorm(self, x, moments, norm: nn.LayerNorm, residual: Optional[torch.Tensor] = None,
-                        want_moments: bool = False):
+                        want_moments: bool = False, skip_out_proj: bool = False):
         """``layer(norm(x))`` (``+ residual``) from the rows ``x`` BEFORE ``norm`` and their moments,
-        the LayerNorm folded into the K/V/Q projection.  Returns (out, moments of out or None)."""
+        the LayerNorm folded into the K/V/Q projection.  Returns (out, moments of out or None).  With
+        ``skip_out_proj`` (num_heads = 1) the result is the layer's output BEFORE ``W_o``, for a caller
+        that fuses the projection into what follows (``ops.outproj_mlp`` with ``self.packed_w_o``)."""
         self._check_mode(x)
         w_qkv, w_conv, w_pw, w_o = self.packed_weights(x.dtype, x.device)
         if getattr(self, "_folded", None) is None:
@@ -163,7 +165,8 @@ class MultiHeadConvNNAttention(nn.Module):
         wf, wx = self._folded.get((w_qkv, norm.weight, norm.bias), x.dtype, x.device, lambda: ops.fold_layernorm(
             w_qkv.view(-1, w_qkv.shape[-1]), None, norm.weight.detach().to(x.device, x.dtype),
             norm.bias.detach().to(x.device, x.dtype)))
-        return ops.prenorm_forward(self._spec(), x, moments, norm.eps, (wf, wx, w_conv, w_pw, w_o),
+        self.packed_w_o = w_o
+        return ops.prenorm_forward(self._spec(), x, moments, norm.eps, (wf, wx, w_conv, w_pw, None if skip_out_proj else w_o),
                                    residual=residual, want_moments=want_moments)
 
     def _forward_staged(self, x, packed, cand, out, residual=None):

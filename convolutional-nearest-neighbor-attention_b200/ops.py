@@ -306,7 +306,7 @@ def prenorm_forward(spec: LayerSpec, x: torch.Tensor, moments: torch.Tensor, eps
                     workspace: Optional[torch.Tensor] = None):
     """``[residual +] layer(LayerNorm(x))`` through ``convnn_b200_prenorm_forward``; ``packed_folded`` =
     (w_qkv_folded (3D, D), w_qkv_extra (3D, 16), w_conv, w_pw, w_o).  Returns (out, moments of out or None)."""
-    w_qkv, w_qkv_x, w_conv, w_pw, w_o = packed_folded
+    w_qkv, w_qkv_x, w_conv, w_pw, w_o = packed_folded      # w_o None: stop before the output projection
     _require_cuda(x, w_qkv, moments)
     L = _capi.lib()
     x, ldx = _rows_view(x)
@@ -325,7 +325,7 @@ def prenorm_forward(spec: LayerSpec, x: torch.Tensor, moments: torch.Tensor, eps
                           device=x.device)
     _capi.check(L.convnn_b200_prenorm_forward(d, x.data_ptr(), ldx, moments.data_ptr(), moments.shape[0], float(eps),
                                               w_qkv.data_ptr(), w_qkv_x.data_ptr(), w_conv.data_ptr(), _capi.ptr(w_pw),
-                                              w_o.data_ptr(), _capi.ptr(res), ldr, out.data_ptr(), D,
+                                              _capi.ptr(w_o), _capi.ptr(res), ldr, out.data_ptr(), D,
                                               _capi.ptr(mom), workspace.data_ptr(), workspace.numel(), _stream(x)))
     return out, mom
 
@@ -349,6 +349,27 @@ def prenorm_mlp(x: torch.Tensor, moments: torch.Tensor, eps: float, w1_folded: t
         mom = torch.empty(L.convnn_b200_prenorm_mlp_moment_planes(), L.convnn_b200_moment_stride(M), 2,
                           dtype=torch.float32, device=x.device)
     _capi.check(L.convnn_b200_prenorm_mlp(xv.data_ptr(), ldx, moments.data_ptr(), moments.shape[0], float(eps),
+                                          w1_folded.data_ptr(), w1_extra.data_ptr(), w2c.data_ptr(), _capi.ptr(b2),
+                                          out.data_ptr(), D, M, D, DM, _capi.ptr(mom), _stream(x)))
+    return out, mom
+
+
+def outproj_mlp(o: torch.Tensor, w_o: torch.Tensor, x: torch.Tensor, eps: float, w1_folded: torch.Tensor,
+                w1_extra: torch.Tensor, w2: torch.Tensor, b2: Optional[torch.Tensor], want_moments: bool = False):
+    """``x1 = x + o @ W_o.T; x1 + mlp(LayerNorm(x1))`` in one kernel (``convnn_b200_outproj_mlp``); ``o`` is the
+    attention layer's head-merged output before its output projection.  Returns (out, moments of out or None)."""
+    _require_cuda(o, w_o, x, w1_folded, w1_extra, w2, b2)
+    L = _capi.lib()
+    ov, M, ld_o = _flat_rows(o)
+    xv, _, ldx = _flat_rows(x)
+    DM, D = w1_folded.shape
+    w2c = w2 if w2.is_contiguous() else w2.contiguous()
+    out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    mom = None
+    if want_moments:
+        mom = torch.empty(L.convnn_b200_prenorm_mlp_moment_planes(), L.convnn_b200_moment_stride(M), 2,
+                          dtype=torch.float32, device=x.device)
+    _capi.check(L.convnn_b200_outproj_mlp(ov.data_ptr(), ld_o, w_o.data_ptr(), xv.data_ptr(), ldx, float(eps),
                                           w1_folded.data_ptr(), w1_extra.data_ptr(), w2c.data_ptr(), _capi.ptr(b2),
                                           out.data_ptr(), D, M, D, DM, _capi.ptr(mom), _stream(x)))
     return out, mom

@@ -96,6 +96,9 @@ class TransformerEncoder(nn.Module):
         # of roundings)
         self.fold_layernorm = True
         self.fuse_mlp = True          # with the fold: norm2 + mlp + skip connection as one kernel where it is built
+        # ... and the attention layer's W_o + skip connection in front of it (one head).  Built and parity-green,
+        # but not faster inside the model (1.70 ms against 1.675 ms per cfg-2 batch on the same GPU): off by default.
+        self.fuse_out_proj = False
         self._fc1_folded = _PackedParams()
 
     def forward(self, x):
@@ -125,6 +128,14 @@ class TransformerEncoder(nn.Module):
         if self.folds_norm1(x):
             if moments is None:
                 moments = ops.row_moments(x)
+            if (fold_mlp and self.fuse_mlp and self.fuse_out_proj and self.attention.num_heads == 1 and
+                    ops.prenorm_mlp_supported(fc1.in_features, fc1.out_features, 1)):
+                # attention up to the gather / conv, then ONE kernel for W_o + skip + norm2 + mlp + skip
+                o, _ = self.attention.forward_prenorm(x, moments, n1, skip_out_proj=True)
+                wf, wx = self._fc1_folded.get((fc1.weight, fc1.bias, n2.weight, n2.bias), x.dtype, x.device,
+                                              lambda: ops.fold_layernorm(fc1.weight, fc1.bias, n2.weight, n2.bias))
+                return ops.outproj_mlp(o, self.attention.packed_w_o, x, n2.eps, wf, wx, fc2.weight, fc2.bias,
+                                       want_moments=want_moments)
             x, m1 = self.attention.forward_prenorm(x, moments, n1, residual=x, want_moments=fold_mlp)
         else:
             xn = ops.layernorm(x, n1.weight, n1.bias, n1.eps)

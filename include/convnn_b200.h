@@ -274,7 +274,9 @@ int convnn_b200_linear_moments(const void* a, int64_t lda, const void* w, const 
                                float* moments_out, void* stream);
 /* convnn_b200_forward on rows x that have NOT been normalised yet (norm1 folded into the K/V/Q
  * projection; sampling 'all' only), optionally emitting the moments of residual + layer(x) for the
- * next folded GEMM (moments_out may be NULL; it needs residual != NULL). */
+ * next folded GEMM (moments_out may be NULL; it needs residual != NULL).  With w_o == NULL
+ * (num_heads = 1 only) the call stops before the output projection and writes the layer's
+ * head-merged pre-projection rows (B, T, D) contiguously to `out`, for convnn_b200_outproj_mlp. */
 int convnn_b200_prenorm_forward(const convnn_desc* d, const void* x, int64_t ldx, const float* moments,
                                 int32_t planes, float eps, const void* w_qkv_folded, const void* w_qkv_extra,
                                 const void* w_conv, const void* w_pw, const void* w_o, const void* residual,
@@ -293,6 +295,17 @@ int convnn_b200_prenorm_forward(const convnn_desc* d, const void* x, int64_t ldx
 int convnn_b200_prenorm_mlp_supported(int32_t D, int32_t DM, int32_t planes);
 int convnn_b200_prenorm_mlp_moment_planes(void);
 int convnn_b200_prenorm_mlp(const void* x, int64_t ldx, const float* moments, int32_t planes, float eps,
+                            const void* w1_folded, const void* w1_extra, const void* w2, const void* b2, void* out,
+                            int64_t ldo, int64_t M, int32_t D, int32_t DM, float* moments_out, void* stream);
+
+/* The output projection of the attention layer, its skip connection and the whole MLP block in one
+ * kernel (layers.py:320 with vit.py:264, then vit.py:267-269):
+ *     x1 = x + o w_o^T,     out = x1 + (GELU(LayerNorm(x1) w1^T + b1) w2^T + b2)
+ * o (M, D) is the head-merged output of convnn_b200_gather_conv (num_heads = 1: the per-head layout IS
+ * (M, D)), w_o (D, D) bias-free, x (M, D) the rows that entered the attention layer.  The moments
+ * of x1 are computed inside.  Shapes as convnn_b200_prenorm_mlp (ask
+ * convnn_b200_prenorm_mlp_supported(D, DM, 1)); moments_out as there.  out may alias neither o nor x. */
+int convnn_b200_outproj_mlp(const void* o, int64_t ld_o, const void* w_o, const void* x, int64_t ldx, float eps,
                             const void* w1_folded, const void* w1_extra, const void* w2, const void* b2, void* out,
                             int64_t ldo, int64_t M, int32_t D, int32_t DM, float* moments_out, void* stream);
 

@@ -220,3 +220,64 @@ def test_prenorm_mlp_takes_moments_in_several_planes_and_refuses_other_shapes():
         ops.prenorm_mlp(rnd(64, 768, seed=47), ops.row_moments(rnd(64, 768, seed=47)), 1e-5,
                         torch.zeros(3072, 768, dtype=BF, device=DEV), torch.zeros(3072, 16, dtype=BF, device=DEV),
                         torch.zeros(768, 3072, dtype=BF, device=DEV), None)
+
+
+@pytest.mark.parametrize("M,D,DM,shift", [(777, 192, 768, 0.0), (1, 192, 768, 0.0), (50432, 192, 768, 1.0),
+                                          (1000, 128, 512, 0.0), (1000, 64, 256, -0.5), (600, 192, 256, 0.0)])
+def test_outproj_mlp_against_float64_and_the_separate_kernels(M, D, DM, shift):
+    """W_o + skip + norm2 + mlp + skip in one kernel: x1 = x + o W_o^T is formed inside (and its moments with
+    it); the result agrees with float64 arithmetic from the rounded x1 as well as linear(+skip) followed by
+    the one-kernel MLP does, and the emitted moments are those of the stored rows."""
+    x, o = rnd(M, D, seed=51, shift=shift), rnd(M, D, seed=52)
+    wo = rnd(D, D, seed=53, scale=D ** -0.5)
+    gamma, beta = rnd(D, seed=54, scale=0.2, shift=1.0), rnd(D, seed=55, scale=0.2)
+    w1, b1 = rnd(DM, D, seed=56, scale=D ** -0.5), rnd(DM, seed=57, scale=0.3)
+    w2, b2 = rnd(D, DM, seed=58, scale=DM ** -0.5), rnd(D, seed=59, scale=0.3)
+    wf, wx = ops.fold_layernorm(w1, b1, gamma, beta)
+    got, mo = ops.outproj_mlp(o, wo, x, 1e-5, wf, wx, w2, b2, want_moments=True)
+    again, _ = ops.outproj_mlp(o, wo, x, 1e-5, wf, wx, w2, b2)
+    torch.cuda.synchronize()
+    assert _capi.device_status() == 0
+    assert torch.equal(got, again)
+    x1 = ops.linear(o, wo, None, residual=x)
+    sep, _ = ops.prenorm_mlp(x1, ops.row_moments(x1), 1e-5, wf, wx, w2, b2)
+    want = mlp_f64(x1, gamma, beta, w1, b1, w2, b2, 1e-5)
+    scale = want.abs().max().item()
+    err = (got.double() - want).abs().max().item() / scale
+    err_sep = (sep.double() - want).abs().max().item() / scale
+    print(f"max err / scale: one kernel {err:.2e}, output projection + MLP kernel {err_sep:.2e}")
+    assert err < 2e-2 and err < 1.5 * err_sep + 1e-3
+    gd = got.double()
+    tot = mo.double()[:, :M].sum(0)
+    assert torch.allclose(tot[:, 0], gd.sum(1), rtol=1e-5, atol=1e-3)
+    assert torch.allclose(tot[:, 1], (gd * gd).sum(1), rtol=1e-5, atol=1e-3)
+
+
+def test_vit_with_the_output_projection_inside_the_mlp_kernel():
+    """`fuse_out_proj` (off by default): same model, W_o + skip handled by the MLP kernel; logits agree with the
+    default path and one more launch per block disappears."""
+    from oracle.vit_oracle import ViTConfig, make_images, make_vit_weights
+    from oracle.convnn_oracle import bf16_round
+    cfg = ViTConfig(layer="ConvNNAttention", d_hidden=192, d_mlp=768, num_heads=1, num_layers=3,
+                    magnitude_type="cosine", convolution_type="depthwise")
+    sd = {k: bf16_round(v) for k, v in make_vit_weights(cfg, seed=7).items()}
+    args = convnn_b200.make_args(**{f: getattr(cfg, f) for f in cfg.__dataclass_fields__}, device=DEV)
+    model = convnn_b200.ViT(args).eval()
+    model.load_state_dict(sd, strict=True)
+    model = model.to(DEV, BF)
+    img = bf16_round(make_images(3, cfg, seed=8)).to(DEV, BF)
+    lib = _capi.lib()
+    with torch.no_grad():
+        model(img)
+        n0 = lib.convnn_b200_launch_count()
+        base = model(img).float()
+        n1 = lib.convnn_b200_launch_count()
+        for blk in model.transformer_encoder:
+            blk.fuse_out_proj = True
+        fused = model(img).float()
+        n2 = lib.convnn_b200_launch_count()
+    assert _capi.device_status() == 0
+    assert (n1 - n0) - (n2 - n1) == cfg.num_layers
+    err = rel_err(fused, base)
+    print(f"logits, W_o inside the MLP kernel against the default path: rel err {err:.3e}")
+    assert err < 0.05
