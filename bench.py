@@ -585,7 +585,7 @@ def other_configs(dev, min_ms=400.0):
 # ncu captures summarised under profiles/ (outputs that are still in L2 when the kernel ends are
 # not in these figures, which is why they sit below the algorithmic bytes).
 NCU_TRAFFIC_BYTES = {"qkv_proj": 19.69e6 + 10.28e6, "sim_topk": 39.2e6 + 0.009e6, "gather_conv": 23.04e6,
-                     "out_proj": 19.5e6}
+                     "out_proj": 19.5e6, "mlp_block": 20.47e6}
 
 
 def algorithmic_work(B, T, S, D, H, K, DM=0, elt=2):
