@@ -114,7 +114,11 @@ sim_topk_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     const uint32_t st0 = smem_u32(stages);
 
     if (warp == 0) {
-        if (lane == 0) {
+        // One thread can start a TMA operation only every ~0.3 us whatever its size, while operations started
+        // by different lanes overlap: the three boxes of a stage (two key tiles, one query tile) are issued by
+        // lanes 0, 1 and 2 with one instruction of the warp (a unit of the ViT shape has 36 of them).
+        if (lane < 3) {
+            const uint32_t m3 = 0x7u;
             uint32_t s = 0, ph = 0;                  // ring slot and phase, advanced incrementally
             bool ok = true;
             for (int unit = blockIdx.x; unit < p.n_units && ok; unit += gridDim.x) {
@@ -126,12 +130,15 @@ sim_topk_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
                 for (int ct = 0; ct < p.n_col_tiles && ok; ++ct) {
                     const int col0 = ct * p.BN;
                     for (int kc = 0; kc < p.KC; ++kc) {
-                        if (!mbar_wait_a(empty0 + 8 * s, ph ^ 1u, abort_flag)) { fail(abort_flag, 1); ok = false; break; }
+                        ok = mbar_wait_a(empty0 + 8 * s, ph ^ 1u, abort_flag);
+                        ok = __all_sync(m3, ok);
+                        if (!ok) { if (lane == 0) fail(abort_flag, 1); break; }
                         const uint32_t st = st0 + s * stage_bytes, fb = full0 + 8 * s;
-                        mbar_expect_tx_a(fb, tx);
-                        tma_load_4d_a(st, &tmK, fb, kc * p.KCH, h, row0, b);
-                        if (has1) tma_load_4d_a(st + a_bytes, &tmK, fb, kc * p.KCH, h, row0 + BM, b);
-                        tma_load_4d_a(st + 2 * a_bytes, &tmQ, fb, kc * p.KCH, h, col0, b);
+                        if (lane == 0) mbar_expect_tx_a(fb, tx);
+                        __syncwarp(m3);
+                        if (lane == 0) tma_load_4d_a(st, &tmK, fb, kc * p.KCH, h, row0, b);
+                        else if (lane == 1) { if (has1) tma_load_4d_a(st + a_bytes, &tmK, fb, kc * p.KCH, h, row0 + BM, b); }
+                        else tma_load_4d_a(st + 2 * a_bytes, &tmQ, fb, kc * p.KCH, h, col0, b);
                         if (++s == STAGES) { s = 0; ph ^= 1u; }
                     }
                 }
