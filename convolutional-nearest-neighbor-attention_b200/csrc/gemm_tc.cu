@@ -493,6 +493,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 optr[g] = cbase + (long long)grow * p.ldc + pc0 + (lane & 3) * 8;
                 rptr[g] = RES ? p.residual + (long long)grow * p.ldr + n0 + (lane & 3) * 8 : nullptr;
             }
+            if (RES && t + 2 * step < last && (lane & 3) == 0) {
+                // the skip connection's rows of this warp's NEXT tile: brought into L2 now, so that the loads in
+                // that tile's chunk loop (issued only a chunk ahead of their use) do not wait on DRAM
+                int mt2, nt2;
+                tile_mn(t + 2 * step, mt2, nt2);
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    const int grow2 = mt2 * TM + (int)rank * BM + lq * 32 + g * 8 + (lane >> 2);
+                    if (grow2 < p.M)
+                        for (int c = c_begin; c < c_end && nt2 * p.BN + c < p.N; c += 32)
+                            asm volatile("prefetch.global.L2 [%0];" ::"l"(p.residual + (long long)grow2 * p.ldr + nt2 * p.BN + c));
+                }
+            }
             // statistic bookkeeping without divisions in the chunk loop
             int head = 0, head_left = 0;
             long long stat_base = 0;
