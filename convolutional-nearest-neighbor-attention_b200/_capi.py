@@ -81,6 +81,8 @@ SIGNATURES = {
                                                c_void, c_void, c_i64, c_i64, c_i32, c_i32, c_void, c_void]),
     "convnn_b200_outproj_mlp": (ctypes.c_int, [c_void, c_i64, c_void, c_void, c_i64, ctypes.c_float, c_void, c_void, c_void,
                                                c_void, c_void, c_i64, c_i64, c_i32, c_i32, c_void, c_void]),
+    "convnn_b200_embed_tokens_moments": (ctypes.c_int, [ctypes.c_int, c_void, c_void, c_void, ctypes.c_float, c_void, c_void,
+                                                        c_void, c_i32, c_i32, c_i32, c_void, c_void]),
     "convnn_b200_attention_workspace_bytes": (c_size, [ctypes.c_int, c_i32, c_i32, c_i32]),
     "convnn_b200_softmax_attention": (ctypes.c_int, [ctypes.c_int, c_void, c_i64, c_void, c_void, c_void, c_i64, c_i32,
                                                      c_i32, c_i32, c_i32, c_void, c_size, c_void]),

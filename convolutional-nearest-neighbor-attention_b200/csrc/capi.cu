@@ -395,20 +395,28 @@ int convnn_b200_layernorm(int dtype, const void* x, int64_t ldx, const void* gam
     int rc = check_device();
     if (rc) return rc;
     if (rows == 0) return CONVNN_OK;
-    return launch_layernorm(dtype, x, ldx, gamma, beta, eps, y, ldy, rows, D, nullptr, nullptr, 0, 0,
+    return launch_layernorm(dtype, x, ldx, gamma, beta, eps, y, ldy, rows, D, nullptr, nullptr, 0, 0, nullptr,
+                            static_cast<cudaStream_t>(stream));
+}
+
+int convnn_b200_embed_tokens_moments(int dtype, const void* proj, const void* gamma, const void* beta, float eps,
+                                     const void* cls, const void* pe, void* out, int32_t B, int32_t Np, int32_t D,
+                                     float* moments_out, void* stream) {
+    if (dtype != CONVNN_F32 && dtype != CONVNN_BF16) return set_error(CONVNN_E_INVALID, "unknown dtype %d", dtype);
+    REQUIRE_PTR(proj); REQUIRE_PTR(gamma); REQUIRE_PTR(beta); REQUIRE_PTR(cls); REQUIRE_PTR(pe); REQUIRE_PTR(out);
+    if (B < 1 || Np < 1 || D < 1) return set_error(CONVNN_E_INVALID, "embed_tokens: bad shape");
+    if (moments_out && (reinterpret_cast<uintptr_t>(moments_out) & 7u))
+        return set_error(CONVNN_E_ALIGN, "embed_tokens: moments_out must be 8-byte aligned");
+    int rc = check_device();
+    if (rc) return rc;
+    return launch_layernorm(dtype, proj, D, gamma, beta, eps, out, D, (long long)B * Np, D, pe, cls, Np, B, moments_out,
                             static_cast<cudaStream_t>(stream));
 }
 
 int convnn_b200_embed_tokens(int dtype, const void* proj, const void* gamma, const void* beta, float eps,
                              const void* cls, const void* pe, void* out, int32_t B, int32_t Np, int32_t D,
                              void* stream) {
-    if (dtype != CONVNN_F32 && dtype != CONVNN_BF16) return set_error(CONVNN_E_INVALID, "unknown dtype %d", dtype);
-    REQUIRE_PTR(proj); REQUIRE_PTR(gamma); REQUIRE_PTR(beta); REQUIRE_PTR(cls); REQUIRE_PTR(pe); REQUIRE_PTR(out);
-    if (B < 1 || Np < 1 || D < 1) return set_error(CONVNN_E_INVALID, "embed_tokens: bad shape");
-    int rc = check_device();
-    if (rc) return rc;
-    return launch_layernorm(dtype, proj, D, gamma, beta, eps, out, D, (long long)B * Np, D, pe, cls, Np, B,
-                            static_cast<cudaStream_t>(stream));
+    return convnn_b200_embed_tokens_moments(dtype, proj, gamma, beta, eps, cls, pe, out, B, Np, D, nullptr, stream);
 }
 
 int convnn_b200_patchify(int dtype, const void* img, void* out, int32_t B, int32_t C, int32_t Hh, int32_t Ww,

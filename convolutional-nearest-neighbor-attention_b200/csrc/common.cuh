@@ -133,7 +133,7 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
                    long long ldc, const GemmTcOpts& o, cudaStream_t st);
 int launch_layernorm(int dtype, const void* x, long long ldx, const void* gamma, const void* beta, float eps, void* y,
                      long long ldy, long long rows, int D, const void* pe, const void* cls, int Np,
-                     long long cls_rows, cudaStream_t st);
+                     long long cls_rows, float* moments, cudaStream_t st);
 // The encoder's MLP block (norm2 folded, GELU, both Linear layers, skip connection) as one kernel.
 bool mlp_tc_supported(int D, int DM, int planes);
 int mlp_tc_moment_planes();

@@ -41,7 +41,9 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const T* __restrict__ x,
                                                         const T* __restrict__ gamma, const T* __restrict__ beta,
                                                         float eps, T* __restrict__ y, long long ldy, long long rows,
                                                         int D, const T* __restrict__ pe, const T* __restrict__ cls,
-                                                        int Np, long long cls_rows) {
+                                                        int Np, long long cls_rows, float2* __restrict__ moments) {
+    // moments (or nullptr): (sum, sum of squares) of every STORED output row, indexed by output row: what the
+    // pre-norm fold of the first GEMM behind the embedding needs
     constexpr int V = Vec16<T>::N;
     const int lane = threadIdx.x & 31;
     const long long wpb = blockDim.x >> 5;
@@ -50,24 +52,44 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const T* __restrict__ x,
         if (r >= rows) {                       // class-token row of image b: cls + pe[0]
             const long long b = r - rows;
             T* out = y + b * (Np + 1) * ldy;
+            float m1 = 0.f, m2 = 0.f;
             for (int i = lane; i < nvec; i += 32) {
                 float c[V], p0[V];
                 load_vec<T>(cls + i * V, c);
                 load_vec<T>(pe + i * V, p0);
 #pragma unroll
-                for (int j = 0; j < V; ++j) c[j] += p0[j];
+                for (int j = 0; j < V; ++j) {
+                    c[j] += p0[j];
+                    const float rv = to_f32<T>(from_f32<T>(c[j]));
+                    m1 += rv;
+                    m2 = fmaf(rv, rv, m2);
+                }
                 store_vec<T>(out + i * V, c);
+            }
+            if (moments) {
+                m1 = warp_sum(m1);
+                m2 = warp_sum(m2);
+                if (lane == 0) moments[b * (Np + 1)] = make_float2(m1, m2);
             }
             continue;
         }
         const T* in = x + r * ldx;
+        long long orow = r;
+        const T* perow = nullptr;
+        if (pe) {
+            const long long b = r / Np, n = r - b * Np;
+            orow = b * (Np + 1) + 1 + n;
+            perow = pe + (1 + n) * (long long)D;
+        }
         float v[NV][V];
+        uint4 pv_raw[NV];                       // the positional row, fetched with the input row
         float s = 0.f;
 #pragma unroll
         for (int k = 0; k < NV; ++k) {
             const int i = lane + 32 * k;
             if (i < nvec) {
                 load_vec<T>(in + i * V, v[k]);
+                if (perow) pv_raw[k] = *reinterpret_cast<const uint4*>(perow + i * V);
 #pragma unroll
                 for (int j = 0; j < V; ++j) s += v[k][j];
             }
@@ -86,14 +108,8 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const T* __restrict__ x,
             }
         }
         const float rstd = rsqrtf(warp_sum(q) / (float)D + eps);
-        long long orow = r;
-        const T* perow = nullptr;
-        if (pe) {
-            const long long b = r / Np, n = r - b * Np;
-            orow = b * (Np + 1) + 1 + n;
-            perow = pe + (1 + n) * (long long)D;
-        }
         T* out = y + orow * ldy;
+        float m1 = 0.f, m2 = 0.f;
 #pragma unroll
         for (int k = 0; k < NV; ++k) {
             const int i = lane + 32 * k;
@@ -104,13 +120,25 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const T* __restrict__ x,
 #pragma unroll
                 for (int j = 0; j < V; ++j) o[j] = (v[k][j] - mean) * rstd * g[j] + bt[j];
                 if (perow) {
-                    float pv[V];
-                    load_vec<T>(perow + i * V, pv);
+                    const T* pv = reinterpret_cast<const T*>(&pv_raw[k]);
 #pragma unroll
-                    for (int j = 0; j < V; ++j) o[j] = to_f32<T>(from_f32<T>(o[j])) + pv[j];
+                    for (int j = 0; j < V; ++j) o[j] = to_f32<T>(from_f32<T>(o[j])) + to_f32<T>(pv[j]);
+                }
+                if (moments) {
+#pragma unroll
+                    for (int j = 0; j < V; ++j) {
+                        const float rv = to_f32<T>(from_f32<T>(o[j]));
+                        m1 += rv;
+                        m2 = fmaf(rv, rv, m2);
+                    }
                 }
                 store_vec<T>(out + i * V, o);
             }
+        }
+        if (moments) {
+            m1 = warp_sum(m1);
+            m2 = warp_sum(m2);
+            if (lane == 0) moments[orow] = make_float2(m1, m2);
         }
     }
 }
@@ -194,67 +222,103 @@ __global__ void __launch_bounds__(256, MINB) layernorm_bf16_row256_kernel(
 // turns Conv2d(kernel = stride = P) into a GEMM with the (D, C*P*P) weight view.  VT is an
 // unsigned integer type carrying VE = sizeof(VT) / sizeof(T) contiguous elements of a patch row.
 template <typename T, typename VT>
-__global__ void patchify_kernel(const T* __restrict__ img, T* __restrict__ out, int B, int C, int Hh, int Ww, int P,
-                                long long total_vec) {
+__global__ void __launch_bounds__(256) patchify_kernel(const T* __restrict__ img, T* __restrict__ out, int C, int Hh,
+                                                       int Ww, int P) {
+    // One CTA per (image, row of patches): C * P image rows of Ww elements, read in image order
+    // (whole rows, coalesced) and stored as the P-element runs of the patches' rows.  The index
+    // arithmetic is 32-bit inside the strip; four vectors per thread are in flight.
     constexpr int V = sizeof(VT) / sizeof(T);
-    const int vec_per_prow = P / V;                  // vectors per patch row
-    const int Wp = Ww / P, Hp = Hh / P;
-    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total_vec;
-         e += (long long)gridDim.x * blockDim.x) {
-        long long t = e;
-        const int jv = (int)(t % vec_per_prow); t /= vec_per_prow;
-        const int i = (int)(t % P); t /= P;
-        const int c = (int)(t % C); t /= C;
-        const int px = (int)(t % Wp); t /= Wp;
-        const int py = (int)(t % Hp); t /= Hp;
-        const long long b = t;
-        const T* src = img + (((b * C + c) * Hh + (py * P + i)) * (long long)Ww + px * P + jv * V);
-        T* dst = out + ((b * Hp + py) * Wp + px) * (long long)(C * P * P) + (c * P + i) * P + jv * V;
-        *reinterpret_cast<VT*>(dst) = *reinterpret_cast<const VT*>(src);
+    constexpr int U = 4;
+    const int Hp = Hh / P, Wp = Ww / P;
+    const int b = blockIdx.x / Hp, py = blockIdx.x - b * Hp;
+    const int vrow = Ww / V, vpp = P / V;            // vectors per image row / per patch row
+    const int n = C * P * vrow;
+    const long long cpp = (long long)C * P * P;
+    const T* src0 = img + ((long long)b * C * Hh + (long long)py * P) * Ww;
+    T* dst0 = out + (long long)blockIdx.x * Wp * cpp;
+    for (int e0 = threadIdx.x; e0 < n; e0 += 256 * U) {
+        VT v[U];
+        int r[U], xv[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int e = e0 + u * 256;
+            if (e < n) {
+                r[u] = e / vrow;                     // c * P + i
+                xv[u] = e - r[u] * vrow;
+                const int c = r[u] / P, i = r[u] - c * P;
+                v[u] = *reinterpret_cast<const VT*>(src0 + ((long long)c * Hh + i) * Ww + xv[u] * V);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (e0 + u * 256 < n) {
+                const int px = xv[u] / vpp, jv = xv[u] - px * vpp;
+                *reinterpret_cast<VT*>(dst0 + px * cpp + r[u] * P + jv * V) = v[u];
+            }
+        }
     }
 }
 
 // The same unfold for images that are still 8-bit (what an image decoder hands over): the
 // loader's ToTensor + Normalize, out = (img / 255 - mean[c]) * inv_std[c], happens on the way.
-// VEC pixels of one patch row per thread (8: one 8-byte load, 16 / 32 bytes stored).
+// VEC pixels of one patch row per vector (8: one 8-byte load, 16 / 32 bytes stored).
 template <typename T, int VEC>
-__global__ void patchify_u8_kernel(const uint8_t* __restrict__ img, const float* __restrict__ mean,
-                                   const float* __restrict__ inv_std, T* __restrict__ out, int B, int C, int Hh, int Ww,
-                                   int P, long long total_vec) {
+__global__ void __launch_bounds__(256) patchify_u8_kernel(const uint8_t* __restrict__ img, const float* __restrict__ mean,
+                                                          const float* __restrict__ inv_std, T* __restrict__ out, int C,
+                                                          int Hh, int Ww, int P) {
+    constexpr int U = VEC == 8 ? 4 : 8;
     const int Hp = Hh / P, Wp = Ww / P;
-    const int vec_per_prow = P / VEC;
-    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total_vec;
-         e += (long long)gridDim.x * blockDim.x) {
-        long long t = e;
-        const int jv = (int)(t % vec_per_prow); t /= vec_per_prow;
-        const int i = (int)(t % P); t /= P;
-        const int c = (int)(t % C); t /= C;
-        const int px = (int)(t % Wp); t /= Wp;
-        const int py = (int)(t % Hp); t /= Hp;
-        const long long b = t;
-        const uint8_t* src = img + (((b * C + c) * Hh + (py * P + i)) * (long long)Ww + px * P + jv * VEC);
-        T* dst = out + ((b * Hp + py) * Wp + px) * (long long)(C * P * P) + (c * P + i) * P + jv * VEC;
-        const float m = mean[c], is = inv_std[c];
-        uint8_t raw[VEC];
-        if (VEC == 8) *reinterpret_cast<uint2*>(raw) = *reinterpret_cast<const uint2*>(src);
-        else raw[0] = src[0];
+    const int b = blockIdx.x / Hp, py = blockIdx.x - b * Hp;
+    const int vrow = Ww / VEC, vpp = P / VEC;
+    const int n = C * P * vrow;
+    const long long cpp = (long long)C * P * P;
+    const uint8_t* src0 = img + ((long long)b * C * Hh + (long long)py * P) * Ww;
+    T* dst0 = out + (long long)blockIdx.x * Wp * cpp;
+    for (int e0 = threadIdx.x; e0 < n; e0 += 256 * U) {
+        uint8_t raw[U][VEC];
+        int r[U], xv[U];
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) dst[k] = from_f32<T>(((float)raw[k] * (1.0f / 255.0f) - m) * is);
+        for (int u = 0; u < U; ++u) {
+            const int e = e0 + u * 256;
+            if (e < n) {
+                r[u] = e / vrow;
+                xv[u] = e - r[u] * vrow;
+                const int c = r[u] / P, i = r[u] - c * P;
+                const uint8_t* src = src0 + ((long long)c * Hh + i) * Ww + xv[u] * VEC;
+                if (VEC == 8) *reinterpret_cast<uint2*>(raw[u]) = *reinterpret_cast<const uint2*>(src);
+                else raw[u][0] = src[0];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (e0 + u * 256 < n) {
+                const int c = r[u] / P;
+                const float m = mean[c], is = inv_std[c];
+                const int px = xv[u] / vpp, jv = xv[u] - px * vpp;
+                T* dst = dst0 + px * cpp + r[u] * P + jv * VEC;
+                float f[VEC];
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) f[k] = ((float)raw[u][k] * (1.0f / 255.0f) - m) * is;
+                if (VEC == 8) {
+                    store_vec<T>(dst, f);
+                    if (Vec16<T>::N == 4) store_vec<T>(dst + 4, f + 4);
+                } else {
+                    dst[0] = from_f32<T>(f[0]);
+                }
+            }
+        }
     }
 }
 
 template <typename T, typename VT>
 void patchify_launch(const void* img, void* out, int B, int C, int Hh, int Ww, int P, cudaStream_t st) {
-    const long long total = (long long)B * C * Hh * Ww / (long long)(sizeof(VT) / sizeof(T));
-    int blocks = (int)((total + 255) / 256);
-    if (blocks > 148 * 32) blocks = 148 * 32;
-    patchify_kernel<T, VT><<<blocks, 256, 0, st>>>(static_cast<const T*>(img), static_cast<T*>(out), B, C, Hh, Ww, P,
-                                                   total);
+    patchify_kernel<T, VT><<<B * (Hh / P), 256, 0, st>>>(static_cast<const T*>(img), static_cast<T*>(out), C, Hh, Ww, P);
 }
 
 template <typename T>
 int ln_dispatch(const void* x, long long ldx, const void* gamma, const void* beta, float eps, void* y, long long ldy,
-                long long rows, int D, const void* pe, const void* cls, int Np, long long cls_rows, cudaStream_t st) {
+                long long rows, int D, const void* pe, const void* cls, int Np, long long cls_rows, float* moments,
+                cudaStream_t st) {
     constexpr int V = Vec16<T>::N;
     const int nvec = D / V;
     const int nv = (nvec + 31) / 32;
@@ -265,7 +329,7 @@ int ln_dispatch(const void* x, long long ldx, const void* gamma, const void* bet
 #define CONVNN_LN(NVV)                                                                                          \
     layernorm_kernel<T, NVV><<<blocks, 256, 0, st>>>(static_cast<const T*>(x), ldx, static_cast<const T*>(gamma), \
         static_cast<const T*>(beta), eps, static_cast<T*>(y), ldy, rows, D, static_cast<const T*>(pe),          \
-        static_cast<const T*>(cls), Np, cls_rows)
+        static_cast<const T*>(cls), Np, cls_rows, reinterpret_cast<float2*>(moments))
     if (nv <= 1) CONVNN_LN(1);
     else if (nv <= 2) CONVNN_LN(2);
     else if (nv <= 4) CONVNN_LN(4);
@@ -280,12 +344,12 @@ int ln_dispatch(const void* x, long long ldx, const void* gamma, const void* bet
 
 int launch_layernorm(int dtype, const void* x, long long ldx, const void* gamma, const void* beta, float eps, void* y,
                      long long ldy, long long rows, int D, const void* pe, const void* cls, int Np,
-                     long long cls_rows, cudaStream_t st) {
+                     long long cls_rows, float* moments, cudaStream_t st) {
     const int V = dtype == CONVNN_F32 ? 4 : 8;
     if (D % V != 0 || ldx % V != 0 || ldy % V != 0 || !aligned16(x) || !aligned16(y) || !aligned16(gamma) ||
         !aligned16(beta) || (pe && (!aligned16(pe) || !aligned16(cls))))
         return set_error(CONVNN_E_ALIGN, "layernorm: D, strides and pointers must be multiples of 16 bytes");
-    if (dtype == CONVNN_BF16 && !pe && D <= 256) {
+    if (dtype == CONVNN_BF16 && !pe && !moments && D <= 256) {
         // Two 8-warp CTAs per SM (the kernel keeps 121 registers: four rows in flight and four
         // requested per warp), measured 9.6 us at 50 k rows of 192 channels against 11.0 us with
         // one row per step and four CTAs per SM; register-capped variants that spill are twice as slow.
@@ -300,8 +364,8 @@ int launch_layernorm(int dtype, const void* x, long long ldx, const void* gamma,
         return CONVNN_OK;
     }
     if (dtype == CONVNN_F32)
-        return ln_dispatch<float>(x, ldx, gamma, beta, eps, y, ldy, rows, D, pe, cls, Np, cls_rows, st);
-    return ln_dispatch<__nv_bfloat16>(x, ldx, gamma, beta, eps, y, ldy, rows, D, pe, cls, Np, cls_rows, st);
+        return ln_dispatch<float>(x, ldx, gamma, beta, eps, y, ldy, rows, D, pe, cls, Np, cls_rows, moments, st);
+    return ln_dispatch<__nv_bfloat16>(x, ldx, gamma, beta, eps, y, ldy, rows, D, pe, cls, Np, cls_rows, moments, st);
 }
 
 namespace {
@@ -388,10 +452,7 @@ int launch_patchify_u8(int dtype, const uint8_t* img, const float* mean, const f
                        int Hh, int Ww, int P, cudaStream_t st) {
     if (Hh % P != 0 || Ww % P != 0) return set_error(CONVNN_E_INVALID, "patchify: image not divisible into patches");
     const bool v8 = P % 8 == 0 && Ww % 8 == 0 && (reinterpret_cast<uintptr_t>(img) & 7u) == 0 && aligned16(out);
-    const long long total = (long long)B * C * Hh * Ww / (v8 ? 8 : 1);
-    int blocks = (int)((total + 255) / 256);
-    if (blocks > 148 * 32) blocks = 148 * 32;
-#define CONVNN_PU8(T, V) patchify_u8_kernel<T, V><<<blocks, 256, 0, st>>>(img, mean, inv_std, static_cast<T*>(out), B, C, Hh, Ww, P, total)
+#define CONVNN_PU8(T, V) patchify_u8_kernel<T, V><<<B * (Hh / P), 256, 0, st>>>(img, mean, inv_std, static_cast<T*>(out), C, Hh, Ww, P)
     if (dtype == CONVNN_F32) { if (v8) CONVNN_PU8(float, 8); else CONVNN_PU8(float, 1); }
     else { if (v8) CONVNN_PU8(__nv_bfloat16, 8); else CONVNN_PU8(__nv_bfloat16, 1); }
 #undef CONVNN_PU8

@@ -149,8 +149,12 @@ class MultiHeadConvNNAttention(nn.Module):
     def prenorm_supported(self, x) -> bool:
         """Whether ``forward_prenorm`` takes this input (bfloat16, sampling 'all', a K/V/Q weight tile
         that stays resident in shared memory); otherwise the caller normalises and calls ``forward``."""
-        return (x.is_cuda and x.dtype == torch.bfloat16 and self.stage_timer is None and
-                ops.prenorm_forward_supported(self._spec(), x.shape[0], x.shape[1], x.dtype))
+        return x.is_cuda and self.prenorm_supported_shape(x.shape[0], x.shape[1], x.dtype)
+
+    def prenorm_supported_shape(self, B: int, T: int, dtype) -> bool:
+        """``prenorm_supported`` for a CUDA input (B, T, d_hidden) of ``dtype`` that does not exist yet."""
+        return (dtype == torch.bfloat16 and self.stage_timer is None and
+                ops.prenorm_forward_supported(self._spec(), B, T, dtype))
 
     def forward_prenorm(self, x, moments, norm: nn.LayerNorm, residual: Optional[torch.Tensor] = None,
                         want_moments: bool = False, skip_out_proj: bool = False):

@@ -467,11 +467,14 @@ def linear(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
 
 def patch_embed(images: torch.Tensor, conv_weight: torch.Tensor, conv_bias: torch.Tensor, norm_weight, norm_bias,
                 cls: torch.Tensor, pe: torch.Tensor, patch: int, eps: float = 1e-5,
-                pixel_mean: Optional[torch.Tensor] = None, pixel_inv_std: Optional[torch.Tensor] = None) -> torch.Tensor:
+                pixel_mean: Optional[torch.Tensor] = None, pixel_inv_std: Optional[torch.Tensor] = None,
+                want_moments: bool = False):
     """PatchEmbedding + PositionalEncoding (reference vit.py:104-109, 126-135): unfold, GEMM
     with the (D, C*P*P) weight view, LayerNorm, class token and positional table -> (B, T, D).
     uint8 images are normalised on the way ((img / 255 - pixel_mean[c]) * pixel_inv_std[c], the
-    loader's ToTensor + Normalize, reference dataset.py:22-23) and computed in the weights' dtype."""
+    loader's ToTensor + Normalize, reference dataset.py:22-23) and computed in the weights' dtype.
+    want_moments: also return the (1, moment_stride(B*T), 2) float32 row moments of the result (what
+    row_moments would compute from it), written by the same kernel."""
     _require_cuda(images, conv_weight)
     L = _capi.lib()
     B, C, Hh, Ww = images.shape
@@ -491,7 +494,12 @@ def patch_embed(images: torch.Tensor, conv_weight: torch.Tensor, conv_bias: torc
     proj = linear(cols, conv_weight.reshape(D, -1), conv_bias)
     out = torch.empty(B, Np + 1, D, dtype=act, device=images.device)
     pe2 = pe.reshape(-1, D)[: Np + 1].contiguous()
-    _capi.check(L.convnn_b200_embed_tokens(dt, proj.data_ptr(), norm_weight.data_ptr(), norm_bias.data_ptr(), float(eps),
-                                           cls.reshape(-1).contiguous().data_ptr(), pe2.data_ptr(), out.data_ptr(),
-                                           B, Np, D, _stream(images)))
-    return out
+    moments = None
+    if want_moments:
+        moments = torch.empty(1, L.convnn_b200_moment_stride(B * (Np + 1)), 2, dtype=torch.float32,
+                              device=images.device)
+    _capi.check(L.convnn_b200_embed_tokens_moments(dt, proj.data_ptr(), norm_weight.data_ptr(), norm_bias.data_ptr(),
+                                                   float(eps), cls.reshape(-1).contiguous().data_ptr(), pe2.data_ptr(),
+                                                   out.data_ptr(), B, Np, D,
+                                                   moments.data_ptr() if want_moments else None, _stream(images)))
+    return (out, moments) if want_moments else out

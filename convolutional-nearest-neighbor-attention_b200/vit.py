@@ -110,8 +110,12 @@ class TransformerEncoder(nn.Module):
     def folds_norm1(self, x) -> bool:
         """Whether this block consumes un-normalised rows plus their moments (norm1 folded into the
         K/V/Q projection): the block before it then emits the moments from its last GEMM."""
+        return x.is_cuda and self.folds_norm1_shape(x.shape[0], x.shape[1], x.dtype)
+
+    def folds_norm1_shape(self, B: int, T: int, dtype) -> bool:
+        """``folds_norm1`` for a CUDA input (B, T, d_hidden) of ``dtype`` that does not exist yet."""
         return (self.fold_layernorm and isinstance(self.attention, MultiHeadConvNNAttention) and
-                self.attention.prenorm_supported(x))
+                self.attention.prenorm_supported_shape(B, T, dtype))
 
     def _forward_library(self, x, moments=None, want_moments=False):
         """The same block in libconvnn_b200: both Linear layers (GELU and the skip connections folded
@@ -193,11 +197,19 @@ class ViT(nn.Module):
                     self._pixel_stats = (key, torch.tensor(self.pixel_mean, dtype=torch.float32, device=x.device),
                                          1.0 / torch.tensor(self.pixel_std, dtype=torch.float32, device=x.device))
                 _, mean, inv_std = self._pixel_stats
+            blocks = list(self.transformer_encoder)
+            act = pemb.linear_projection.weight.dtype if x.dtype == torch.uint8 else x.dtype
+            T = self.n_patches + 1
+            # the first block's folded norm1 reads the row moments: the embedding's last kernel writes them
+            first_folds = (bool(blocks) and act == torch.bfloat16 and x.dim() == 4 and
+                           not (blocks[0].training and (blocks[0].dropout1.p > 0 or blocks[0].dropout2.p > 0)) and
+                           blocks[0].folds_norm1_shape(x.shape[0], T, act))
             x = ops.patch_embed(x, pemb.linear_projection.weight, pemb.linear_projection.bias, pemb.norm.weight,
                                 pemb.norm.bias, pe_mod.cls_tokens, pe_mod.pe, self.args.patch_size, pemb.norm.eps,
-                                pixel_mean=mean, pixel_inv_std=inv_std)
-            blocks = list(self.transformer_encoder)
+                                pixel_mean=mean, pixel_inv_std=inv_std, want_moments=first_folds)
             moments = None
+            if first_folds:
+                x, moments = x
             for i, blk in enumerate(blocks):
                 if blk.training and (blk.dropout1.p > 0 or blk.dropout2.p > 0):
                     x, moments = blk(x), None

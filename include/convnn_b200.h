@@ -309,6 +309,13 @@ int convnn_b200_outproj_mlp(const void* o, int64_t ld_o, const void* w_o, const 
                             const void* w1_folded, const void* w1_extra, const void* w2, const void* b2, void* out,
                             int64_t ldo, int64_t M, int32_t D, int32_t DM, float* moments_out, void* stream);
 
+/* convnn_b200_embed_tokens that also writes the moments (sum, sum of squares) of every row it
+ * stores: moments_out = float32 [convnn_b200_moment_stride(B * (Np + 1))][2], one plane, for the first
+ * folded GEMM behind the embedding (instead of a convnn_b200_row_moments pass).  moments_out may be NULL. */
+int convnn_b200_embed_tokens_moments(int dtype, const void* proj, const void* gamma, const void* beta, float eps,
+                                     const void* cls, const void* pe, void* out, int32_t B, int32_t Np, int32_t D,
+                                     float* moments_out, void* stream);
+
 /* ---- the other halves of the reference's branching wrappers (layers.py:574-577, 648-651) ---- */
 
 /* MultiHeadAttention.forward (layers.py:105-130), eval mode, no mask: q, k, v projections with the

@@ -152,12 +152,35 @@ def test_vit_with_and_without_the_fold():
         plain = model(img).float()
         n2 = lib.convnn_b200_launch_count()
     assert _capi.device_status() == 0
-    # per block: two LayerNorm launches and (fused MLP) one GEMM launch fewer; once per forward one
-    # row-moments launch more
-    assert (n2 - n1) - (n1 - n0) == 3 * cfg.num_layers - 1
+    # per block: two LayerNorm launches and (fused MLP) one GEMM launch fewer; the first block's row
+    # moments come from the embedding's last kernel, not from a launch of their own
+    assert (n2 - n1) - (n1 - n0) == 3 * cfg.num_layers
     err = rel_err(folded, plain)
     print(f"logits, folded against unfused: rel err {err:.3e}")
     assert err < 0.1
+
+
+def test_patch_embed_emits_the_moments_of_the_rows_it_stores():
+    """The embedding's last kernel (LayerNorm + class token + positional table) also writes (sum, sum of
+    squares) of every stored row, class-token rows included: the same numbers row_moments computes from
+    the result, and the result itself is unchanged by asking for them."""
+    B, C, HW, P, D = 5, 3, 64, 16, 192
+    Np = (HW // P) ** 2
+    img = rnd(B, C, HW, HW, seed=71)
+    w, b = rnd(D, C, P, P, seed=72, scale=(C * P * P) ** -0.5), rnd(D, seed=73, scale=0.1)
+    g, bt = rnd(D, seed=74, scale=0.2, shift=1.0), rnd(D, seed=75, scale=0.2)
+    cls, pe = rnd(1, 1, D, seed=76), rnd(1, Np + 1, D, seed=77)
+    plain = ops.patch_embed(img, w, b, g, bt, cls, pe, P)
+    out, mom = ops.patch_embed(img, w, b, g, bt, cls, pe, P, want_moments=True)
+    torch.cuda.synchronize()
+    assert torch.equal(out, plain)
+    M = B * (Np + 1)
+    assert mom.shape == (1, _capi.lib().convnn_b200_moment_stride(M), 2)
+    want = ops.row_moments(out)
+    assert torch.allclose(mom[0, :M], want[0, :M], rtol=1e-5, atol=1e-4)
+    od = out.double().view(M, D)
+    assert torch.allclose(mom[0, :M, 0].double(), od.sum(1), rtol=1e-5, atol=1e-3)
+    assert torch.allclose(mom[0, :M, 1].double(), (od * od).sum(1), rtol=1e-5, atol=1e-3)
 
 
 def mlp_f64(x, gamma, beta, w1, b1, w2, b2, eps):
