@@ -128,17 +128,18 @@ enum Bar : int {            // indices into the barrier array
     XFREE = 2,              // [2] local: the tile's TMA store has read the buffer
     W1FULL = 4,             // [2] leader
     A1FULL = 6,             // [2] local: acc1 super-chunk complete (= its W1 slot is free again)
-    A1EMPTY = 8,            // [2] leader: 16 warps x 2 CTAs have read it
+    A1EMPTY = 8,            // [2] leader: the warps that drain it (8, with OP 16, x 2 CTAs) have read it
     W2FULL = 10,            // [NSW2] leader
     W2EMPTY = 13,           // [NSW2] local (committed by MMA 2)
     HFULL = 16,             // [2] leader: 8 warps x 2 CTAs have written the h chunk
-    HEMPTY = 18,            // [2] local: MMA 2 has read it
+    HEMPTY = 18,            // [2] local: MMA 2 has read it (written by epilogue group 0, or by all warps with OP)
     A2FULL = 20,            // [1] local: acc2 of a tile complete
     A2EMPTY = 21,           // [1] leader: 16 warps x 2 CTAs have read it
     XAFULL = 22,            // [2] leader: extra chunk of both CTAs written
     OUTREADY = 24,          // [2] local: the 16 epilogue warps have finished the tile's rows in the x buffer
     STATREADY = 26,         // [2] local (OP): the 16 epilogue warps have written x1 and its partial moments
-    NBARS = 28
+    HEMPTY1 = 28,           // [2] local: MMA 2 has read the h chunk that epilogue group 1 wrote
+    NBARS = 30
 };
 
 // OP: the attention layer's output projection and skip connection run first, per tile:
@@ -173,9 +174,9 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     if (threadIdx.x == 0) {
         auto init = [&](int i, int n, int count) { for (int k = 0; k < n; ++k) mbar_init(&bars[i + k], count); };
         init(XFULL, 2, 1); init(XFREE, 2, 1);
-        init(W1FULL, 2, 1); init(A1FULL, 2, 1); init(A1EMPTY, 2, 32);
+        init(W1FULL, 2, 1); init(A1FULL, 2, 1); init(A1EMPTY, 2, OP ? 32 : 16);
         init(W2FULL, NSW2, 1); init(W2EMPTY, NSW2, 1);
-        init(HFULL, 2, 16); init(HEMPTY, 2, 1);
+        init(HFULL, 2, 16); init(HEMPTY, 2, 1); init(HEMPTY1, 2, 1);
         init(A2FULL, 1, 1); init(A2EMPTY, 1, 32);
         init(XAFULL, 2, 2);
         init(OUTREADY, 2, 16);
@@ -207,6 +208,7 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     const uint32_t x_tile_bytes = (uint32_t)p.KC * 16384u;
     auto row0_of = [&](int it) { return (cluster_id + it * n_clusters) * 2 * BM + (int)rank * BM; };
     const uint32_t acc2_col = 2 * SC;            // TMEM: acc1[2] at columns 0 / 128, acc2 behind them
+    const uint32_t h_col = 512 - 2 * (CH / 2);   // !OP: the two h chunks (bfloat16 pairs: 32 columns each) in the last 64
     // Order of the accumulator items of a tile (the same in the producer, the MMA 1 thread and the epilogue
     // warps): its super-chunks 0 .. nsc - 1 and, with OP, the two output-projection items of the NEXT tile in
     // front of super-chunk kp, so that x1, its moments and the extra operand chunk of the next tile are
@@ -377,9 +379,20 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                 if (!mbar_wait_a(lbar(W2FULL + s), ph, abort_flag)) { give_up(60); break; }
                 mtrace(cluster_id == 0, 6, g);
                 tc_fence_after_sync();
-                mma_chunk_pair(d2, desc(dhi, base + L.h + hb * 16384u), desc(dhi, base + L.w2 + s * L.w2_slot), idesc2, 4, c != 0);
+                const uint64_t w2d = desc(dhi, base + L.w2 + s * L.w2_slot);
+                if constexpr (OP) {
+                    mma_chunk_pair(d2, desc(dhi, base + L.h + hb * 16384u), w2d, idesc2, 4, c != 0);
+                } else {
+                    // h straight from tensor memory, where the epilogue warps put it: 8 columns per K = 16 step
+                    const uint32_t ha = tmem_base + h_col + hb * 32u;
+                    mma_bf16_ts_pair(d2, ha, w2d, idesc2, c != 0);
+                    mma_bf16_ts_pair(d2, ha + 8, w2d + 2, idesc2, 1);
+                    mma_bf16_ts_pair(d2, ha + 16, w2d + 4, idesc2, 1);
+                    mma_bf16_ts_pair(d2, ha + 24, w2d + 6, idesc2, 1);
+                }
                 mma_commit_pair_both(lbar(W2EMPTY + s));
-                mma_commit_pair_both(lbar(HEMPTY + hb));
+                // without OP the super-chunks alternate between the two epilogue groups, each with barriers of its own
+                mma_commit_pair_both(lbar((!OP && ((g >> 1) & 1u) ? HEMPTY1 : HEMPTY) + hb));
                 if (c == nch - 1) mma_commit_pair_both(lbar(A2FULL));
                 mtrace(cluster_id == 0, 7, g);
                 if (++s == NSW2) { s = 0; ph ^= 1u; }
@@ -454,8 +467,11 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             if (lane == 0) mbar_arrive_cluster(leadbar(XAFULL + xb));
         }
     } else {
-        // ---- epilogue warps: 32 columns of every super-chunk through GELU, then a quarter of the tile's
-        // output columns
+        // ---- epilogue warps: the super-chunks through GELU, then a quarter of the tile's output columns.
+        // Without OP the sixteen warps form two groups of eight that take the super-chunks in turn (group g
+        // drains acc1[g]; a warp covers 32 columns of each of the super-chunk's two h chunks), so that one
+        // group's special-function phase overlaps the other group's TMEM reads, stores, fences and waits;
+        // with OP all sixteen take 32 columns of every super-chunk.
         const int ew = warp - 3;
         const int cg = ew >> 2, lq = warp & 3;                    // column group, TMEM lane quarter
         const int hb = cg >> 1;                                   // h chunk this warp writes into
@@ -578,20 +594,57 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             if (lane == 0) mbar_arrive(&bars[STATREADY + xb2]);
             n += 2;
         };
+        // !OP: super-chunk number `n` (parity = this warp's group, j = n / 2) of tile tn
+        const int grp = ew >> 3, half = cg & 1;
+        int cur_tile = -1;
+        auto gelu_step2 = [&](int tn, uint32_t j) {
+            const uint32_t b = (uint32_t)grp;
+            bool ok = mbar_wait(&bars[A1FULL + b], j & 1u, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) { die(63); return; }
+            mtrace(cluster_id == 0 && rank == 0 && (ew & 7) == 0 && lane == 0, 8, 2 * j + b);
+            tc_fence_after_sync();
+            if (tn != cur_tile) { rstd = rstd_s[((uint32_t)tn & 1u) * BM + r]; cur_tile = tn; }
+            const f32x2 r2 = pack2(0.5f * rstd, 0.5f * rstd);
+#pragma unroll 1
+            for (int c = 0; c < 2; ++c) {
+                uint32_t acc[32];
+                tmem_ld_x32(tmem_base + lane_addr + b * SC + c * CH + half * 32, acc);
+                tmem_ld_wait();
+                if (c == 1) {
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(leadbar(A1EMPTY + b));          // acc1 buffer may be overwritten
+                }
+                uint32_t pk[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e)
+                    pk[e] = gelu_pair_bf16x2(__uint_as_float(acc[2 * e]), __uint_as_float(acc[2 * e + 1]), r2);
+                if (c == 0) mtrace(cluster_id == 0 && rank == 0 && (ew & 7) == 0 && lane == 0, 9, 2 * j + b);
+                // MMA 2 has read the h chunk of the super-chunk before this one (the other group's; it is
+                // consumed after this group's previous one, so this wait covers both)
+                ok = grp ? mbar_wait(&bars[HEMPTY + c], j & 1u, abort_flag)
+                         : mbar_wait(&bars[HEMPTY1 + c], (j & 1u) ^ 1u, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) { die(64); return; }
+                if (c == 0) mtrace(cluster_id == 0 && rank == 0 && (ew & 7) == 0 && lane == 0, 10, 2 * j + b);
+                // the packed pairs are MMA 2's A operand as they are: 16 tensor-memory columns of this warp's rows
+                tc_fence_after_sync();
+                tmem_st_x16(tmem_base + lane_addr + h_col + (uint32_t)c * 32u + (uint32_t)half * 16u, pk);
+                tmem_st_wait();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(leadbar(HFULL + c));
+            }
+            mtrace(cluster_id == 0 && rank == 0 && (ew & 7) == 0 && lane == 0, 11, 2 * j + b);
+        };
         // Per tile `it`: its super-chunks 1 .. nsc - 1, then super-chunk 0 of tile it + 1 (slot sc == nsc: it is
         // activated before the final epilogue of tile it, whose last MMA 2 drains meanwhile), with the
         // output-projection step of tile it + 1 in front of slot kp.  Round it = -1 (OP only) holds what
         // precedes tile 0: its output-projection step and its super-chunk 0.
-        for (int it = OP ? -1 : 0; it < my_tiles; ++it) {
+        // final epilogue of tile `it`: out = x + round(acc2 + b2), in place in the x tile
+        auto final_epilogue = [&](int it) {
             const uint32_t xb = (uint32_t)it & 1u;
-            for (int sc = it < 0 ? kp : ((it == 0 && !OP) ? 0 : 1); sc <= nsc && alive; ++sc) {
-                if (OP && sc == kp - 1 && it + 1 < my_tiles) outproj_prefetch(it + 1);
-                if (OP && sc == kp && it + 1 < my_tiles) outproj_step(it + 1);
-                const int git = sc < nsc ? it : it + 1, gsc = sc < nsc ? sc : 0;
-                if (alive && git >= 0 && git < my_tiles) gelu_step(git, gsc);
-            }
-            if (it < 0) continue;
-            // ---- final epilogue of the tile: out = x + round(acc2 + b2), in place in the x tile ----
             if (alive) {
                 bool ok = mbar_wait(&bars[A2FULL], (uint32_t)it & 1u, abort_flag);
                 ok = __all_sync(0xffffffffu, ok);
@@ -650,6 +703,33 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             mtrace(cluster_id == 0 && rank == 0 && ew == 0 && lane == 0, 14, it);
             __syncwarp();
             if (lane == 0 && alive) mbar_arrive(&bars[OUTREADY + xb]);   // 16 of these let the TMA store go
+        };
+        if constexpr (OP) {
+            for (int it = -1; it < my_tiles; ++it) {
+                for (int sc = it < 0 ? kp : 1; sc <= nsc && alive; ++sc) {
+                    if (sc == kp - 1 && it + 1 < my_tiles) outproj_prefetch(it + 1);
+                    if (sc == kp && it + 1 < my_tiles) outproj_step(it + 1);
+                    const int git = sc < nsc ? it : it + 1, gsc = sc < nsc ? sc : 0;
+                    if (alive && git >= 0 && git < my_tiles) gelu_step(git, gsc);
+                }
+                if (it >= 0) final_epilogue(it);
+            }
+        } else {
+            // Group g takes the super-chunks whose running number has parity g.  Before the final epilogue of
+            // tile `it` a group finishes its super-chunks of that tile and, if it is the one that owns it,
+            // super-chunk 0 of tile it + 1 (whose MMA 1 is long done; the tile's last MMA 2 drains meanwhile).
+            uint32_t j = 0;
+            int tn = 0, sc = grp;
+            while (sc >= nsc) { sc -= nsc; ++tn; }
+            for (int it = 0; it < my_tiles; ++it) {
+                while (alive && tn < my_tiles && (tn <= it || (tn == it + 1 && sc == 0))) {
+                    gelu_step2(tn, j);
+                    ++j;
+                    sc += 2;
+                    while (sc >= nsc) { sc -= nsc; ++tn; }
+                }
+                final_epilogue(it);
+            }
         }
     }
 

@@ -299,6 +299,17 @@ __device__ __forceinline__ void mma_chunk_pair(uint32_t d_tmem, uint64_t adesc, 
         mma_bf16_ss_pair(d_tmem, adesc + 2, bdesc + 2, idesc, 1);
     }
 }
+// The same with the A operand in tensor memory: each CTA of the pair supplies its 128 rows from its own
+// TMEM at `tmem_a` (lane = row, two consecutive K elements of 16 bits per 32-bit column, K-major).
+__device__ __forceinline__ void mma_bf16_ts_pair(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 // One arrival on the barrier at `bar_cluster` (own or peer CTA) when every MMA this thread
 // has issued so far has completed in both CTAs.
 __device__ __forceinline__ void mma_commit_pair(uint32_t bar_cluster) {
@@ -339,6 +350,16 @@ __device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Registers -> 16 consecutive 32-bit TMEM columns of the warp's 32 lanes (lane i <- thread i).
+__device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ bool elect_one() {
     uint32_t pred;

@@ -196,7 +196,10 @@ def mlp_f64(x, gamma, beta, w1, b1, w2, b2, eps):
 @pytest.mark.parametrize("M,D,DM,shift,bias2", [(777, 192, 768, 0.0, True), (1, 192, 768, 0.0, True), (256, 192, 768, 2.0, False),
                                                 (50432, 192, 768, 0.0, True), (5000, 192, 768, -1.0, True),
                                                 (1000, 128, 512, 0.5, True), (1000, 64, 256, 0.0, True),
-                                                (300, 192, 1536, 0.0, True)])
+                                                (300, 192, 1536, 0.0, True),
+                                                # odd and single super-chunk counts, several tiles per cluster
+                                                (60000, 192, 384, 0.0, True), (60000, 128, 128, 0.0, True),
+                                                (40000, 64, 640, 0.3, False)])
 def test_prenorm_mlp_against_float64(M, D, DM, shift, bias2):
     """The whole MLP block in one kernel (norm2 folded, GELU, both Linear layers, skip connection): within
     the bfloat16 tolerance of float64 arithmetic on the same inputs and as close as the two-kernel path
