@@ -82,8 +82,9 @@ __device__ __forceinline__ uint32_t gelu_pair_bf16x2(float a, float b, f32x2 hal
 constexpr int BM = 128;        // rows per CTA
 constexpr int SC = 128;        // hidden columns per MMA 1 step ("super-chunk"): two h chunks
 constexpr int CH = 64;         // hidden columns per h chunk (MMA 2 step)
-constexpr int NSW2 = 3;        // ring depth of the W2 chunks
-constexpr int NT = 20 * 32;    // TMA, MMA 1, extra-chunk, 16 epilogue warps, MMA 2
+// ring depth of the W2 chunks: 3 with OP (h chunks in shared memory), 5 without (h in tensor memory)
+__host__ __device__ constexpr int nsw2(bool op) { return op ? 3 : 5; }
+constexpr int NT = 21 * 32;    // TMA, MMA 1, extra-chunk, 16 epilogue warps, MMA 2, W2 stream
 
 struct MlpParams {
     int M, D, DM;
@@ -105,16 +106,16 @@ struct Smem {           // byte offsets from the 1 KB-aligned base
     uint32_t w1_slot, w2_slot;
 };
 
-__host__ __device__ inline Smem smem_plan(int D) {
+__host__ __device__ inline Smem smem_plan(int D, bool op) {
     Smem s;
     const uint32_t KC = D / 64;
     uint32_t o = 0;
     s.x = o; o += 2u * KC * 16384u;                 // two x tiles of KC sub-chunks [128 x 64]
-    s.h = o; o += 2u * 16384u;                      // the two h chunks [128 x 64] of a super-chunk
+    s.h = o; o += op ? 2u * 16384u : 0u;            // OP: the two h chunks [128 x 64] of a super-chunk
     s.w1_slot = KC * 8192u + 2048u;                 // [64 x 64] per sub-chunk + the fold's extra rows [64 x 16]
     s.w1 = o; o += 2u * s.w1_slot;
     s.w2_slot = ((uint32_t)(D / 2) * 128u + 1023u) & ~1023u;   // [D/2 x 64]
-    s.w2 = o; o += NSW2 * s.w2_slot;
+    s.w2 = o; o += (uint32_t)nsw2(op) * s.w2_slot;
     s.xa = o; o += 2u * 4096u;
     s.rstd = o; o += 2u * BM * 4u;
     s.bias = o; o += (uint32_t)D * 2u;              // b2
@@ -129,8 +130,6 @@ enum Bar : int {            // indices into the barrier array
     W1FULL = 4,             // [2] leader
     A1FULL = 6,             // [2] local: acc1 super-chunk complete (= its W1 slot is free again)
     A1EMPTY = 8,            // [2] leader: the warps that drain it (8, with OP 16, x 2 CTAs) have read it
-    W2FULL = 10,            // [NSW2] leader
-    W2EMPTY = 13,           // [NSW2] local (committed by MMA 2)
     HFULL = 16,             // [2] leader: 8 warps x 2 CTAs have written the h chunk
     HEMPTY = 18,            // [2] local: MMA 2 has read it (written by epilogue group 0, or by all warps with OP)
     A2FULL = 20,            // [1] local: acc2 of a tile complete
@@ -139,7 +138,9 @@ enum Bar : int {            // indices into the barrier array
     OUTREADY = 24,          // [2] local: the 16 epilogue warps have finished the tile's rows in the x buffer
     STATREADY = 26,         // [2] local (OP): the 16 epilogue warps have written x1 and its partial moments
     HEMPTY1 = 28,           // [2] local: MMA 2 has read the h chunk that epilogue group 1 wrote
-    NBARS = 30
+    W2FULL = 30,            // [nsw2] leader
+    W2EMPTY = 35,           // [nsw2] local (committed by MMA 2)
+    NBARS = 40
 };
 
 // OP: the attention layer's output projection and skip connection run first, per tile:
@@ -156,7 +157,8 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
               const __grid_constant__ CUtensorMap tmW2, const __grid_constant__ CUtensorMap tmWO, const MlpParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    const Smem L = smem_plan(p.D);
+    const Smem L = smem_plan(p.D, OP);
+    constexpr int NSW2 = nsw2(OP);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bars);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 40);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -219,8 +221,8 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         // ---- TMA producers (each CTA fetches its own rows of x and its half of every weight chunk).
         // One thread can start a TMA operation only every ~0.3 us, whatever its size, while operations
         // started by different lanes overlap: lanes 0 .. KC issue the sub-chunks of a W1 super-chunk (and
-        // the x tiles) with one instruction of the warp; lane KC + 1 runs the W2 stream, whose slots are
-        // released later (by MMA 2) and which must not hold up W1.
+        // the x tiles) with one instruction of the warp; lane KC + 2 stores finished tiles and refills their
+        // buffers.  The W2 stream, whose slots are released by MMA 2, has warp 20.
         const uint32_t w1_mask = (2u << p.KC) - 1u;              // lanes 0 .. KC
         if (lane <= p.KC) {
             bool ok = true;
@@ -291,19 +293,6 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                 if (it + 2 < my_tiles) load_next(it + 2);
             }
             tma_store_wait<0>();
-        } else if (lane == p.KC + 1) {
-            const uint32_t total = (uint32_t)my_tiles * (uint32_t)nsc * 2u;   // h chunks
-            uint32_t s = 0, ph = 0;
-            int c = 0;
-            const int nch = nsc * 2;
-            for (uint32_t g = 0; g < total; ++g) {
-                if (!mbar_wait_a(lbar(W2EMPTY + s), ph ^ 1u, abort_flag)) { give_up(53); break; }
-                mtrace(cluster_id == 0 && rank == 0, 0, g);
-                if (rank == 0) mbar_expect_tx_a(lbar(W2FULL + s), 2u * (uint32_t)(p.D / 2) * 128u);
-                tma_load_2d_pair(base + L.w2 + s * L.w2_slot, &tmW2, leadbar(W2FULL + s), c * CH, (int)rank * (p.D / 2));
-                if (++s == NSW2) { s = 0; ph ^= 1u; }
-                if (++c == nch) c = 0;
-            }
         }
     } else if (warp == 1) {
         // ---- issuer of MMA 1 (leader only): acc1[n & 1] = x W1'[super-chunk]^T, N = 128.  A tcgen05.mma
@@ -397,6 +386,23 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                 mtrace(cluster_id == 0, 7, g);
                 if (++s == NSW2) { s = 0; ph ^= 1u; }
                 if (++c == nch) { c = 0; ++it; }
+            }
+        }
+    } else if (warp == 20) {
+        // ---- the W2 stream, a warp of its own: lanes of one warp that wait in different loops take turns, and
+        // a W2 lane next to the W1 lanes only advanced when those came out of their (long) waits
+        if (lane == 0) {
+            const uint32_t total = (uint32_t)my_tiles * (uint32_t)nsc * 2u;   // h chunks
+            uint32_t s = 0, ph = 0;
+            int c = 0;
+            const int nch = nsc * 2;
+            for (uint32_t g = 0; g < total; ++g) {
+                if (!mbar_wait_a(lbar(W2EMPTY + s), ph ^ 1u, abort_flag)) { give_up(53); break; }
+                mtrace(cluster_id == 0 && rank == 0, 0, g);
+                if (rank == 0) mbar_expect_tx_a(lbar(W2FULL + s), 2u * (uint32_t)(p.D / 2) * 128u);
+                tma_load_2d_pair(base + L.w2 + s * L.w2_slot, &tmW2, leadbar(W2FULL + s), c * CH, (int)rank * (p.D / 2));
+                if (++s == NSW2) { s = 0; ph ^= 1u; }
+                if (++c == nch) c = 0;
             }
         }
     } else if (warp == 2) {
@@ -606,6 +612,8 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             tc_fence_after_sync();
             if (tn != cur_tile) { rstd = rstd_s[((uint32_t)tn & 1u) * BM + r]; cur_tile = tn; }
             const f32x2 r2 = pack2(0.5f * rstd, 0.5f * rstd);
+            // one 32-column piece after the other (reading both up front hands acc1 back earlier, but MMA 1 then
+            // runs ahead of MMA 2 on the one tensor pipe and the kernel is 4 % slower)
 #pragma unroll 1
             for (int c = 0; c < 2; ++c) {
                 uint32_t acc[32];
@@ -750,7 +758,7 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
 
 bool mlp_tc_supported(int D, int DM, int planes) {
     if (D % 64 != 0 || D < 64 || D > 192 || DM % 128 != 0 || DM < 128 || planes < 1 || planes > 16) return false;
-    return smem_plan(D).total + 1024 <= 227 * 1024;
+    return smem_plan(D, true).total + 1024 <= 227 * 1024 && smem_plan(D, false).total + 1024 <= 227 * 1024;
 }
 
 int mlp_tc_moment_planes() { return 4; }
@@ -802,7 +810,7 @@ int launch_mlp_tc(const void* x, long long ldx, const float* moments, int planes
     } else {
         tmWO = tmW2;
     }
-    const size_t smem = smem_plan(D).total + 1024;
+    const size_t smem = smem_plan(D, w_o != nullptr).total + 1024;
     auto kern = w_o ? mlp_tc_kernel<true> : mlp_tc_kernel<false>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return set_error(CONVNN_E_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
@@ -813,7 +821,8 @@ int launch_mlp_tc(const void* x, long long ldx, const float* moments, int planes
     cfg.blockDim = dim3(NT); cfg.dynamicSmemBytes = smem; cfg.stream = st;
     cfg.attrs = attr; cfg.numAttrs = 1;
     cfg.gridDim = dim3(2);
-    static std::atomic<long long> occ_cache{-1};         // co-resident clusters for this shared-memory size
+    static std::atomic<long long> occ_caches[2] = {{-1}, {-1}};   // co-resident clusters per kernel and shared-memory size
+    std::atomic<long long>& occ_cache = occ_caches[w_o ? 1 : 0];
     int max_clusters = 0;
     const long long seen = occ_cache.load(std::memory_order_relaxed);
     if (seen >= 0 && (size_t)(seen >> 20) == smem) {
