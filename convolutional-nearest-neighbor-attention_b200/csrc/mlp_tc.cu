@@ -3,10 +3,11 @@
 // The hidden activations (rows x d_mlp, four times the size of x) never leave the SM: a CTA pair
 // owns 256 rows (128 per CTA) and walks the hidden width in super-chunks of 128 columns,
 //     MMA 1  acc1 = x W1'[super-chunk]^T (+ the pre-norm fold's extra K = 16 step)   M = 256, N = 128
-//     GELU   h = bf16(GELU(rstd * acc1)) written as two 64-column A operands (128-byte swizzle)
-//     MMA 2  acc2 += h[chunk] W2[:, chunk]^T, twice                                  M = 256, N = D
+//     GELU   h = bf16(GELU(rstd * acc1)) stored back to TMEM as two 64-column A operands (bfloat16 pairs)
+//     MMA 2  acc2 += h[chunk] W2[:, chunk]^T, twice, A read from TMEM                M = 256, N = D
 // with acc1 double-buffered (super-chunk n + 1 is multiplied while n is activated), all in TMEM
-// (2 x 128 + D <= 512 columns).  The LayerNorm
+// (2 x 128 + D + 2 x 32 <= 512 columns): h does not pass through shared memory, whose bandwidth the
+// MMAs' operand reads, the TMA writes and the epilogue already share.  The LayerNorm
 // is folded as in gemm_tc.cu: W1' = W1 diag(gamma), the rows' moments (sum x, sum x^2) arrive
 // from the kernel that wrote x, one warp turns them into the extra operand chunk [-mean, sigma].
 // The skip connection needs no second read of x: the final epilogue adds the rounded result to
@@ -15,8 +16,10 @@
 //
 // Two CTAs of a cluster form one tcgen05 cta_group::2 unit so that each CTA fetches only half of
 // every weight chunk: per 128 rows a CTA streams (d_mlp x D + D x d_mlp) / 2 weights from L2.
-// Warps: 0 TMA producer, 1 issuer of MMA 1 (leader CTA), 2 extra-chunk preparation, 3-18 epilogue
-// (chunk parity x column half x TMEM lane quarter), 19 issuer of MMA 2 (leader CTA).  "Operands landed" barriers live in the
+// Warps: 0 TMA producer of x and W1 (and the tile store), 1 issuer of MMA 1 (leader CTA), 2 extra-chunk
+// preparation, 3-18 epilogue (column group x TMEM lane quarter), 19 issuer of MMA 2 (leader CTA), 20 TMA
+// producer of W2 (a warp of its own: lanes of one warp that wait in different loops only take turns).
+// "Operands landed" barriers live in the
 // leader and are credited by both CTAs' loads; completions are committed to both CTAs.  Every
 // wait is bounded; a warp whose wait expires raises the pair's abort flags and stops working, which
 // makes every other wait of the pair give up: nothing can hang.
@@ -82,8 +85,7 @@ __device__ __forceinline__ uint32_t gelu_pair_bf16x2(float a, float b, f32x2 hal
 constexpr int BM = 128;        // rows per CTA
 constexpr int SC = 128;        // hidden columns per MMA 1 step ("super-chunk"): two h chunks
 constexpr int CH = 64;         // hidden columns per h chunk (MMA 2 step)
-// ring depth of the W2 chunks: 3 with OP (h chunks in shared memory), 5 without (h in tensor memory)
-__host__ __device__ constexpr int nsw2(bool op) { return op ? 3 : 5; }
+constexpr int NSW2 = 5;        // ring depth of the W2 chunks
 constexpr int NT = 21 * 32;    // TMA, MMA 1, extra-chunk, 16 epilogue warps, MMA 2, W2 stream
 
 struct MlpParams {
@@ -102,20 +104,19 @@ struct MlpParams {
 };
 
 struct Smem {           // byte offsets from the 1 KB-aligned base
-    uint32_t x, h, w1, w2, xa, rstd, bias, bars, total;
+    uint32_t x, w1, w2, xa, rstd, bias, bars, total;
     uint32_t w1_slot, w2_slot;
 };
 
-__host__ __device__ inline Smem smem_plan(int D, bool op) {
+__host__ __device__ inline Smem smem_plan(int D) {
     Smem s;
     const uint32_t KC = D / 64;
     uint32_t o = 0;
     s.x = o; o += 2u * KC * 16384u;                 // two x tiles of KC sub-chunks [128 x 64]
-    s.h = o; o += op ? 2u * 16384u : 0u;            // OP: the two h chunks [128 x 64] of a super-chunk
     s.w1_slot = KC * 8192u + 2048u;                 // [64 x 64] per sub-chunk + the fold's extra rows [64 x 16]
     s.w1 = o; o += 2u * s.w1_slot;
     s.w2_slot = ((uint32_t)(D / 2) * 128u + 1023u) & ~1023u;   // [D/2 x 64]
-    s.w2 = o; o += (uint32_t)nsw2(op) * s.w2_slot;
+    s.w2 = o; o += NSW2 * s.w2_slot;
     s.xa = o; o += 2u * 4096u;
     s.rstd = o; o += 2u * BM * 4u;
     s.bias = o; o += (uint32_t)D * 2u;              // b2
@@ -129,18 +130,17 @@ enum Bar : int {            // indices into the barrier array
     XFREE = 2,              // [2] local: the tile's TMA store has read the buffer
     W1FULL = 4,             // [2] leader
     A1FULL = 6,             // [2] local: acc1 super-chunk complete (= its W1 slot is free again)
-    A1EMPTY = 8,            // [2] leader: the warps that drain it (8, with OP 16, x 2 CTAs) have read it
+    A1EMPTY = 8,            // [2] leader: 16 warps x 2 CTAs have read it
     HFULL = 16,             // [2] leader: 8 warps x 2 CTAs have written the h chunk
-    HEMPTY = 18,            // [2] local: MMA 2 has read it (written by epilogue group 0, or by all warps with OP)
+    HEMPTY = 18,            // [2] local: MMA 2 has read it
     A2FULL = 20,            // [1] local: acc2 of a tile complete
     A2EMPTY = 21,           // [1] leader: 16 warps x 2 CTAs have read it
     XAFULL = 22,            // [2] leader: extra chunk of both CTAs written
     OUTREADY = 24,          // [2] local: the 16 epilogue warps have finished the tile's rows in the x buffer
     STATREADY = 26,         // [2] local (OP): the 16 epilogue warps have written x1 and its partial moments
-    HEMPTY1 = 28,           // [2] local: MMA 2 has read the h chunk that epilogue group 1 wrote
-    W2FULL = 30,            // [nsw2] leader
-    W2EMPTY = 35,           // [nsw2] local (committed by MMA 2)
-    NBARS = 40
+    W2FULL = 28,            // [NSW2] leader
+    W2EMPTY = 33,           // [NSW2] local (committed by MMA 2)
+    NBARS = 38
 };
 
 // OP: the attention layer's output projection and skip connection run first, per tile:
@@ -157,8 +157,7 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
               const __grid_constant__ CUtensorMap tmW2, const __grid_constant__ CUtensorMap tmWO, const MlpParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    const Smem L = smem_plan(p.D, OP);
-    constexpr int NSW2 = nsw2(OP);
+    const Smem L = smem_plan(p.D);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bars);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 40);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -176,9 +175,9 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     if (threadIdx.x == 0) {
         auto init = [&](int i, int n, int count) { for (int k = 0; k < n; ++k) mbar_init(&bars[i + k], count); };
         init(XFULL, 2, 1); init(XFREE, 2, 1);
-        init(W1FULL, 2, 1); init(A1FULL, 2, 1); init(A1EMPTY, 2, OP ? 32 : 16);
+        init(W1FULL, 2, 1); init(A1FULL, 2, 1); init(A1EMPTY, 2, 32);
         init(W2FULL, NSW2, 1); init(W2EMPTY, NSW2, 1);
-        init(HFULL, 2, 16); init(HEMPTY, 2, 1); init(HEMPTY1, 2, 1);
+        init(HFULL, 2, 16); init(HEMPTY, 2, 1);
         init(A2FULL, 1, 1); init(A2EMPTY, 1, 32);
         init(XAFULL, 2, 2);
         init(OUTREADY, 2, 16);
@@ -210,7 +209,7 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     const uint32_t x_tile_bytes = (uint32_t)p.KC * 16384u;
     auto row0_of = [&](int it) { return (cluster_id + it * n_clusters) * 2 * BM + (int)rank * BM; };
     const uint32_t acc2_col = 2 * SC;            // TMEM: acc1[2] at columns 0 / 128, acc2 behind them
-    const uint32_t h_col = 512 - 2 * (CH / 2);   // !OP: the two h chunks (bfloat16 pairs: 32 columns each) in the last 64
+    const uint32_t h_col = 512 - 2 * (CH / 2);   // the two h chunks (bfloat16 pairs: 32 columns each) in the last 64
     // Order of the accumulator items of a tile (the same in the producer, the MMA 1 thread and the epilogue
     // warps): its super-chunks 0 .. nsc - 1 and, with OP, the two output-projection items of the NEXT tile in
     // front of super-chunk kp, so that x1, its moments and the extra operand chunk of the next tile are
@@ -368,20 +367,15 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                 if (!mbar_wait_a(lbar(W2FULL + s), ph, abort_flag)) { give_up(60); break; }
                 mtrace(cluster_id == 0, 6, g);
                 tc_fence_after_sync();
+                // h straight from tensor memory, where the epilogue warps put it: 8 columns per K = 16 step
                 const uint64_t w2d = desc(dhi, base + L.w2 + s * L.w2_slot);
-                if constexpr (OP) {
-                    mma_chunk_pair(d2, desc(dhi, base + L.h + hb * 16384u), w2d, idesc2, 4, c != 0);
-                } else {
-                    // h straight from tensor memory, where the epilogue warps put it: 8 columns per K = 16 step
-                    const uint32_t ha = tmem_base + h_col + hb * 32u;
-                    mma_bf16_ts_pair(d2, ha, w2d, idesc2, c != 0);
-                    mma_bf16_ts_pair(d2, ha + 8, w2d + 2, idesc2, 1);
-                    mma_bf16_ts_pair(d2, ha + 16, w2d + 4, idesc2, 1);
-                    mma_bf16_ts_pair(d2, ha + 24, w2d + 6, idesc2, 1);
-                }
+                const uint32_t ha = tmem_base + h_col + hb * 32u;
+                mma_bf16_ts_pair(d2, ha, w2d, idesc2, c != 0);
+                mma_bf16_ts_pair(d2, ha + 8, w2d + 2, idesc2, 1);
+                mma_bf16_ts_pair(d2, ha + 16, w2d + 4, idesc2, 1);
+                mma_bf16_ts_pair(d2, ha + 24, w2d + 6, idesc2, 1);
                 mma_commit_pair_both(lbar(W2EMPTY + s));
-                // without OP the super-chunks alternate between the two epilogue groups, each with barriers of its own
-                mma_commit_pair_both(lbar((!OP && ((g >> 1) & 1u) ? HEMPTY1 : HEMPTY) + hb));
+                mma_commit_pair_both(lbar(HEMPTY + hb));
                 if (c == nch - 1) mma_commit_pair_both(lbar(A2FULL));
                 mtrace(cluster_id == 0, 7, g);
                 if (++s == NSW2) { s = 0; ph ^= 1u; }
@@ -473,11 +467,11 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             if (lane == 0) mbar_arrive_cluster(leadbar(XAFULL + xb));
         }
     } else {
-        // ---- epilogue warps: the super-chunks through GELU, then a quarter of the tile's output columns.
-        // Without OP the sixteen warps form two groups of eight that take the super-chunks in turn (group g
-        // drains acc1[g]; a warp covers 32 columns of each of the super-chunk's two h chunks), so that one
-        // group's special-function phase overlaps the other group's TMEM reads, stores, fences and waits;
-        // with OP all sixteen take 32 columns of every super-chunk.
+        // ---- epilogue warps: 32 columns of every super-chunk through GELU, then a quarter of the tile's
+        // output columns.  The GELU output is the A operand of MMA 2: the packed bfloat16 pairs go straight
+        // back to tensor memory (16 columns of this warp's rows) and MMA 2 reads them there, so h never
+        // passes through shared memory.  (Two groups of eight warps that alternated over the super-chunks
+        // were measured too: the same time.)
         const int ew = warp - 3;
         const int cg = ew >> 2, lq = warp & 3;                    // column group, TMEM lane quarter
         const int hb = cg >> 1;                                   // h chunk this warp writes into
@@ -514,15 +508,11 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) { die(64); return; }
             mtrace(cluster_id == 0 && rank == 0 && ew == 0 && lane == 0, 10, n);
-            const uint32_t hrow = base + L.h + hb * 16384u + (uint32_t)r * 128u;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const uint32_t slot = (uint32_t)((cg & 1) * 4 + j) ^ ((uint32_t)r & 7u);
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(hrow + (slot << 4)), "r"(pk[4 * j]),
-                             "r"(pk[4 * j + 1]), "r"(pk[4 * j + 2]), "r"(pk[4 * j + 3])
-                             : "memory");
-            }
-            fence_proxy_async();                                  // generic-proxy writes -> visible to MMA 2
+            // the packed pairs are MMA 2's A operand as they are: 16 tensor-memory columns of this warp's rows
+            tc_fence_after_sync();
+            tmem_st_x16(tmem_base + lane_addr + h_col + (uint32_t)hb * 32u + (uint32_t)(cg & 1) * 16u, pk);
+            tmem_st_wait();
+            tc_fence_before_sync();
             __syncwarp();
             mtrace(cluster_id == 0 && rank == 0 && ew == 0 && lane == 0, 11, n);
             if (lane == 0) mbar_arrive_cluster(leadbar(HFULL + hb));
@@ -599,52 +589,6 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars[STATREADY + xb2]);
             n += 2;
-        };
-        // !OP: super-chunk number `n` (parity = this warp's group, j = n / 2) of tile tn
-        const int grp = ew >> 3, half = cg & 1;
-        int cur_tile = -1;
-        auto gelu_step2 = [&](int tn, uint32_t j) {
-            const uint32_t b = (uint32_t)grp;
-            bool ok = mbar_wait(&bars[A1FULL + b], j & 1u, abort_flag);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) { die(63); return; }
-            mtrace(cluster_id == 0 && rank == 0 && (ew & 7) == 0 && lane == 0, 8, 2 * j + b);
-            tc_fence_after_sync();
-            if (tn != cur_tile) { rstd = rstd_s[((uint32_t)tn & 1u) * BM + r]; cur_tile = tn; }
-            const f32x2 r2 = pack2(0.5f * rstd, 0.5f * rstd);
-            // one 32-column piece after the other (reading both up front hands acc1 back earlier, but MMA 1 then
-            // runs ahead of MMA 2 on the one tensor pipe and the kernel is 4 % slower)
-#pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
-                uint32_t acc[32];
-                tmem_ld_x32(tmem_base + lane_addr + b * SC + c * CH + half * 32, acc);
-                tmem_ld_wait();
-                if (c == 1) {
-                    tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster(leadbar(A1EMPTY + b));          // acc1 buffer may be overwritten
-                }
-                uint32_t pk[16];
-#pragma unroll
-                for (int e = 0; e < 16; ++e)
-                    pk[e] = gelu_pair_bf16x2(__uint_as_float(acc[2 * e]), __uint_as_float(acc[2 * e + 1]), r2);
-                if (c == 0) mtrace(cluster_id == 0 && rank == 0 && (ew & 7) == 0 && lane == 0, 9, 2 * j + b);
-                // MMA 2 has read the h chunk of the super-chunk before this one (the other group's; it is
-                // consumed after this group's previous one, so this wait covers both)
-                ok = grp ? mbar_wait(&bars[HEMPTY + c], j & 1u, abort_flag)
-                         : mbar_wait(&bars[HEMPTY1 + c], (j & 1u) ^ 1u, abort_flag);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) { die(64); return; }
-                if (c == 0) mtrace(cluster_id == 0 && rank == 0 && (ew & 7) == 0 && lane == 0, 10, 2 * j + b);
-                // the packed pairs are MMA 2's A operand as they are: 16 tensor-memory columns of this warp's rows
-                tc_fence_after_sync();
-                tmem_st_x16(tmem_base + lane_addr + h_col + (uint32_t)c * 32u + (uint32_t)half * 16u, pk);
-                tmem_st_wait();
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(leadbar(HFULL + c));
-            }
-            mtrace(cluster_id == 0 && rank == 0 && (ew & 7) == 0 && lane == 0, 11, 2 * j + b);
         };
         // Per tile `it`: its super-chunks 1 .. nsc - 1, then super-chunk 0 of tile it + 1 (slot sc == nsc: it is
         // activated before the final epilogue of tile it, whose last MMA 2 drains meanwhile), with the
@@ -723,18 +667,10 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                 if (it >= 0) final_epilogue(it);
             }
         } else {
-            // Group g takes the super-chunks whose running number has parity g.  Before the final epilogue of
-            // tile `it` a group finishes its super-chunks of that tile and, if it is the one that owns it,
-            // super-chunk 0 of tile it + 1 (whose MMA 1 is long done; the tile's last MMA 2 drains meanwhile).
-            uint32_t j = 0;
-            int tn = 0, sc = grp;
-            while (sc >= nsc) { sc -= nsc; ++tn; }
             for (int it = 0; it < my_tiles; ++it) {
-                while (alive && tn < my_tiles && (tn <= it || (tn == it + 1 && sc == 0))) {
-                    gelu_step2(tn, j);
-                    ++j;
-                    sc += 2;
-                    while (sc >= nsc) { sc -= nsc; ++tn; }
+                for (int sc = it == 0 ? 0 : 1; sc <= nsc && alive; ++sc) {
+                    const int git = sc < nsc ? it : it + 1, gsc = sc < nsc ? sc : 0;
+                    if (alive && git < my_tiles) gelu_step(git, gsc);
                 }
                 final_epilogue(it);
             }
@@ -758,7 +694,7 @@ mlp_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
 
 bool mlp_tc_supported(int D, int DM, int planes) {
     if (D % 64 != 0 || D < 64 || D > 192 || DM % 128 != 0 || DM < 128 || planes < 1 || planes > 16) return false;
-    return smem_plan(D, true).total + 1024 <= 227 * 1024 && smem_plan(D, false).total + 1024 <= 227 * 1024;
+    return smem_plan(D).total + 1024 <= 227 * 1024;
 }
 
 int mlp_tc_moment_planes() { return 4; }
@@ -810,7 +746,7 @@ int launch_mlp_tc(const void* x, long long ldx, const float* moments, int planes
     } else {
         tmWO = tmW2;
     }
-    const size_t smem = smem_plan(D, w_o != nullptr).total + 1024;
+    const size_t smem = smem_plan(D).total + 1024;
     auto kern = w_o ? mlp_tc_kernel<true> : mlp_tc_kernel<false>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return set_error(CONVNN_E_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
