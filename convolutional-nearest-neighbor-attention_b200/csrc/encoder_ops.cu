@@ -147,11 +147,15 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const T* __restrict__ x,
 // fp32 pairs, affine parameters held in registers.  Same results as the generic kernel.  A warp
 // works on R consecutive rows at a time and requests the next R while it does so: what bounds
 // the kernel is the number of bytes an SM has in flight, not its arithmetic.
-template <int R, int MINB>
+// EMBED: the embedding tail of the generic kernel (row (b, n) lands at token 1 + n of image b with pe[1 + n]
+// added after rounding, `cls_rows` class-token rows cls + pe[0], optional moments of every stored row);
+// rows < 2^31.
+template <int R, int MINB, bool EMBED>
 __global__ void __launch_bounds__(256, MINB) layernorm_bf16_row256_kernel(
     const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bfloat16* __restrict__ gamma,
     const __nv_bfloat16* __restrict__ beta, float eps, __nv_bfloat16* __restrict__ y, long long ldy, long long rows,
-    int D) {
+    int D, const __nv_bfloat16* __restrict__ pe, const __nv_bfloat16* __restrict__ cls, int Np, long long cls_rows,
+    float2* __restrict__ moments) {
     const int lane = threadIdx.x & 31;
     const long long wpb = blockDim.x >> 5;
     const bool act = lane < D / 8;
@@ -204,15 +208,82 @@ __global__ void __launch_bounds__(256, MINB) layernorm_bf16_row256_kernel(
         for (int o = 16; o > 0; o >>= 1)
 #pragma unroll
             for (int j = 0; j < R; ++j) q[j] += __shfl_xor_sync(0xffffffffu, q[j], o);
+        float m1[R], m2[R];
+        long long orow[R];
 #pragma unroll
         for (int j = 0; j < R; ++j) {
             const float rstd = rsqrtf(q[j] * invD + eps);
+            m1[j] = m2[j] = 0.f;
+            orow[j] = r0 + j;
             if (act && r0 + j < rows) {
                 const f32x2 r2 = pack2(rstd, rstd);
                 f32x2 o2[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) o2[e] = fma2(mul2(d2[j][e], r2), g2[e], b2[e]);
-                *reinterpret_cast<uint4*>(y + (r0 + j) * ldy + lane * 8) = f32x2_to_bf16x8(o2);
+                uint4 ov = f32x2_to_bf16x8(o2);
+                if (EMBED) {
+                    const unsigned rr = (unsigned)(r0 + j), b = rr / (unsigned)Np, n = rr - b * (unsigned)Np;
+                    orow[j] = (long long)b * (Np + 1) + 1 + n;
+                    f32x2 pf[4];
+                    bf16x8_to_f32x2(*reinterpret_cast<const uint4*>(pe + (long long)(1 + n) * D + lane * 8), pf);
+                    bf16x8_to_f32x2(ov, o2);                       // the rounded LayerNorm output, then + pe
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) o2[e] = add2(o2[e], pf[e]);
+                    ov = f32x2_to_bf16x8(o2);
+                    if (moments) {
+                        const uint32_t w[4] = {ov.x, ov.y, ov.z, ov.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float lo = __uint_as_float(w[e] << 16), hi = __uint_as_float(w[e] & 0xffff0000u);
+                            m1[j] += lo + hi;
+                            m2[j] = fmaf(hi, hi, fmaf(lo, lo, m2[j]));
+                        }
+                    }
+                }
+                *reinterpret_cast<uint4*>(y + orow[j] * ldy + lane * 8) = ov;
+            }
+        }
+        if (EMBED && moments) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                for (int j = 0; j < R; ++j) {
+                    m1[j] += __shfl_xor_sync(0xffffffffu, m1[j], o);
+                    m2[j] += __shfl_xor_sync(0xffffffffu, m2[j], o);
+                }
+#pragma unroll
+            for (int j = 0; j < R; ++j)
+                if (lane == 0 && r0 + j < rows) {
+                    const unsigned rr = (unsigned)(r0 + j), b = rr / (unsigned)Np, n = rr - b * (unsigned)Np;
+                    moments[(long long)b * (Np + 1) + 1 + n] = make_float2(m1[j], m2[j]);
+                }
+        }
+    }
+    if (EMBED) {
+        // class-token rows: cls + pe[0], one warp per image
+        const long long gw = blockIdx.x * wpb + (threadIdx.x >> 5), nw = (long long)gridDim.x * wpb;
+        for (long long b = gw; b < cls_rows; b += nw) {
+            float s1 = 0.f, s2 = 0.f;
+            if (act) {
+                f32x2 c2[4], p2[4];
+                bf16x8_to_f32x2(*reinterpret_cast<const uint4*>(cls + lane * 8), c2);
+                bf16x8_to_f32x2(*reinterpret_cast<const uint4*>(pe + lane * 8), p2);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) c2[e] = add2(c2[e], p2[e]);
+                const uint4 ov = f32x2_to_bf16x8(c2);
+                *reinterpret_cast<uint4*>(y + b * (Np + 1) * ldy + lane * 8) = ov;
+                const uint32_t w[4] = {ov.x, ov.y, ov.z, ov.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float lo = __uint_as_float(w[e] << 16), hi = __uint_as_float(w[e] & 0xffff0000u);
+                    s1 += lo + hi;
+                    s2 = fmaf(hi, hi, fmaf(lo, lo, s2));
+                }
+            }
+            if (moments) {
+                s1 = warp_sum(s1);
+                s2 = warp_sum(s2);
+                if (lane == 0) moments[b * (Np + 1)] = make_float2(s1, s2);
             }
         }
     }
@@ -349,7 +420,7 @@ int launch_layernorm(int dtype, const void* x, long long ldx, const void* gamma,
     if (D % V != 0 || ldx % V != 0 || ldy % V != 0 || !aligned16(x) || !aligned16(y) || !aligned16(gamma) ||
         !aligned16(beta) || (pe && (!aligned16(pe) || !aligned16(cls))))
         return set_error(CONVNN_E_ALIGN, "layernorm: D, strides and pointers must be multiples of 16 bytes");
-    if (dtype == CONVNN_BF16 && !pe && !moments && D <= 256) {
+    if (dtype == CONVNN_BF16 && D <= 256 && (pe ? (cls != nullptr && rows < (1ll << 31) && Np > 0) : !moments)) {
         // Two 8-warp CTAs per SM (the kernel keeps 121 registers: four rows in flight and four
         // requested per warp), measured 9.6 us at 50 k rows of 192 channels against 11.0 us with
         // one row per step and four CTAs per SM; register-capped variants that spill are twice as slow.
@@ -357,9 +428,15 @@ int launch_layernorm(int dtype, const void* x, long long ldx, const void* gamma,
         int blocks = (int)((rows + 8 * R - 1) / (8 * R));
         if (blocks > 148 * MINB) blocks = 148 * MINB;
         if (blocks < 1) blocks = 1;
-        layernorm_bf16_row256_kernel<R, MINB><<<blocks, 256, 0, st>>>(
-            static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(gamma),
-            static_cast<const __nv_bfloat16*>(beta), eps, static_cast<__nv_bfloat16*>(y), ldy, rows, D);
+        const auto* xb = static_cast<const __nv_bfloat16*>(x);
+        const auto *gb = static_cast<const __nv_bfloat16*>(gamma), *bb = static_cast<const __nv_bfloat16*>(beta);
+        if (pe)
+            layernorm_bf16_row256_kernel<R, MINB, true><<<blocks, 256, 0, st>>>(
+                xb, ldx, gb, bb, eps, static_cast<__nv_bfloat16*>(y), ldy, rows, D, static_cast<const __nv_bfloat16*>(pe),
+                static_cast<const __nv_bfloat16*>(cls), Np, cls_rows, reinterpret_cast<float2*>(moments));
+        else
+            layernorm_bf16_row256_kernel<R, MINB, false><<<blocks, 256, 0, st>>>(
+                xb, ldx, gb, bb, eps, static_cast<__nv_bfloat16*>(y), ldy, rows, D, nullptr, nullptr, 0, 0, nullptr);
         CONVNN_CHECK_LAUNCH("layernorm_bf16_row256");
         return CONVNN_OK;
     }
