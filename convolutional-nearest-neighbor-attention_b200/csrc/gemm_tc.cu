@@ -194,7 +194,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint8_t* mring = reinterpret_cast<uint8_t*>(rstd_s + 2 * BM);      // [MOM_SLOTS][ln_planes][128] float2
     uint64_t* bars = LNF ? reinterpret_cast<uint64_t*>(mring + (size_t)MOM_SLOTS * p.ln_planes * 1024)
                          : reinterpret_cast<uint64_t*>(btile + (p.mma_bias ? (size_t)p.n_n_tiles * bn_cta * 32 : 0));
-    static_assert(!(STAT && WIDE), "the fused statistic needs a row's whole head in one warp");
+    static_assert(!(STAT && WIDE) || LNF, "the statistic with sixteen epilogue warps is built for the pre-norm fold");
     uint64_t* full = bars;
     uint64_t* empty = bars + MAX_STAGES;
     uint64_t* tfull = bars + 2 * MAX_STAGES;
@@ -204,6 +204,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint64_t* mfull = xfull + 2;                               // LNF: moment tile landed in ring slot 0..3
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mfull + MOM_SLOTS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    // STAT with sixteen epilogue warps: the two warps that share a row exchange their halves of the sum of
+    // squares here, [accumulator buffer][tile parity of that buffer][row]
+    float* ssx = reinterpret_cast<float*>(tmem_slot + 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t ncols = 2u * p.BNpad;
@@ -557,7 +560,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     if (stat) {
                         ss += css;
                         head_left -= 32;
-                        if (head_left == 0) {                 // chunk ends a head (dk % 32 == 0)
+                        if (!WIDE && head_left == 0) {        // chunk ends a head (dk % 32 == 0)
                             if (row < p.M)
                                 stat[stat_piece + stat_base + (long long)head * p.rows_per_batch] =
                                     (p.stat_mode == CONVNN_COSINE && p.stat_pieces == 1) ? 1.0f / fmaxf(sqrtf(ss), 1e-12f) : ss;
@@ -628,6 +631,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 if (PAIR) mbar_arrive_cluster(lead_tempty0 + 8 * buf);
                 else mbar_arrive(&tempty[buf]);
             }
+            if (STAT && WIDE) {
+                // one head per tile (dk = BN): this warp has the sum over its half of the columns; the upper
+                // half's warp hands its part over, the lower half's warp writes the statistic
+                if (stat) {
+                    float* slot = ssx + ((buf * 2u + (u & 1u)) * BM) + r;
+                    if (chalf) *slot = ss;
+                    asm volatile("bar.sync %0, 64;" ::"r"(1 + half * 4 + lq) : "memory");
+                    if (!chalf && row < p.M) {
+                        const float tot = ss + *slot;
+                        stat[stat_base + (long long)head * p.rows_per_batch] =
+                            p.stat_mode == CONVNN_COSINE ? 1.0f / fmaxf(sqrtf(tot), 1e-12f) : tot;
+                    }
+                }
+            }
             if (MOM) {
                 // the four lanes that share a row add up; plane = (column tile, column half)
                 float2* mplane = p.moments_out + (long long)(nt * 2 + chalf) * p.mom_ld;
@@ -691,11 +708,11 @@ bool gemm_tc_can_fuse_stats(int part_cols, int dk) {
 
 // Shared-memory plan of the pre-norm fold (W-resident mode is required: the extra W rows travel with
 // the W tile).  Returns the ring depth (>= 3) or 0 when the W tile does not fit.
-static int prenorm_stages(int BN, int Kd, bool wide, int planes) {
+static int prenorm_stages(int BN, int Kd, bool wide, int planes, bool wide_stat = false) {
     const int KCH = Kd % 64 == 0 ? 64 : (Kd % 32 == 0 ? 32 : 16);
     const size_t pitch = (size_t)KCH * 2, a_bytes = BM * pitch, w_tile = (size_t)(Kd / KCH) * BN * pitch;
     const size_t fixed = 1024 + (wide ? 16 : 8) * 2048 + 1024 + 2 * 4096 + (((size_t)BN * 32 + 1023) & ~(size_t)1023) +
-                         2 * BM * 4 + (size_t)MOM_SLOTS * planes * 1024 + (2 * MAX_STAGES + 7 + MOM_SLOTS) * 8 + 16;
+                         2 * BM * 4 + (size_t)MOM_SLOTS * planes * 1024 + (2 * MAX_STAGES + 7 + MOM_SLOTS) * 8 + 16 + (wide_stat ? 2048 : 0);
     if (fixed + w_tile + 3 * a_bytes > 226 * 1024) return 0;
     const int st = (int)((226 * 1024 - fixed - w_tile) / a_bytes);
     return st > MAX_STAGES ? MAX_STAGES : st;
@@ -798,7 +815,11 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
     // connection) is bound by its own instruction latencies: sixteen epilogue warps (each tile's
     // columns split between two warps per TMEM lane quarter) cover them better than eight warps
     // with ping-pong registers.
-    const bool wide = !has_stat && ((o.bias && !bias_by_mma) || o.gelu || o.residual);
+    // The statistic epilogue of the folded K/V/Q projection too, where a tile is one head (the two warps
+    // of a row exchange their halves of the sum of squares).
+    const bool wide_stat = lnf && has_stat && p.stat_pieces == 1 && p.dk == p.BN && p.BN % 64 == 0 &&
+                           prenorm_stages(p.BN, Kd, true, o.ln_planes, true) >= 3;
+    const bool wide = wide_stat || (!has_stat && ((o.bias && !bias_by_mma) || o.gelu || o.residual));
     size_t fixed = 1024 + (wide ? 16 : 8) * 2048 + (2 * MAX_STAGES + 7 + MOM_SLOTS) * 8 + 16;
     // W-resident mode is judged against 200 KB (with more, shapes whose W tile barely fits would
     // be left with a ring too short to cover the TMA latency); the streaming ring takes all the
@@ -816,7 +837,7 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
     p.wstat = (w_tile + 3 * a_bytes + fixed <= budget && p.n_tiles >= 2 * sms) ? 1 : 0;
     int lnf_stages = 0;
     if (lnf) {
-        lnf_stages = prenorm_stages(p.BN, Kd, wide, o.ln_planes);
+        lnf_stages = prenorm_stages(p.BN, Kd, wide, o.ln_planes, wide_stat);
         if (lnf_stages < 3)
             return set_error(CONVNN_E_UNSUPPORTED, "gemm_tc: the pre-norm fold needs the %d x %d tile of W resident in shared memory", p.BN, Kd);
         p.wstat = 1;
@@ -951,7 +972,8 @@ int launch_gemm_tc(const void* a, long long lda, const void* w, int M, int N, in
         else CONVNN_GEMM_LAUNCH1(S, B, G, R, false);            \
     } while (0)
     if (lnf) {
-        if (has_stat) CONVNN_GEMM_LAUNCH_X(true, false, false, false, true, false);
+        if (has_stat && wide) CONVNN_GEMM_LAUNCH_X(true, false, false, true, true, false);
+        else if (has_stat) CONVNN_GEMM_LAUNCH_X(true, false, false, false, true, false);
         else if (p.gelu) CONVNN_GEMM_LAUNCH_X(false, true, false, true, true, false);
         else CONVNN_GEMM_LAUNCH_X(false, false, false, false, true, false);
     } else if (o.moments_out) {
