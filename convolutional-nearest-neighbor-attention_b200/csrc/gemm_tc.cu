@@ -204,9 +204,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint64_t* mfull = xfull + 2;                               // LNF: moment tile landed in ring slot 0..3
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mfull + MOM_SLOTS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    // STAT with sixteen epilogue warps: the two warps that share a row exchange their halves of the sum of
-    // squares here, [accumulator buffer][tile parity of that buffer][row]
+    // STAT with sixteen epilogue warps: the upper column half's warp hands its part of a row's sum of squares
+    // to the lower half's warp here, [accumulator buffer][tile parity of that buffer][row], and then publishes
+    // the count of tiles it has handed over in ssx_seq[buffer * 4 + lane quarter]
     float* ssx = reinterpret_cast<float*>(tmem_slot + 4);
+    volatile uint32_t* ssx_seq = reinterpret_cast<volatile uint32_t*>(ssx + 4 * BM);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t ncols = 2u * p.BNpad;
@@ -224,6 +226,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         mbar_init(&xfull[0], 1);
         mbar_init(&xfull[1], 1);
         for (int i = 0; i < MOM_SLOTS; ++i) mbar_init(&mfull[i], 1);
+        if (STAT && WIDE)
+            for (int i = 0; i < 8; ++i) ssx_seq[i] = 0u;
         *abort_flag = 0;
         fence_barrier_init();
         prefetch_tensormap(&tmA);
@@ -633,15 +637,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
             if (STAT && WIDE) {
                 // one head per tile (dk = BN): this warp has the sum over its half of the columns; the upper
-                // half's warp hands its part over, the lower half's warp writes the statistic
+                // half's warp hands its part over, the lower half's warp writes the statistic.  A slot is
+                // rewritten two tiles of this buffer later, after both warps have released the accumulator
+                // in between; the wait is bounded like every other.
                 if (stat) {
                     float* slot = ssx + ((buf * 2u + (u & 1u)) * BM) + r;
-                    if (chalf) *slot = ss;
-                    asm volatile("bar.sync %0, 64;" ::"r"(1 + half * 4 + lq) : "memory");
-                    if (!chalf && row < p.M) {
-                        const float tot = ss + *slot;
-                        stat[stat_base + (long long)head * p.rows_per_batch] =
-                            p.stat_mode == CONVNN_COSINE ? 1.0f / fmaxf(sqrtf(tot), 1e-12f) : tot;
+                    volatile uint32_t* seq = ssx_seq + half * 4 + lq;
+                    if (chalf) {
+                        *slot = ss;
+                        __threadfence_block();
+                        __syncwarp();
+                        if (lane == 0) *seq = u + 1u;
+                    } else {
+                        bool got = *seq >= u + 1u;
+                        if (!got) {
+                            const unsigned long long t0 = global_timer_ns();
+                            for (uint32_t i = 0; i < kWaitPollLimit && !got; ++i) {
+                                got = *seq >= u + 1u;
+                                if (!got && (i & 255u) == 255u && (*abort_flag || global_timer_ns() - t0 > kWaitBudgetNs)) break;
+                            }
+                        }
+                        got = __all_sync(0xffffffffu, got);
+                        if (!got) { if (lane == 0) give_up(20); ok = false; }
+                        __threadfence_block();
+                        if (got && row < p.M) {
+                            const float tot = ss + *reinterpret_cast<volatile float*>(slot);
+                            stat[stat_base + (long long)head * p.rows_per_batch] =
+                                p.stat_mode == CONVNN_COSINE ? 1.0f / fmaxf(sqrtf(tot), 1e-12f) : tot;
+                        }
                     }
                 }
             }
@@ -712,7 +735,7 @@ static int prenorm_stages(int BN, int Kd, bool wide, int planes, bool wide_stat 
     const int KCH = Kd % 64 == 0 ? 64 : (Kd % 32 == 0 ? 32 : 16);
     const size_t pitch = (size_t)KCH * 2, a_bytes = BM * pitch, w_tile = (size_t)(Kd / KCH) * BN * pitch;
     const size_t fixed = 1024 + (wide ? 16 : 8) * 2048 + 1024 + 2 * 4096 + (((size_t)BN * 32 + 1023) & ~(size_t)1023) +
-                         2 * BM * 4 + (size_t)MOM_SLOTS * planes * 1024 + (2 * MAX_STAGES + 7 + MOM_SLOTS) * 8 + 16 + (wide_stat ? 2048 : 0);
+                         2 * BM * 4 + (size_t)MOM_SLOTS * planes * 1024 + (2 * MAX_STAGES + 7 + MOM_SLOTS) * 8 + 16 + (wide_stat ? 2048 + 64 : 0);
     if (fixed + w_tile + 3 * a_bytes > 226 * 1024) return 0;
     const int st = (int)((226 * 1024 - fixed - w_tile) / a_bytes);
     return st > MAX_STAGES ? MAX_STAGES : st;
