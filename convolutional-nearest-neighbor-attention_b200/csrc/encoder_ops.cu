@@ -36,7 +36,7 @@ __device__ __forceinline__ float warp_sum(float v) {
 // registers).  Output row r goes to y + out_row(r) * ldy; with `pe` != nullptr the kernel
 // is the embedding tail: row r = (b, n) of the patch projection lands at token 1 + n of
 // image b with pe[1 + n] added after rounding, and `cls_rows` extra rows write cls + pe[0].
-template <typename T, int NV>
+template <typename T, int NV, bool EMBED>
 __global__ void __launch_bounds__(256) layernorm_kernel(const T* __restrict__ x, long long ldx,
                                                         const T* __restrict__ gamma, const T* __restrict__ beta,
                                                         float eps, T* __restrict__ y, long long ldy, long long rows,
@@ -49,7 +49,7 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const T* __restrict__ x,
     const long long wpb = blockDim.x >> 5;
     const int nvec = D / V;
     for (long long r = blockIdx.x * wpb + (threadIdx.x >> 5); r < rows + cls_rows; r += (long long)gridDim.x * wpb) {
-        if (r >= rows) {                       // class-token row of image b: cls + pe[0]
+        if (EMBED && r >= rows) {              // class-token row of image b: cls + pe[0]
             const long long b = r - rows;
             T* out = y + b * (Np + 1) * ldy;
             float m1 = 0.f, m2 = 0.f;
@@ -76,20 +76,20 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const T* __restrict__ x,
         const T* in = x + r * ldx;
         long long orow = r;
         const T* perow = nullptr;
-        if (pe) {
+        if (EMBED && pe) {
             const long long b = r / Np, n = r - b * Np;
             orow = b * (Np + 1) + 1 + n;
             perow = pe + (1 + n) * (long long)D;
         }
         float v[NV][V];
-        uint4 pv_raw[NV];                       // the positional row, fetched with the input row
+        uint4 pv_raw[EMBED ? NV : 1];           // the positional row, fetched with the input row
         float s = 0.f;
 #pragma unroll
         for (int k = 0; k < NV; ++k) {
             const int i = lane + 32 * k;
             if (i < nvec) {
                 load_vec<T>(in + i * V, v[k]);
-                if (perow) pv_raw[k] = *reinterpret_cast<const uint4*>(perow + i * V);
+                if (EMBED && perow) pv_raw[EMBED ? k : 0] = *reinterpret_cast<const uint4*>(perow + i * V);
 #pragma unroll
                 for (int j = 0; j < V; ++j) s += v[k][j];
             }
@@ -119,12 +119,12 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const T* __restrict__ x,
                 load_vec<T>(beta + i * V, bt);
 #pragma unroll
                 for (int j = 0; j < V; ++j) o[j] = (v[k][j] - mean) * rstd * g[j] + bt[j];
-                if (perow) {
-                    const T* pv = reinterpret_cast<const T*>(&pv_raw[k]);
+                if (EMBED && perow) {
+                    const T* pv = reinterpret_cast<const T*>(&pv_raw[EMBED ? k : 0]);
 #pragma unroll
                     for (int j = 0; j < V; ++j) o[j] = to_f32<T>(from_f32<T>(o[j])) + to_f32<T>(pv[j]);
                 }
-                if (moments) {
+                if (EMBED && moments) {
 #pragma unroll
                     for (int j = 0; j < V; ++j) {
                         const float rv = to_f32<T>(from_f32<T>(o[j]));
@@ -135,7 +135,7 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const T* __restrict__ x,
                 store_vec<T>(out + i * V, o);
             }
         }
-        if (moments) {
+        if (EMBED && moments) {
             m1 = warp_sum(m1);
             m2 = warp_sum(m2);
             if (lane == 0) moments[orow] = make_float2(m1, m2);
@@ -397,10 +397,19 @@ int ln_dispatch(const void* x, long long ldx, const void* gamma, const void* bet
     int blocks = (int)((total + 7) / 8);
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (blocks < 1) blocks = 1;
+    // the plain LayerNorm is a kernel of its own: the embedding tail's extra state costs it registers (64 -> 100 at
+    // 768 channels) and with them half of its resident warps
 #define CONVNN_LN(NVV)                                                                                          \
-    layernorm_kernel<T, NVV><<<blocks, 256, 0, st>>>(static_cast<const T*>(x), ldx, static_cast<const T*>(gamma), \
-        static_cast<const T*>(beta), eps, static_cast<T*>(y), ldy, rows, D, static_cast<const T*>(pe),          \
-        static_cast<const T*>(cls), Np, cls_rows, reinterpret_cast<float2*>(moments))
+    do {                                                                                                        \
+        if (pe)                                                                                                 \
+            layernorm_kernel<T, NVV, true><<<blocks, 256, 0, st>>>(static_cast<const T*>(x), ldx,              \
+                static_cast<const T*>(gamma), static_cast<const T*>(beta), eps, static_cast<T*>(y), ldy, rows, D, \
+                static_cast<const T*>(pe), static_cast<const T*>(cls), Np, cls_rows, reinterpret_cast<float2*>(moments)); \
+        else                                                                                                    \
+            layernorm_kernel<T, NVV, false><<<blocks, 256, 0, st>>>(static_cast<const T*>(x), ldx,             \
+                static_cast<const T*>(gamma), static_cast<const T*>(beta), eps, static_cast<T*>(y), ldy, rows, D, \
+                nullptr, nullptr, 0, 0, nullptr);                                                               \
+    } while (0)
     if (nv <= 1) CONVNN_LN(1);
     else if (nv <= 2) CONVNN_LN(2);
     else if (nv <= 4) CONVNN_LN(4);
@@ -420,6 +429,7 @@ int launch_layernorm(int dtype, const void* x, long long ldx, const void* gamma,
     if (D % V != 0 || ldx % V != 0 || ldy % V != 0 || !aligned16(x) || !aligned16(y) || !aligned16(gamma) ||
         !aligned16(beta) || (pe && (!aligned16(pe) || !aligned16(cls))))
         return set_error(CONVNN_E_ALIGN, "layernorm: D, strides and pointers must be multiples of 16 bytes");
+    if (moments && !pe) return set_error(CONVNN_E_INVALID, "layernorm: row moments come from the embedding tail only");
     if (dtype == CONVNN_BF16 && D <= 256 && (pe ? (cls != nullptr && rows < (1ll << 31) && Np > 0) : !moments)) {
         // Two 8-warp CTAs per SM (the kernel keeps 121 registers: four rows in flight and four
         // requested per warp), measured 9.6 us at 50 k rows of 192 channels against 11.0 us with
