@@ -192,6 +192,25 @@ def test_encoder_ops_match_torch(dtype, tol):
     assert rel_err(got, ref) < max(tol, 6e-3 if dtype == torch.bfloat16 else tol)
 
 
+@pytest.mark.parametrize("D", [64, 192, 256, 384, 768, 1024])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_layernorm_widths(D, dtype):
+    """Every instantiation of the LayerNorm kernels (vectors per lane 1, 2, 4, 8; the four-rows-per-warp
+    bfloat16 kernel below 257 channels) against float64, on contiguous rows and on a column slice."""
+    g = torch.Generator().manual_seed(D)
+    rows = 1000
+    x = (torch.randn(rows, D, generator=g) * 2 + 0.5).to(DEV, dtype)
+    w = (1 + 0.1 * torch.randn(D, generator=g)).to(DEV, dtype)
+    b = (0.1 * torch.randn(D, generator=g)).to(DEV, dtype)
+    want = torch.nn.functional.layer_norm(x.double(), (D,), w.double(), b.double(), 1e-5)
+    tol = 1e-5 if dtype == torch.float32 else 4e-3
+    assert rel_err(ops.layernorm(x, w, b, 1e-5), want) < tol
+    wide = (torch.randn(rows, 2 * D, generator=g)).to(DEV, dtype)
+    part = wide[:, D:]                                  # rows with a stride of 2 D
+    want = torch.nn.functional.layer_norm(part.double(), (D,), w.double(), b.double(), 1e-5)
+    assert rel_err(ops.layernorm(part, w, b, 1e-5), want) < tol
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_uint8_images_are_normalised_in_the_unfold(dtype):
     """8-bit images through convnn_b200_patchify_u8 equal the float path fed with the loader's
