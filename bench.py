@@ -116,12 +116,14 @@ def inner_iters_for(steps: int) -> int:
     return max(1, -(-640 // max(1, steps)))
 
 
-def config_record(world: int, inner: int) -> dict:
+def config_record(world: int, inner: int, lanes: int = 2) -> dict:
     return {"workload": WORKLOAD_NAME, "batch_per_gpu": BATCH_PER_GPU, "global_batch": BATCH_PER_GPU * world,
             "inner_iters": inner, "images_per_step": BATCH_PER_GPU * world * inner,
             "parallelism": f"batch-shard x{world}",
-            "l2": "3 distinct resident input batches (231 MB) rotate, larger than L2",
-            "launch": "cuda_graph (one per resident input batch, one memory pool; a replay reads its batch in place)",
+            "l2": "4 distinct resident input batches (308 MB) rotate, larger than L2",
+            "launch": "cuda_graph (one per resident input batch; a replay reads its batch in place)",
+            "batches_in_flight": f"{lanes} (convnn_b200.ForwardLanes: that many streams, each replaying the graphs of its "
+                                 "input buffers out of a memory pool of its own)",
             "e2e_host_images": "uint8 (normalised on the GPU); `e2e_bf16_images`: pre-normalised bfloat16",
             "collective": "none (one rank)" if world == 1 else
                           "one NCCL all_gather_into_tensor of the logits per group of batches (default: per step), "
@@ -142,7 +144,7 @@ def run_reference_arm(args) -> int:
         "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": done,
         "warmup": warm, "ms_per_step": per * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": config_record(int(os.environ.get("WORLD_SIZE", "1")), args.inner_iters),
+        "config": config_record(int(os.environ.get("WORLD_SIZE", "1")), args.inner_iters, max(1, args.lanes)),
         "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": kind,
                          "sample": f"{done} forwards of {batch} images (a sample of the workload's 256-image batches), "
                                    f"fp32, torch CPU, {what}"},
@@ -632,27 +634,32 @@ def run_ours(args) -> int:
     B = BATCH_PER_GPU
     classes = WORKLOAD["num_classes"]
     g = torch.Generator(device="cpu").manual_seed(100 + rank)
-    NBUF = 3   # 3 x 77 MB of distinct resident inputs > 126 MB L2
+    NBUF = 4   # 4 x 77 MB of distinct resident inputs > 126 MB L2, two per lane
+    LANES = max(1, args.lanes)
     host = [torch.randn(B, 3, 224, 224, generator=g).to(torch.bfloat16).pin_memory() for _ in range(NBUF)]
     resident = [h.to(dev) for h in host]
     total = B * world
 
     # One CUDA graph of the whole forward per resident input batch (ctypes launches on the capturing
-    # stream are captured): a replay reads its batch where it lies, no staging copy in between.
+    # stream are captured): a replay reads its batch where it lies, no staging copy in between.  The
+    # batches run on LANES streams at once (convnn_b200.ForwardLanes: a lane's graphs share a memory pool):
+    # the second batch's kernels fill the tails of the first one's.
     with torch.no_grad():
         model(resident[0])                # builds the packed / folded weights (launches of their own, once)
+        torch.cuda.synchronize()
         n_cap = lib.convnn_b200_launch_count()
-        fwd = [graph_model(model, resident[0])]
-        per_forward = (lib.convnn_b200_launch_count() - n_cap) // 3      # two eager calls + the capture
-        fwd += [graph_model(model, r, pool=fwd[0][0].pool()) for r in resident[1:]]
+        model(resident[0])
+        torch.cuda.synchronize()
+        per_forward = lib.convnn_b200_launch_count() - n_cap
+        fl = convnn_b200.ForwardLanes(model, resident, lanes=LANES)
     from convnn_b200.sharded import LogitsGather
     per_flush = args.gather_every if args.gather_every > 0 else inner
     gather = LogitsGather(world, per_flush, B, classes, torch.bfloat16, dev)    # default: one collective per step
 
     def batch_step(i):
-        g_i, out_i = fwd[i % NBUF]
-        g_i.replay()
-        return gather.add(out_i)
+        k = i % NBUF
+        with fl.lane(k):
+            return gather.add(fl.replay(k))
 
     def barrier():
         if world > 1:
@@ -662,19 +669,23 @@ def run_ours(args) -> int:
     with torch.no_grad():
         # ---- device-resident timing -------------------------------------------------------
         n = 0
+        fl.fork()
         for _ in range(args.warmup):
             for _ in range(inner):
                 batch_step(n)
                 n += 1
+        fl.join()
         gather.drain()
         barrier()
         sampler = ClockSampler(local) if rank == 0 else None
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
+        fl.fork()
         for _ in range(args.steps):
             for _ in range(inner):
                 batch_step(n)
                 n += 1
+        fl.join()
         gather.drain()
         e1.record()
         barrier()
@@ -687,27 +698,25 @@ def run_ours(args) -> int:
         out_host = torch.empty(world * inner * B, classes, dtype=torch.bfloat16).pin_memory()   # one step's logits
 
         def e2e_timed(host_batches):
-            """ms for args.steps x inner batches from pinned host batches: two staging buffers on the
-            device, each with its own graph of the forward, filled in turn by the copy stream."""
-            staging = [host_batches[0].to(dev), host_batches[1 % len(host_batches)].to(dev)]
-            graphs = graph_model_per_input(model, staging)
-            ready = [torch.cuda.Event() for _ in range(2)]
-            freed = [torch.cuda.Event() for _ in range(2)]
+            """ms for args.steps x inner batches from pinned host batches: two staging buffers per lane on
+            the device, each with its own graph of the forward, filled in turn by the copy stream."""
+            NS = 2 * LANES
+            staging = [host_batches[k % len(host_batches)].to(dev) for k in range(NS)]
+            lf = convnn_b200.ForwardLanes(model, staging, lanes=LANES)
+            ready = [torch.cuda.Event() for _ in range(NS)]
 
             def run(n_batches):
                 cur = torch.cuda.current_stream()
-                for f in freed:
-                    f.record(cur)
+                lf.fork()
+                copy_stream.wait_stream(cur)
                 for i in range(n_batches):
-                    s = i % 2
+                    k = i % NS
                     with torch.cuda.stream(copy_stream):
-                        copy_stream.wait_event(freed[s])
-                        staging[s].copy_(host_batches[i % len(host_batches)], non_blocking=True)
-                        ready[s].record(copy_stream)
-                    cur.wait_event(ready[s])
-                    graphs[s][0].replay()
-                    group = gather.add(graphs[s][1])
-                    freed[s].record(cur)
+                        copy_stream.wait_event(lf.done[k])     # the forward that last read this buffer
+                        staging[k].copy_(host_batches[i % len(host_batches)], non_blocking=True)
+                        ready[k].record(copy_stream)
+                    with lf.lane(k):
+                        group = gather.add(lf.replay(k, after=ready[k]))
                     if group is not None:
                         # a step's logits are complete (and gathered): read them back on a stream of their
                         # own (behind the input copies they would hold up the next batch)
@@ -715,6 +724,7 @@ def run_ours(args) -> int:
                         with torch.cuda.stream(d2h_stream):
                             d2h_stream.wait_event(done)
                             out_host[: logits.numel() // classes].view(logits.shape).copy_(logits, non_blocking=True)
+                lf.join()
                 gather.drain()
                 cur.wait_stream(copy_stream)
                 cur.wait_stream(d2h_stream)
@@ -741,22 +751,26 @@ def run_ours(args) -> int:
         if world > 1:
             Bs = BATCH_PER_GPU // world
             xs = [r[:Bs].contiguous() for r in resident]
-            s_fwd = graph_model_per_input(model, xs)
+            s_fwd = convnn_b200.ForwardLanes(model, xs, lanes=LANES)
             s_gather = LogitsGather(world, per_flush, Bs, classes, torch.bfloat16, dev)
 
             def strong_step(i):
-                g_i, out_i = s_fwd[i % NBUF]
-                g_i.replay()
-                s_gather.add(out_i)
-            for i in range(10):
+                k = i % NBUF
+                with s_fwd.lane(k):
+                    s_gather.add(s_fwd.replay(k))
+            s_fwd.fork()
+            for i in range(12):
                 strong_step(i)
+            s_fwd.join()
             s_gather.drain()
             barrier()
             n_strong = max(50, args.steps * inner)
             g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             g0.record()
+            s_fwd.fork()
             for i in range(n_strong):
                 strong_step(i)
+            s_fwd.join()
             s_gather.drain()
             g1.record()
             barrier()
@@ -806,7 +820,7 @@ def run_ours(args) -> int:
             "metric": METRIC, "value": total * n_batches / (ms / 1e3), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": config_record(world, inner),
+            "config": config_record(world, inner, LANES),
             "ms_per_batch": ms / n_batches, "host_numa_bound": bool(numa_bound),
             "per_rank_ms_per_batch": {"device_resident": [r[0] / n_batches for r in per_rank],
                                       "e2e": [r[3] / n_batches for r in per_rank]},
@@ -836,7 +850,7 @@ def run_ours(args) -> int:
 
         if world == 1 and not args.no_extras:
             with torch.no_grad():
-                fwd.clear()
+                del fl                                   # the graphs and their pools
                 torch.cuda.empty_cache()
                 line["configs"] = other_configs(dev)
                 line["layer_sweep"] = layer_sweep(dev, [4096, 16384])
@@ -854,6 +868,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--inner-iters", type=int, default=0,
                     help="batches per step (default: chosen so that the timed region lasts about a second)")
+    ap.add_argument("--lanes", type=int, default=2,
+                    help="batches in flight per GPU (CUDA streams with a graph set each); 1 = one after another")
     ap.add_argument("--gather-every", type=int, default=0,
                     help="batches per logits all-gather at N > 1 (default: one collective per step)")
     ap.add_argument("--no-extras", action="store_true", help="skip the cfg-3 / cfg-4 models and the layer sweep")

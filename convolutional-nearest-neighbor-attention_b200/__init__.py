@@ -3,7 +3,8 @@
 Import as ``convnn_b200`` (a shim at the repository root aliases this package, whose
 directory name is not a Python identifier).
 """
-from . import build, _capi, ops, layers, vit, dropin, sharded  # noqa: F401
+from . import build, _capi, ops, layers, vit, dropin, sharded, lanes  # noqa: F401
+from .lanes import ForwardLanes  # noqa: F401
 from .layers import (MultiHeadAttention, MultiHeadBranchingAttention, MultiHeadBranchingConv,  # noqa: F401
                      MultiHeadConv1dAttention, MultiHeadConvNNAttention)
 from .ops import LayerSpec  # noqa: F401

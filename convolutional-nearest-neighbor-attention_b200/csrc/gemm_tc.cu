@@ -335,7 +335,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const uint64_t dhi32 = kmajor_desc_hi(32);
             const uint64_t ones_desc = dhi32 | (uint64_t)((smem_u32(ones) & 0x3FFFFu) >> 4);
             const uint32_t btile0 = smem_u32(btile) & 0x3FFFFu;
-            uint32_t s = 0, ph = 0, tile = 0, wloads = 0;
+            uint32_t s = 0, ph = 0, tile = 0, wloads = 0, last_stage = 0;
             int cur_nt = -1;
             bool ok = true;
             const bool tr = !PAIR && trace_enabled() && blockIdx.x == 0;
@@ -373,7 +373,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         mma_commit_pair(peer_empty0 + 8 * s);
                     } else {
                         mma_chunk(d_tmem, adesc, bdesc, idesc, nk16, (kc != 0) | mbias);
-                        mma_commit_a(empty0 + 8 * s);
+                        // LNF: the tile's last stage is released behind the extra MMA below.  The producer takes
+                        // the release of the most recently filled stage as "every MMA that reads the resident W
+                        // tile has completed" before it loads the next W tile, and the extra MMA reads the
+                        // extra rows that travel with that tile.
+                        if (LNF && kc == p.KC - 1) last_stage = s;
+                        else mma_commit_a(empty0 + 8 * s);
                     }
                     if (++s == STAGES) { s = 0; ph ^= 1u; }
                 }
@@ -384,6 +389,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     const uint64_t xa_desc = dhi32 | (uint64_t)(((smem_u32(xa) + buf * 4096u) & 0x3FFFFu) >> 4);
                     const uint64_t xb_desc = dhi32 | (uint64_t)((smem_u32(xb) & 0x3FFFFu) >> 4);
                     mma_bf16_ss(d_tmem, xa_desc, xb_desc, idesc, 1);
+                    mma_commit_a(empty0 + 8 * last_stage);
                 }
                 if (ok) {
                     if (PAIR) { mma_commit_pair(tfull0 + 8 * buf); mma_commit_pair(peer_tfull0 + 8 * buf); }

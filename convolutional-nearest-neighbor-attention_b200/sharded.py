@@ -52,12 +52,15 @@ class LogitsGather:
     collective on a side stream, double-buffered, so that the exchange of one group of batches runs
     under the forwards of the next group instead of between them on the compute stream.  (A
     collective per batch costs its launch latency and a slice of the SMs every 2 ms; the logits of
-    32 ViT-Tiny batches are 16 MB per rank.)  With one rank it only collects."""
+    32 ViT-Tiny batches are 16 MB per rank.)  With one rank it only collects.  ``add`` may be called from
+    different streams (batches in flight on several lanes): every add is ordered on the stream that is
+    current at the call, and the flush waits for all of them."""
 
     def __init__(self, world, batches_per_flush, n_local, classes, dtype, dev):
         self.world, self.per, self.n_local = world, max(1, int(batches_per_flush)), n_local
         self.local = [torch.empty(self.per, n_local, classes, dtype=dtype, device=dev) for _ in range(2)]
         self.copied = [torch.cuda.Event() for _ in range(2)]
+        self.added = [[torch.cuda.Event() for _ in range(self.per)] for _ in range(2)]
         self.done = [torch.cuda.Event() for _ in range(2)]
         self.slot, self.j = 0, 0
         self.last = None                         # (tensor with the most recent group's logits, event that says when)
@@ -70,9 +73,9 @@ class LogitsGather:
         of the group this call completed, else None."""
         s = self.slot
         cur = torch.cuda.current_stream()
-        if self.j == 0:
-            cur.wait_event(self.done[s])         # whoever last read this slot has finished
+        cur.wait_event(self.done[s])             # whoever last read this slot has finished
         self.local[s][self.j].copy_(logits, non_blocking=True)
+        self.added[s][self.j].record(cur)
         self.j += 1
         return self.flush() if self.j == self.per else None
 
@@ -81,6 +84,8 @@ class LogitsGather:
             return self.last
         s, n = self.slot, self.j
         cur = torch.cuda.current_stream()
+        for e in self.added[s][:n]:              # adds made on other streams
+            cur.wait_event(e)
         self.copied[s].record(cur)
         if self.world > 1:
             with torch.cuda.stream(self.side):

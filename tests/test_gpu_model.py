@@ -311,3 +311,35 @@ def test_linear_on_cta_pairs():
     assert rel_err(z, h.float() + (x.float() @ W3.float().t() + b1.float())) < 1.2e-2
     torch.cuda.synchronize()
     assert _capi.device_status() == 0
+
+
+def test_forward_lanes_reproduce_the_eager_forward():
+    """Two batches in flight (convnn_b200.ForwardLanes: one stream and one graph pool per lane) give the
+    bits of the eager forward for every input buffer, whatever the interleaving, and LogitsGather
+    collects adds made on different streams in call order."""
+    from convnn_b200.sharded import LogitsGather
+    cfg, sd, _, _ = vit_case("vit_tiny_cifar_convnn")
+    model = build_vit(cfg, sd, torch.bfloat16)
+    g = torch.Generator().manual_seed(3)
+    xs = [torch.randn(6, *cfg.img_size, generator=g).to(DEV, torch.bfloat16) for _ in range(4)]
+    with torch.no_grad():
+        want = [model(x).clone() for x in xs]
+        fl = convnn_b200.ForwardLanes(model, xs, lanes=2)
+        gather = LogitsGather(1, 8, 6, want[0].shape[-1], torch.bfloat16, torch.device(DEV))
+        fl.fork()
+        groups = []
+        for i in range(16):
+            k = i % 4
+            with fl.lane(k):
+                done = gather.add(fl.replay(k))
+            if done is not None:
+                groups.append(done)
+        fl.join()
+        torch.cuda.synchronize()
+    for k in range(4):
+        assert torch.equal(fl.outputs[k], want[k])
+    assert len(groups) == 2
+    logits, _ = groups[-1]
+    for j in range(8):
+        assert torch.equal(logits[j], want[j % 4])
+    assert _capi.device_status() == 0
