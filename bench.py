@@ -122,8 +122,8 @@ def config_record(world: int, inner: int, lanes: int = 2) -> dict:
             "parallelism": f"batch-shard x{world}",
             "l2": "4 distinct resident input batches (308 MB) rotate, larger than L2",
             "launch": "cuda_graph (one per resident input batch; a replay reads its batch in place)",
-            "batches_in_flight": f"{lanes} (convnn_b200.ForwardLanes: that many streams, each replaying the graphs of its "
-                                 "input buffers out of a memory pool of its own)",
+            "batches_in_flight": f"{lanes} (convnn_b200.ForwardLanes: a CUDA graph holds the forwards of that many batches "
+                                 "as parallel branches)",
             "e2e_host_images": "uint8 (normalised on the GPU); `e2e_bf16_images`: pre-normalised bfloat16",
             "collective": "none (one rank)" if world == 1 else
                           "one NCCL all_gather_into_tensor of the logits per group of batches (default: per step), "
@@ -641,9 +641,9 @@ def run_ours(args) -> int:
     total = B * world
 
     # One CUDA graph of the whole forward per resident input batch (ctypes launches on the capturing
-    # stream are captured): a replay reads its batch where it lies, no staging copy in between.  The
-    # batches run on LANES streams at once (convnn_b200.ForwardLanes: a lane's graphs share a memory pool):
-    # the second batch's kernels fill the tails of the first one's.
+    # stream are captured): a replay reads its batches where they lie, no staging copy in between.  A graph
+    # holds the forwards of LANES batches as parallel branches (convnn_b200.ForwardLanes): the second
+    # batch's kernels fill the tails of the first one's.
     with torch.no_grad():
         model(resident[0])                # builds the packed / folded weights (launches of their own, once)
         torch.cuda.synchronize()
@@ -656,10 +656,13 @@ def run_ours(args) -> int:
     per_flush = args.gather_every if args.gather_every > 0 else inner
     gather = LogitsGather(world, per_flush, B, classes, torch.bfloat16, dev)    # default: one collective per step
 
-    def batch_step(i):
-        k = i % NBUF
-        with fl.lane(k):
-            return gather.add(fl.replay(k))
+    if inner % LANES != 0:
+        raise SystemExit("--inner-iters must be a multiple of --lanes")
+
+    def group_step(i):
+        """Batches i .. i + LANES - 1 (one graph replay)."""
+        for y in fl.replay((i // LANES) % fl.n_groups):
+            gather.add(y)
 
     def barrier():
         if world > 1:
@@ -669,23 +672,19 @@ def run_ours(args) -> int:
     with torch.no_grad():
         # ---- device-resident timing -------------------------------------------------------
         n = 0
-        fl.fork()
         for _ in range(args.warmup):
-            for _ in range(inner):
-                batch_step(n)
-                n += 1
-        fl.join()
+            for _ in range(inner // LANES):
+                group_step(n)
+                n += LANES
         gather.drain()
         barrier()
         sampler = ClockSampler(local) if rank == 0 else None
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        fl.fork()
         for _ in range(args.steps):
-            for _ in range(inner):
-                batch_step(n)
-                n += 1
-        fl.join()
+            for _ in range(inner // LANES):
+                group_step(n)
+                n += LANES
         gather.drain()
         e1.record()
         barrier()
@@ -707,29 +706,28 @@ def run_ours(args) -> int:
 
             def run(n_batches):
                 cur = torch.cuda.current_stream()
-                lf.fork()
                 copy_stream.wait_stream(cur)
-                for i in range(n_batches):
-                    k = i % NS
+                for i in range(0, n_batches, LANES):
+                    gi = (i // LANES) % lf.n_groups
                     with torch.cuda.stream(copy_stream):
-                        copy_stream.wait_event(lf.done[k])     # the forward that last read this buffer
-                        staging[k].copy_(host_batches[i % len(host_batches)], non_blocking=True)
-                        ready[k].record(copy_stream)
-                    with lf.lane(k):
-                        group = gather.add(lf.replay(k, after=ready[k]))
-                    if group is not None:
-                        # a step's logits are complete (and gathered): read them back on a stream of their
-                        # own (behind the input copies they would hold up the next batch)
-                        logits, done = group
-                        with torch.cuda.stream(d2h_stream):
-                            d2h_stream.wait_event(done)
-                            out_host[: logits.numel() // classes].view(logits.shape).copy_(logits, non_blocking=True)
-                lf.join()
+                        copy_stream.wait_event(lf.done[gi])    # the forwards that last read these buffers
+                        for j, k in enumerate(lf.groups[gi]):
+                            staging[k].copy_(host_batches[(i + j) % len(host_batches)], non_blocking=True)
+                            ready[k].record(copy_stream)
+                    for y in lf.replay(gi, after=[ready[k] for k in lf.groups[gi]]):
+                        group = gather.add(y)
+                        if group is not None:
+                            # a step's logits are complete (and gathered): read them back on a stream of their
+                            # own (behind the input copies they would hold up the next batch)
+                            logits, done = group
+                            with torch.cuda.stream(d2h_stream):
+                                d2h_stream.wait_event(done)
+                                out_host[: logits.numel() // classes].view(logits.shape).copy_(logits, non_blocking=True)
                 gather.drain()
                 cur.wait_stream(copy_stream)
                 cur.wait_stream(d2h_stream)
 
-            run(max(2, args.warmup))
+            run(max(2, args.warmup) * LANES)
             barrier()
             f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             f0.record()
@@ -755,22 +753,18 @@ def run_ours(args) -> int:
             s_gather = LogitsGather(world, per_flush, Bs, classes, torch.bfloat16, dev)
 
             def strong_step(i):
-                k = i % NBUF
-                with s_fwd.lane(k):
-                    s_gather.add(s_fwd.replay(k))
-            s_fwd.fork()
-            for i in range(12):
+                for y in s_fwd.replay((i // LANES) % s_fwd.n_groups):
+                    s_gather.add(y)
+            for i in range(0, 12 * LANES, LANES):
                 strong_step(i)
-            s_fwd.join()
             s_gather.drain()
             barrier()
             n_strong = max(50, args.steps * inner)
+            n_strong -= n_strong % LANES
             g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             g0.record()
-            s_fwd.fork()
-            for i in range(n_strong):
+            for i in range(0, n_strong, LANES):
                 strong_step(i)
-            s_fwd.join()
             s_gather.drain()
             g1.record()
             barrier()

@@ -314,32 +314,31 @@ def test_linear_on_cta_pairs():
 
 
 def test_forward_lanes_reproduce_the_eager_forward():
-    """Two batches in flight (convnn_b200.ForwardLanes: one stream and one graph pool per lane) give the
-    bits of the eager forward for every input buffer, whatever the interleaving, and LogitsGather
-    collects adds made on different streams in call order."""
+    """Two batches in flight (convnn_b200.ForwardLanes: the forwards of a group of input buffers are
+    parallel branches of one CUDA graph) give the bits of the eager forward for every buffer, replay
+    after replay, and LogitsGather collects them in call order."""
     from convnn_b200.sharded import LogitsGather
     cfg, sd, _, _ = vit_case("vit_tiny_cifar_convnn")
     model = build_vit(cfg, sd, torch.bfloat16)
     g = torch.Generator().manual_seed(3)
-    xs = [torch.randn(6, *cfg.img_size, generator=g).to(DEV, torch.bfloat16) for _ in range(4)]
+    xs = [torch.randn(6, *cfg.img_size, generator=g).to(DEV, torch.bfloat16) for _ in range(5)]
     with torch.no_grad():
         want = [model(x).clone() for x in xs]
         fl = convnn_b200.ForwardLanes(model, xs, lanes=2)
-        gather = LogitsGather(1, 8, 6, want[0].shape[-1], torch.bfloat16, torch.device(DEV))
-        fl.fork()
+        assert fl.groups == [[0, 1], [2, 3], [4]]
+        gather = LogitsGather(1, 10, 6, want[0].shape[-1], torch.bfloat16, torch.device(DEV))
         groups = []
-        for i in range(16):
-            k = i % 4
-            with fl.lane(k):
-                done = gather.add(fl.replay(k))
-            if done is not None:
-                groups.append(done)
-        fl.join()
+        for rep in range(4):
+            for gi in range(fl.n_groups):
+                for y in fl.replay(gi):
+                    done = gather.add(y)
+                    if done is not None:
+                        groups.append(done)
         torch.cuda.synchronize()
-    for k in range(4):
+    for k in range(5):
         assert torch.equal(fl.outputs[k], want[k])
     assert len(groups) == 2
     logits, _ = groups[-1]
-    for j in range(8):
-        assert torch.equal(logits[j], want[j % 4])
+    for j in range(10):
+        assert torch.equal(logits[j], want[j % 5])
     assert _capi.device_status() == 0
