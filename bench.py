@@ -580,7 +580,7 @@ def other_configs(dev, min_ms=400.0):
         out[name] = {"images_per_s": 2 * B / (ms / 1e3), "ms_per_forward": ms / 2, "batch": B, "batches_in_flight": 2,
                      "forwards_timed": 2 * reps, "dtype": "bf16", "clocks": sampler.stop()}
         del fl
-        del graphs, model, xs
+        del model, xs
         torch.cuda.empty_cache()
     return out
 
