@@ -636,6 +636,7 @@ def run_ours(args) -> int:
     classes = WORKLOAD["num_classes"]
     g = torch.Generator(device="cpu").manual_seed(100 + rank)
     LANES = max(1, args.lanes)
+    inner += (-inner) % LANES               # whole groups of LANES batches per step (recorded in `config`)
     NBUF = 3 if LANES == 1 else 2 * LANES   # >= 3 x 77 MB of distinct resident inputs > 126 MB L2; whole groups of LANES
     host = [torch.randn(B, 3, 224, 224, generator=g).to(torch.bfloat16).pin_memory() for _ in range(NBUF)]
     resident = [h.to(dev) for h in host]
@@ -657,8 +658,6 @@ def run_ours(args) -> int:
     per_flush = args.gather_every if args.gather_every > 0 else inner
     gather = LogitsGather(world, per_flush, B, classes, torch.bfloat16, dev)    # default: one collective per step
 
-    if inner % LANES != 0:
-        raise SystemExit("--inner-iters must be a multiple of --lanes")
 
     def group_step(i):
         """Batches i .. i + LANES - 1 (one graph replay)."""
