@@ -530,29 +530,6 @@ OTHER_CONFIGS = {
 }
 
 
-def graph_model(model, x, pool=None):
-    """Capture model(x) in a CUDA graph (after two eager warm-up calls) -> (graph, static output).
-    Graphs of the same model over different input batches are captured into one memory pool
-    (`pool` = the first graph's): their intermediates then occupy the same addresses, as they do in a
-    server with one workspace, instead of a private set per graph that evicts the others' from L2
-    (measured: 2.16 ms per batch with private pools against 2.01 ms).  Such graphs must be replayed
-    one after another on one stream, which is what every loop here does."""
-    for _ in range(2):
-        model(x)
-    torch.cuda.synchronize()
-    g = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g, pool=pool):
-        y = model(x)
-    return g, y
-
-
-def graph_model_per_input(model, xs):
-    """[(graph, static output)] with one graph per input batch of `xs`, all in one memory pool."""
-    out = [graph_model(model, xs[0])]
-    out += [graph_model(model, x_, pool=out[0][0].pool()) for x_ in xs[1:]]
-    return out
-
-
 def other_configs(dev, min_ms=400.0):
     """Whole-model images/s of the baseline's other ViT configurations (device-resident inputs, two
     distinct input batches alternating, CUDA graph, >= 10 forwards and >= 400 ms each)."""
